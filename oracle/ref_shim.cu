@@ -1,0 +1,341 @@
+// C entry points over the reference's OWN code for the quantized-Linear path.
+//
+// TEST INFRASTRUCTURE ONLY. This file contains no arithmetic of its own: it
+// includes the reference's headers and test fixtures where they lie in the
+// reference tree and forwards to them, so that Python tests can run the
+// reference's host fixtures on the CPU and the reference's CUDA kernels /
+// LinearRunner on a GPU, on the same buffers as the new kernels. It is
+// compiled, together with the reference's unmodified sources, into
+// oracle/_ref/libslopfab_ref.so by oracle/Makefile. The product never loads it.
+//
+// Every function returns 0 on success and -1 after recording the exception
+// text (ref_last_error). Device pointers are plain device addresses; all device
+// entry points run on the default stream and synchronise before returning.
+
+#include "tests/detail/nn_weight_fixture.h"  // includes nn_kernels_fixture.h, dtype.h, the cuda headers
+
+#include <cstring>
+#include <string>
+
+#include "slopfab/int8_weight.h"
+
+namespace {
+thread_local std::string g_error;
+
+template <class F> int guarded(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const std::exception& e) {
+    g_error = e.what();
+    return -1;
+  } catch (...) {
+    g_error = "unknown exception";
+    return -1;
+  }
+}
+
+void sync() {
+  SLOPFAB_CUDA_CHECK(cudaDeviceSynchronize());
+}
+
+using bf16 = __nv_bfloat16;
+namespace sc = slopfab::cuda;
+}  // namespace
+
+#define REF_API extern "C" __attribute__((visibility("default")))
+
+REF_API const char* ref_last_error() { return g_error.c_str(); }
+
+// ---------------------------------------------------------------------------
+// Host fixtures (run anywhere)
+// ---------------------------------------------------------------------------
+REF_API void ref_make_data(float* out, size_t n, uint32_t seed, float scale) {
+  const auto v = make_data(n, seed, scale);
+  std::memcpy(out, v.data(), n * sizeof(float));
+}
+REF_API void ref_make_gaussian(float* out, size_t n, uint32_t seed, float sigma) {
+  const auto v = make_gaussian(n, seed, sigma);
+  std::memcpy(out, v.data(), n * sizeof(float));
+}
+REF_API uint16_t ref_f32_to_bf16(float f) { return slopfab::f32_to_bf16(f); }
+REF_API uint16_t ref_f32_to_f16(float f) { return slopfab::f32_to_f16(f); }
+REF_API float ref_f16_to_f32(uint16_t h) { return slopfab::f16_to_f32(h); }
+REF_API float ref_e4m3_to_f32(uint8_t v) { return slopfab::f8_e4m3_to_f32(v); }
+REF_API float ref_e2m1_to_f32(uint8_t v) { return slopfab::f4_e2m1_to_f32(v); }
+REF_API uint8_t ref_host_e4m3(float v) { return host_e4m3(v); }
+REF_API uint8_t ref_host_e2m1(float v) { return host_e2m1(v); }
+REF_API uint64_t ref_nvfp4_scale_slot(int o, int k, int blocks_per_row) {
+  return nvfp4_scale_slot(o, k, blocks_per_row);
+}
+
+// make_nvfp4(out, in, global, seed): random codes/scales in storage form.
+REF_API void ref_make_nvfp4(int out_features, int in_features, float global, uint32_t seed,
+                            uint8_t* packed, uint8_t* stored_scales, uint8_t* plain_scales,
+                            float* reference_bf16_values) {
+  const Nvfp4Weight w = make_nvfp4(out_features, in_features, global, seed);
+  std::memcpy(packed, w.packed.data(), w.packed.size());
+  std::memcpy(stored_scales, w.stored.data(), w.stored.size());
+  if (plain_scales) std::memcpy(plain_scales, w.scales.data(), w.scales.size());
+  if (reference_bf16_values) {
+    const auto r = nvfp4_reference(w);
+    std::memcpy(reference_bf16_values, r.data(), r.size() * sizeof(float));
+  }
+}
+
+REF_API void ref_pack_nvfp4(const float* w, int rows, int cols, float global, int high_even,
+                            int swizzled, uint8_t* data, uint8_t* scale, float* dense) {
+  const std::vector<float> in(w, w + size_t(rows) * cols);
+  const NvfpPacked p = pack_nvfp4(in, rows, cols, global, high_even != 0, swizzled != 0);
+  std::memcpy(data, p.data.data(), p.data.size());
+  std::memcpy(scale, p.scale.data(), p.scale.size());
+  if (dense) std::memcpy(dense, p.dense.data(), p.dense.size() * sizeof(float));
+}
+
+REF_API void ref_host_quantise_act(const float* x, int rows, int dim, float* out) {
+  const std::vector<float> in(x, x + size_t(rows) * dim);
+  const auto q = host_quantise_act(in, rows, dim);
+  std::memcpy(out, q.data(), q.size() * sizeof(float));
+}
+
+REF_API void ref_cpu_matmul_nt(const float* A, const float* B, int M, int N, int K, float* C) {
+  const std::vector<float> a(A, A + size_t(M) * K), b(B, B + size_t(N) * K);
+  const auto c = cpu_matmul_nt(a, b, M, N, K);
+  std::memcpy(C, c.data(), c.size() * sizeof(float));
+}
+
+REF_API void ref_cpu_rmsnorm(const float* x, const float* w, const float* scale, const float* shift,
+                             const int32_t* a, int rows, int dim, float eps, float* out) {
+  const std::vector<float> xv(x, x + size_t(rows) * dim), wv(w, w + dim);
+  std::vector<float> r;
+  if (scale) {
+    int amax = 0;
+    for (int i = 0; i < rows; ++i) amax = std::max(amax, a[i]);
+    const std::vector<float> sc(scale, scale + size_t(amax + 1) * dim), sh(shift, shift + size_t(amax + 1) * dim);
+    const std::vector<int32_t> av(a, a + rows);
+    r = cpu_modulate(xv, wv, sc, sh, av, rows, dim, eps, true);
+  } else {
+    r = cpu_rmsnorm(xv, wv, rows, dim, eps);
+  }
+  std::memcpy(out, r.data(), r.size() * sizeof(float));
+}
+
+REF_API void ref_kron_h4_256(float* out) {  // kron^4(h4), unnormalised, 256x256
+  const auto h = kron_power(&kH4[0][0], 4, 4);
+  std::memcpy(out, h.data(), h.size() * sizeof(float));
+}
+
+REF_API void ref_unpack_int8_weight(const int8_t* codes, const float* scales, int rows, int cols,
+                                    int group, int canonicalize, uint16_t* out) {
+  slopfab::Int8WeightState s;
+  s.rows = rows;
+  s.columns = cols;
+  s.rotation_group = group;
+  s.codes = codes;
+  s.scales = scales;
+  const auto v = slopfab::unpack_int8_weight(s, canonicalize != 0);
+  std::memcpy(out, v.data(), v.size() * sizeof(uint16_t));
+}
+
+// ---------------------------------------------------------------------------
+// Device kernels of the reference (need a GPU)
+// ---------------------------------------------------------------------------
+REF_API int ref_dev_dequant_nvfp4(const uint8_t* src, const uint8_t* scale, float global, void* dst,
+                                  int out_features, int in_features) {
+  return guarded([&] {
+    sc::launch_dequant_nvfp4(src, scale, global, static_cast<bf16*>(dst), out_features, in_features, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_dequant_i8(const int8_t* src, const float* scale, void* dst, int out_features,
+                               int in_features) {
+  return guarded([&] {
+    sc::launch_dequant_i8_per_channel(src, scale, static_cast<bf16*>(dst), out_features, in_features, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_dequant_w4a8(const int8_t* packed, const uint8_t* gs, const float* codebook,
+                                 int8_t* out, int out_features, int in_features, int group) {
+  return guarded([&] {
+    sc::launch_dequant_w4a8_weight(packed, gs, codebook, out, out_features, in_features, group, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_dequant_w6a8(const int8_t* packed, const uint8_t* gs, int8_t* out, int out_features,
+                                 int in_features, int group) {
+  return guarded([&] {
+    sc::launch_dequant_w6a8_weight(packed, gs, out, out_features, in_features, group, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_convrot(const void* in, void* out, int rows, int dim, int group) {
+  return guarded([&] {
+    sc::launch_convrot(static_cast<const bf16*>(in), static_cast<bf16*>(out), rows, dim, group, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_quantize_int8_bf16(const void* rotated, int8_t* q, float* scales, int rows, int width) {
+  return guarded([&] {
+    sc::launch_quantize_w4a8_bf16(static_cast<const bf16*>(rotated), q, scales, rows, width, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_quantize_int8_f16(const void* x, int8_t* q, float* scales, int rows, int width) {
+  return guarded([&] {
+    sc::launch_quantize_w4a8_activation(static_cast<const __half*>(x), q, scales, rows, width, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_output_bf16(const int32_t* acc, const float* rows_s, const float* chan_s, void* y,
+                                int rows, int cols) {
+  return guarded([&] {
+    sc::launch_w4a8_output_bf16(acc, rows_s, chan_s, static_cast<bf16*>(y), rows, cols, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_quantize_nvfp4_act(const void* x, uint8_t* packed, uint8_t* scales, int rows, int dim) {
+  return guarded([&] {
+    sc::launch_quantize_nvfp4_activations(static_cast<const bf16*>(x), packed, scales, rows, dim, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_rmsnorm(const void* x, const void* w, const float* scale, const float* shift,
+                            const int32_t* a, void* out, int rows, int dim, float eps) {
+  return guarded([&] {
+    if (scale)
+      sc::launch_rmsnorm_modulate(static_cast<const bf16*>(x), static_cast<const bf16*>(w), scale, shift, a,
+                                  static_cast<bf16*>(out), rows, dim, eps, nullptr);
+    else
+      sc::launch_rmsnorm(static_cast<const bf16*>(x), static_cast<const bf16*>(w), static_cast<bf16*>(out),
+                         rows, dim, eps, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_gelu_tanh(void* x, size_t n) {
+  return guarded([&] {
+    sc::launch_gelu_tanh(static_cast<bf16*>(x), n, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_swiglu(const void* fused, void* out, int rows, int inner) {
+  return guarded([&] {
+    sc::launch_swiglu(static_cast<const bf16*>(fused), static_cast<bf16*>(out), rows, inner, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_add_gated(void* x, const void* branch, const float* gate, const int32_t* a, int rows,
+                              int dim) {
+  return guarded([&] {
+    sc::launch_add_gated(static_cast<bf16*>(x), static_cast<const bf16*>(branch), gate, a, rows, dim, nullptr);
+    sync();
+  });
+}
+
+// ---------------------------------------------------------------------------
+// LinearRunner of the reference
+// ---------------------------------------------------------------------------
+struct RefWeight {  // plain mirror of the fields the path uses
+  int format;       // QuantFormat as int
+  const void* data;
+  int out_features, in_features;
+  const float* weight_scale;
+  int per_channel_scale;
+  const uint8_t* block_scale;
+  uint32_t packed_group_size;
+  const float* w4_codebook;
+  float global_scale;
+  int convrot, convrot_group;
+  const void* bias;
+  int bias_format;
+};
+
+namespace {
+sc::QuantWeight to_weight(const RefWeight& r) {
+  sc::QuantWeight w;
+  w.format = static_cast<sc::QuantFormat>(r.format);
+  w.data = r.data;
+  w.out_features = r.out_features;
+  w.in_features = r.in_features;
+  w.weight_scale = r.weight_scale;
+  w.per_channel_scale = r.per_channel_scale != 0;
+  w.block_scale = r.block_scale;
+  w.packed_group_size = r.packed_group_size;
+  w.w4_codebook = r.w4_codebook;
+  w.global_scale = r.global_scale;
+  w.convrot = r.convrot != 0;
+  w.convrot_group = r.convrot_group;
+  w.bias = r.bias;
+  w.bias_format = static_cast<sc::QuantFormat>(r.bias_format);
+  return w;
+}
+
+struct Runner {
+  CublasScope blas;
+  sc::LinearRunner runner;
+  Workspace ws;
+  Runner() { runner.init(blas.h, nullptr); }
+};
+Runner& runner() {
+  static Runner r;
+  return r;
+}
+}  // namespace
+
+// y = LinearRunner::forward(w, x). `iters` > 0 additionally times that many
+// repeats with CUDA events after 3 warm-ups and stores the mean milliseconds.
+REF_API int ref_dev_linear_forward(const RefWeight* rw, const void* x, int rows, void* y, int native,
+                                   int iters, float* mean_ms) {
+  return guarded([&] {
+    Runner& r = runner();
+    const sc::QuantWeight w = to_weight(*rw);
+    r.runner.set_native(native != 0);
+    r.ws.reserve(sc::linear_workspace_bytes(w, rows, sc::ComputeType::kBF16) + 4096);
+    r.runner.forward(w, static_cast<const bf16*>(x), rows, static_cast<bf16*>(y), r.ws);
+    sync();
+    if (iters > 0) {
+      for (int i = 0; i < 3; ++i)
+        r.runner.forward(w, static_cast<const bf16*>(x), rows, static_cast<bf16*>(y), r.ws);
+      cudaEvent_t a, b;
+      SLOPFAB_CUDA_CHECK(cudaEventCreate(&a));
+      SLOPFAB_CUDA_CHECK(cudaEventCreate(&b));
+      SLOPFAB_CUDA_CHECK(cudaEventRecord(a, nullptr));
+      for (int i = 0; i < iters; ++i)
+        r.runner.forward(w, static_cast<const bf16*>(x), rows, static_cast<bf16*>(y), r.ws);
+      SLOPFAB_CUDA_CHECK(cudaEventRecord(b, nullptr));
+      SLOPFAB_CUDA_CHECK(cudaEventSynchronize(b));
+      float ms = 0;
+      SLOPFAB_CUDA_CHECK(cudaEventElapsedTime(&ms, a, b));
+      cudaEventDestroy(a);
+      cudaEventDestroy(b);
+      if (mean_ms) *mean_ms = ms / float(iters);
+    }
+  });
+}
+
+// The int32 accumulators of the packed-int8 arm, produced by the same calls
+// LinearRunner::forward_prepared makes (src/cuda/linear.cu:188-203), stopping
+// before the output scaling. All buffers are caller-provided device memory.
+REF_API int ref_dev_packed_int8_accumulate(const RefWeight* rw, const void* x, int rows, int8_t* codes,
+                                           void* rotated, int8_t* activation, float* scales,
+                                           int32_t* accum) {
+  return guarded([&] {
+    Runner& r = runner();
+    const sc::QuantWeight w = to_weight(*rw);
+    if (w.format == sc::QuantFormat::kW6A8)
+      sc::launch_dequant_w6a8_weight(static_cast<const int8_t*>(w.data), w.block_scale, codes,
+                                     w.out_features, w.in_features, w.packed_group_size, nullptr);
+    else
+      sc::launch_dequant_w4a8_weight(static_cast<const int8_t*>(w.data), w.block_scale, w.w4_codebook, codes,
+                                     w.out_features, w.in_features, 16, nullptr);
+    sc::launch_convrot(static_cast<const bf16*>(x), static_cast<bf16*>(rotated), rows, w.in_features, 256,
+                       nullptr);
+    sc::launch_quantize_w4a8_bf16(static_cast<const bf16*>(rotated), activation, scales, rows, w.in_features,
+                                  nullptr);
+    const int32_t one = 1, zero = 0;
+    SLOPFAB_CUBLAS_CHECK(sc::cublas_gemm_ex(r.blas.h, CUBLAS_OP_T, CUBLAS_OP_N, w.out_features, rows,
+                                            w.in_features, &one, codes, CUDA_R_8I, w.in_features, activation,
+                                            CUDA_R_8I, w.in_features, &zero, accum, CUDA_R_32I,
+                                            w.out_features, CUBLAS_COMPUTE_32I, CUBLAS_GEMM_DEFAULT));
+    sync();
+  });
+}
