@@ -1,0 +1,265 @@
+/* sfq -- C ABI of the B200 quantized-Linear library (libsfq.so).
+ *
+ * Drop-in boundary for the quantized Linear of slopfab's DiT: weight packing and
+ * unpacking (NVFP4, W4A8, W6A8, INT8), the fused norm + activation quantizer, the
+ * tcgen05 GEMMs with their fused epilogue, and the LinearRunner dispatch above
+ * them. Each entry point names the reference interface it replaces (paths are
+ * relative to the reference project root).
+ *
+ * Conventions (modelled on include/slopfab/capi.h:172-200 and
+ * src/capi/internal.h:54-130 of the reference):
+ *   - every function returns an int status: SFQ_OK, or a negative code; the text
+ *     of the failure is available from sfq_last_error() on the calling thread;
+ *     no C++ exception crosses this boundary;
+ *   - pointers named d_* are device pointers, h_* are host pointers; nothing is
+ *     owned by the library except an opaque runner handle;
+ *   - `stream` is a cudaStream_t passed as void*; every device entry point only
+ *     enqueues work on it and never synchronises;
+ *   - weights are [out_features, in_features] row-major, contraction over the
+ *     second axis, never transposed (include/slopfab/cuda/linear.cuh:18-20).
+ *
+ * There is no CPU fallback: without a CUDA device every device entry point fails
+ * with SFQ_ERR_RUNTIME.
+ */
+#ifndef SFQ_H_
+#define SFQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define SFQ_API __declspec(dllexport)
+#else
+#define SFQ_API __attribute__((visibility("default")))
+#endif
+
+enum {
+  SFQ_OK = 0,
+  SFQ_ERR_INVALID_ARGUMENT = -1, /* std::invalid_argument in the reference */
+  SFQ_ERR_RUNTIME = -2,          /* std::runtime_error / cuda::Error in the reference */
+  SFQ_ERR_OUT_OF_MEMORY = -3,    /* workspace exhausted or cudaErrorMemoryAllocation */
+  SFQ_ERR_DEVICE_TIMEOUT = -4    /* a kernel gave up a bounded wait; see sfq_device_status */
+};
+
+/* QuantFormat, include/slopfab/cuda/linear.cuh:49-59 (same order, same values). */
+typedef enum {
+  SFQ_F32 = 0, SFQ_F16 = 1, SFQ_BF16 = 2, SFQ_F8E4M3 = 3, SFQ_I8 = 4,
+  SFQ_NVFP4 = 5, SFQ_NF4 = 6, SFQ_W4A8 = 7, SFQ_W6A8 = 8
+} sfq_format;
+
+/* ComputeType, include/slopfab/cuda/linear.cuh:73-76. */
+typedef enum { SFQ_COMPUTE_BF16 = 0, SFQ_COMPUTE_F32 = 1 } sfq_compute;
+
+/* Fused activation of the GEMM epilogue. GELU-tanh is the arithmetic of
+ * launch_gelu_tanh (src/cuda/nn_pointwise.cu:74-81) applied to the bf16 result. */
+typedef enum { SFQ_ACT_NONE = 0, SFQ_ACT_GELU_TANH = 1 } sfq_activation;
+
+/* Layout of quantized NVFP4 activations.
+ * REFERENCE: low nibble = even element, scales row-major [rows, dim/16]
+ *   (launch_quantize_nvfp4_activations, include/slopfab/cuda/nvfp4_gemm.cuh:77-82).
+ * GEMM_FEED: high nibble = even element (the weight file's convention, so no nibble
+ *   swap is needed on either operand) and scales in the 128x4-tiled layout of the
+ *   weight scales, rows padded to a multiple of 128. */
+typedef enum { SFQ_NVFP4_ACT_REFERENCE = 0, SFQ_NVFP4_ACT_GEMM_FEED = 1 } sfq_nvfp4_act_layout;
+
+/* QuantWeight, include/slopfab/cuda/linear.cuh:80-152: same fields, same defaults
+ * (use sfq_quant_weight_init). Owns nothing. */
+typedef struct sfq_quant_weight {
+  int32_t format;              /* sfq_format */
+  const void* data;            /* device */
+  int32_t out_features;
+  int32_t in_features;
+  const float* weight_scale;   /* device; 1 element, or out_features when per_channel_scale */
+  int32_t per_channel_scale;
+  float input_scale;
+  int32_t full_precision;
+  const uint8_t* block_scale;  /* device; NVFP4: 128x4-tiled e4m3; W4A8/W6A8: row-major e4m3 groups */
+  uint32_t packed_group_size;  /* W4A8: 16; W6A8: multiple of 16 */
+  const float* w4_codebook;    /* device, 16 entries, W4A8 only */
+  float global_scale;          /* NVFP4 .weight_scale_2 */
+  const void* pre_quant_scale; /* device bf16 [in_features], AWQ; must be null on the native paths */
+  const uint8_t* nf4_absmax;
+  const float* nf4_quant_map;
+  const float* nf4_nested_quant_map;
+  const float* nf4_nested_absmax;
+  int32_t nf4_block_size;
+  int32_t nf4_nested_block_size;
+  float nf4_nested_offset;
+  int32_t convrot;
+  int32_t convrot_group;
+  const void* bias;            /* device, out_features elements, optional */
+  int32_t bias_format;         /* SFQ_F32 or SFQ_BF16 */
+} sfq_quant_weight;
+
+/* Epilogue of the stand-alone GEMM entry points. */
+typedef struct sfq_epilogue {
+  const float* d_row_scale;    /* int8: per-token activation scale [M] */
+  const float* d_col_scale;    /* int8: per-output-channel weight scale [N] */
+  float global_scale;          /* nvfp4: multiplies the accumulator once */
+  const void* d_bias;          /* optional [N] */
+  int32_t bias_format;         /* SFQ_F32 or SFQ_BF16 */
+  int32_t activation;          /* sfq_activation */
+} sfq_epilogue;
+
+/* Optional RMSNorm / adaLN-modulate stage fused in front of a quantizer.
+ * out = (x * rsqrt(mean(x^2) + eps)) * w, then fma(out, 1 + scale[a[r]], shift[a[r]])
+ * when d_scale is non-null (launch_rmsnorm / launch_rmsnorm_modulate,
+ * include/slopfab/cuda/nn_kernels.cuh:28-57; tables are fp32 [*, dim], a[r] int32).
+ * A null d_norm_weight disables the stage. */
+typedef struct sfq_norm {
+  const void* d_norm_weight;   /* bf16 [dim] */
+  const float* d_scale;
+  const float* d_shift;
+  const int32_t* d_adaln_index;
+  float eps;
+} sfq_norm;
+
+typedef struct sfq_runner sfq_runner;
+
+SFQ_API const char* sfq_last_error(void);
+SFQ_API int sfq_version(void);
+SFQ_API void sfq_quant_weight_init(sfq_quant_weight* w);
+
+/* Reads and clears the device status word of the current device: 0, or the code a
+ * kernel stored when it abandoned a bounded wait. Synchronises the device. */
+SFQ_API int sfq_device_status(int* h_code);
+
+/* ---- host packers -------------------------------------------------------- */
+
+/* fp32 [out,in] -> NVFP4 storage: data u8 [out,in/2] (even element in the high
+ * nibble), scale u8 [out*in/16] in the 128x4-tiled layout, with the caller's
+ * global scale. Byte-identical to the reference's fixture packer pack_nvfp4
+ * (tests/detail/nn_weight_fixture.h:333-360). Needs out % 128 == 0, in % 64 == 0. */
+SFQ_API int sfq_pack_nvfp4(const float* h_w, int out_features, int in_features, float global_scale,
+                           uint8_t* h_data, uint8_t* h_scale_tiled);
+
+/* fp32 [out,in] -> W4A8 storage of docs/w4a8.md: ConvRot-256 along in_features,
+ * int4 codes low-nibble-first [out,in/2], E4M3 group scales [out,in/16] row-major,
+ * fp32 channel scales [out], and the 16-entry codebook (i - 8). The reference
+ * ships no encoder for this format (its files come from a third-party tool), so the
+ * rule is this library's; the bytes satisfy validate_packed_int8_weight
+ * (src/core/w4a8.cpp:127-162) and decode through launch_dequant_w4a8_weight. */
+SFQ_API int sfq_pack_w4a8(const float* h_w, int out_features, int in_features, int8_t* h_packed,
+                          uint8_t* h_group_scale, float* h_channel_scale, float* h_codebook16);
+
+/* fp32 [out,in] -> W6A8 storage of docs/w6a8.md: per row in/2 low-nibble bytes then
+ * in/4 bytes of 2-bit highs, levels code-32, E4M3 group scales [out,in/group]. */
+SFQ_API int sfq_pack_w6a8(const float* h_w, int out_features, int in_features, int group,
+                          int8_t* h_packed, uint8_t* h_group_scale, float* h_channel_scale);
+
+/* fp32 [out,in] -> INT8 weight-only ("int8_tensorwise" with per-row scales,
+ * src/core/int8_weight.cpp:11-64): optional ConvRot with group in {4,16,64,256}
+ * (0 = none; skipped when in % group != 0), codes [out,in], scales [out]. */
+SFQ_API int sfq_pack_int8(const float* h_w, int out_features, int in_features, int convrot_group,
+                          int8_t* h_codes, float* h_scale);
+
+/* ---- device unpackers ---------------------------------------------------- */
+
+/* launch_dequant_nvfp4, include/slopfab/cuda/linear.cuh:289-291 (bit-exact). */
+SFQ_API int sfq_unpack_nvfp4_bf16(const uint8_t* d_data, const uint8_t* d_scale_tiled, float global_scale,
+                                  void* d_out_bf16, int out_features, int in_features, void* stream);
+/* launch_dequant_w4a8_weight, include/slopfab/cuda/w4a8.cuh:18-20 (bit-exact). */
+SFQ_API int sfq_unpack_w4a8_int8(const int8_t* d_packed, const uint8_t* d_group_scale, const float* d_codebook,
+                                 int8_t* d_out, int out_features, int in_features, int group, void* stream);
+/* launch_dequant_w6a8_weight, include/slopfab/cuda/w4a8.cuh:12-14 (bit-exact). */
+SFQ_API int sfq_unpack_w6a8_int8(const int8_t* d_packed, const uint8_t* d_group_scale, int8_t* d_out,
+                                 int out_features, int in_features, int group, void* stream);
+/* launch_dequant_i8_per_channel, include/slopfab/cuda/linear.cuh:264-265 (bit-exact). */
+SFQ_API int sfq_unpack_int8_bf16(const int8_t* d_codes, const float* d_scale, void* d_out_bf16,
+                                 int out_features, int in_features, void* stream);
+/* F16Weight::materialize for INT8 ConvRot weights (src/cuda/nf4_weight.cu:20-51; host twin
+ * unpack_int8_weight, src/core/int8_weight.cpp:66-100): inverse rotation into fp16 (bit-exact). */
+SFQ_API int sfq_unpack_int8_f16(const int8_t* d_codes, const float* d_scale, void* d_out_f16, int out_features,
+                                int in_features, int rotation_group, int canonicalize_subnormals, void* stream);
+
+/* ---- activation side ------------------------------------------------------ */
+
+/* launch_rmsnorm / launch_rmsnorm_modulate, include/slopfab/cuda/nn_kernels.cuh:28-57 (bit-exact for dim % 8 == 0). */
+SFQ_API int sfq_rmsnorm(const void* d_x_bf16, const sfq_norm* norm, void* d_out_bf16, int rows, int dim, void* stream);
+/* launch_convrot, include/slopfab/cuda/linear.cuh:251-252 (bit-exact). */
+SFQ_API int sfq_convrot(const void* d_x_bf16, void* d_out_bf16, int rows, int dim, int group, void* stream);
+
+/* One pass: [RMSNorm / modulate] -> ConvRot-256 -> per-token int8. Replaces
+ * launch_rmsnorm_modulate + launch_convrot + launch_quantize_w4a8_bf16
+ * (src/dit/transformer_execution.cpp:260; src/cuda/linear.cu:199-200) with identical
+ * bits: q int8 [rows,dim], row scales fp32 [rows]. dim % 256 == 0. `norm` may be null.
+ * `d_normed_out_bf16`, when non-null, also receives the normed activation. */
+SFQ_API int sfq_quantize_int8_token(const void* d_x_bf16, const sfq_norm* norm, int8_t* d_q, float* d_row_scale,
+                                    void* d_normed_out_bf16, int rows, int dim, int apply_convrot, void* stream);
+
+/* One pass: [RMSNorm / modulate] -> per-16-block fp4. The REFERENCE layout is
+ * launch_quantize_nvfp4_activations (src/cuda/nvfp4_gemm.cu:107-158, byte-exact);
+ * GEMM_FEED is what sfq_gemm_nvfp4 consumes. dim % 16 == 0 (GEMM_FEED: dim % 64 == 0).
+ * GEMM_FEED scale buffer size: sfq_nvfp4_act_scale_bytes(rows, dim). */
+SFQ_API int sfq_quantize_nvfp4_block(const void* d_x_bf16, const sfq_norm* norm, uint8_t* d_packed, uint8_t* d_scales,
+                                     void* d_normed_out_bf16, int rows, int dim, int layout, void* stream);
+SFQ_API size_t sfq_nvfp4_act_scale_bytes(int rows, int dim);
+
+/* launch_gelu_tanh / launch_swiglu / launch_add_gated, include/slopfab/cuda/nn_kernels.cuh:68-88. */
+SFQ_API int sfq_gelu_tanh(void* d_x_bf16, size_t n, void* stream);
+SFQ_API int sfq_swiglu(const void* d_fused_bf16, void* d_out_bf16, int rows, int inner, void* stream);
+SFQ_API int sfq_add_gated(void* d_x_bf16, const void* d_branch_bf16, const float* d_gate, const int32_t* d_adaln_index,
+                          int rows, int dim, void* stream);
+
+/* ---- GEMMs ---------------------------------------------------------------- */
+
+/* y[M,N] bf16 = epilogue(int32(q[M,K] * w8[N,K]^T)). Replaces the cuBLAS int8 GemmEx,
+ * launch_w4a8_output_bf16 and add_bias of src/cuda/linear.cu:202-206; the int32
+ * accumulators and therefore the bf16 output are bit-exact. K % 16 == 0. */
+SFQ_API int sfq_gemm_int8(const int8_t* d_q, const int8_t* d_w8, const sfq_epilogue* ep, void* d_y_bf16,
+                          int M, int N, int K, void* stream);
+/* y = epilogue(global * sum(a_fp4 * w_fp4 * block scales)). Replaces nvfp4_gemm_forward_q
+ * (include/slopfab/cuda/nvfp4_gemm.cuh:101-113). Activations in the GEMM_FEED layout. */
+SFQ_API int sfq_gemm_nvfp4(const uint8_t* d_a_packed, const uint8_t* d_a_scale_tiled, const uint8_t* d_w_packed,
+                           const uint8_t* d_w_scale_tiled, const sfq_epilogue* ep, void* d_y_bf16,
+                           int M, int N, int K, void* stream);
+/* y = epilogue(x[M,K] * w[N,K]^T), bf16 operands, fp32 accumulate: the cuBLAS bf16 GemmEx of
+ * src/cuda/linear.cu:243-246. K % 8 == 0. */
+SFQ_API int sfq_gemm_bf16(const void* d_x_bf16, const void* d_w_bf16, const sfq_epilogue* ep, void* d_y_bf16,
+                          int M, int N, int K, void* stream);
+/* Tuning knobs of the three GEMMs, for experiments: tile_n in {0,128,256}, band_m row tiles
+ * per raster band (0 = default), max_ctas (0 = one per SM). Process-wide. */
+SFQ_API void sfq_gemm_tuning(int tile_n, int band_m, int max_ctas);
+
+/* ---- LinearRunner (include/slopfab/cuda/linear.cuh:182-242) ---------------- */
+
+SFQ_API int sfq_runner_create(void* stream, sfq_runner** out);
+SFQ_API void sfq_runner_destroy(sfq_runner* r);
+SFQ_API int sfq_runner_set_native(sfq_runner* r, int enable); /* LinearRunner::set_native */
+SFQ_API int sfq_runner_native(const sfq_runner* r);
+/* Fused epilogue activation applied by forward/forward_prepared (default none). Not part of
+ * the reference runner, which runs launch_gelu_tanh as a separate launch. */
+SFQ_API int sfq_runner_set_activation(sfq_runner* r, int activation);
+
+/* linear_workspace_bytes / linear_dense_weight_bytes / linear_activation_workspace_bytes,
+ * include/slopfab/cuda/linear.cuh:156,179-180. Sizes are for THIS library's kernels
+ * (smaller than the reference's: no int32 [M,N] buffer, no rotated bf16 copy). */
+SFQ_API int sfq_linear_workspace_bytes(const sfq_quant_weight* w, int rows, int compute, size_t* out);
+SFQ_API int sfq_linear_dense_weight_bytes(const sfq_quant_weight* w, size_t* out);
+SFQ_API int sfq_linear_activation_workspace_bytes(const sfq_quant_weight* w, int rows, int compute, size_t* out);
+
+/* LinearRunner::forward: y[rows,out] = x[rows,in] W^T + b. The workspace is a caller-owned
+ * device arena (256-byte aligned carving, rewound at return; Workspace of
+ * include/slopfab/cuda/workspace.cuh:21-76). rows <= 0 is a no-op. */
+SFQ_API int sfq_linear_forward(sfq_runner* r, const sfq_quant_weight* w, const void* d_x_bf16, int rows,
+                               void* d_y_bf16, void* d_workspace, size_t workspace_bytes);
+/* LinearRunner::prepare: carves what stays constant across a row-chunk loop out of the
+ * front of the workspace and reports how many bytes it consumed; *d_prepared is null exactly
+ * when the weight has no dense bf16 form (native NVFP4), as in the reference. For W4A8/W6A8 the
+ * expanded int8 weight is kept in the consumed prefix so that chunks do not re-expand it. */
+SFQ_API int sfq_linear_prepare(sfq_runner* r, const sfq_quant_weight* w, void* d_workspace, size_t workspace_bytes,
+                               const void** d_prepared, size_t* consumed_bytes);
+/* LinearRunner::forward_prepared. `d_prepared` is what sfq_linear_prepare returned for `w`;
+ * the workspace passed here must start after the consumed prefix. */
+SFQ_API int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w, const void* d_prepared,
+                                        const void* d_x_bf16, int rows, void* d_y_bf16, void* d_workspace,
+                                        size_t workspace_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SFQ_H_ */

@@ -1,0 +1,474 @@
+// Fused activation front end of the quantized Linear, one pass over HBM:
+//
+//   [RMSNorm | RMSNorm + adaLN modulate]  ->  [ConvRot-256 -> per-token int8]  |  [per-16-block fp4]
+//
+// Replaces, with identical bits, the separate launches of the reference:
+// rmsnorm_modulate_bf16_kernel (src/cuda/nn_kernels.cu:153-198), convrot_kernel
+// (src/cuda/linear_weights.cu:422-471), quantize_bf16 (src/cuda/w4a8.cu:193-216)
+// and quantize_act_kernel (src/cuda/nvfp4_gemm.cu:107-158). The activation is read
+// once (2 bytes/element, 128-bit loads) and only the quantized form is written.
+//
+// Work split: one CTA per token row, one thread per 16 consecutive elements (one
+// fp4 scale block; 16 threads = one 256-wide rotation group, always inside one
+// warp). The rotation runs two radix-4 stages in registers, transposes the group
+// through a padded, conflict-free shared-memory tile, and runs the other two.
+//
+// Bit-exactness notes. The sum of squares is accumulated in the order of the
+// reference's 256-thread block kernel (thread v owns packs v, v+256, ... with a
+// fused multiply-add chain, then the shfl_down tree); 1/sqrt is the reference's
+// integer Newton iteration; the butterfly adds associate left to right; bf16
+// roundings sit where the reference stores bf16 between its kernels.
+#include "kernels.cuh"
+
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "codec.cuh"
+
+namespace sfq {
+namespace {
+
+enum Mode { kModeInt8 = 0, kModeFp4Ref = 1, kModeFp4Feed = 2, kModeNormOnly = 3, kModeRotOnly = 4 };
+
+struct FusedArgs {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* norm_w;
+  const float* mod_scale;
+  const float* mod_shift;
+  const int32_t* mod_index;
+  float eps;
+  int rows, dim;
+  int apply_convrot;
+  int8_t* q;
+  float* row_scale;
+  uint8_t* packed;
+  uint8_t* scales;
+  __nv_bfloat16* bf16_out;  // normed activation (optional) or the rotated one (rot-only mode)
+};
+
+// ---- integer-exact norm reciprocal (include/slopfab/cuda/deterministic_math.cuh:26-197) ----
+__device__ __forceinline__ uint64_t shift_rne(uint64_t v, unsigned s) {
+  const uint64_t q = v >> s;
+  const uint64_t rem = v & ((uint64_t(1) << s) - 1);
+  const uint64_t half = uint64_t(1) << (s - 1);
+  return q + ((rem > half || (rem == half && (q & 1))) ? 1 : 0);
+}
+// 1/sqrt(v) for a positive normal v: Newton in unsigned Q30 with round-half-even shifts, six
+// steps from a seed chosen by the exponent's parity, then rounded to 24 bits.
+__device__ float rsqrt_q30(float value) {
+  const uint32_t mag = __float_as_uint(value) & 0x7FFFFFFFu;
+  if (mag == 0u) return __uint_as_float(0x7F800000u);
+  if ((__float_as_uint(value) & 0x80000000u) || mag > 0x7F800000u) return __uint_as_float(0x7FC00000u);
+  if (mag == 0x7F800000u) return 0.0f;
+  uint32_t sig = mag & 0x007FFFFFu;
+  int expo;
+  if (mag < 0x00800000u) {
+    const int t = 31 - __clz(sig);
+    expo = t - 149;
+    sig <<= unsigned(23 - t);
+  } else {
+    expo = int(mag >> 23) - 127;
+    sig |= 0x00800000u;
+  }
+  const int odd = expo & 1;
+  const uint64_t m = uint64_t(sig) << (7 + odd);
+  const int out_scale = -(expo - odd) / 2;
+  uint64_t y = odd ? 637534208ull : 872415232ull;
+#pragma unroll 1
+  for (int it = 0; it < 6; ++it) {
+    const uint64_t y2 = shift_rne(y * y, 30);
+    const uint64_t my2 = shift_rne(m * y2, 30);
+    y = shift_rne(y * (3ull * (1ull << 30) - my2), 31);
+  }
+  int t = 63 - __clzll((long long)y);
+  uint64_t r = shift_rne(y, unsigned(t - 23));
+  if (r == (1ull << 24)) {
+    r >>= 1;
+    ++t;
+  }
+  return __uint_as_float((uint32_t(t - 30 + out_scale + 127) << 23) | (uint32_t(r) & 0x007FFFFFu));
+}
+// rsqrt(RNE(sum / dim) + eps); IEEE division and addition are the reference's integer forms.
+__device__ float norm_rsqrt(float sum, int dim, float eps) {
+  const float mean = sum == 0.0f ? 0.0f : __fdiv_rn(sum, float(dim));
+  return rsqrt_q30(__fadd_rn(mean, eps));
+}
+
+// One radix-4 stage of the regular Hadamard on (a,b,c,d) -> rows of h4, each a left-to-right
+// sum as in convrot_kernel (src/cuda/linear_weights.cu:458-461). a-b is exactly -(b-a), so the
+// four outputs cost ten additions instead of twelve.
+__device__ __forceinline__ void h4(float& a, float& b, float& c, float& d) {
+  const float s = __fadd_rn(a, b);
+  const float u = __fsub_rn(a, b);
+  const float r0 = __fsub_rn(__fadd_rn(s, c), d);
+  const float r1 = __fadd_rn(__fsub_rn(s, c), d);
+  const float r2 = __fadd_rn(__fadd_rn(u, c), d);
+  const float r3 = __fadd_rn(__fadd_rn(-u, c), d);
+  a = r0, b = r1, c = r2, d = r3;
+}
+// Two stages (strides 1 and 4) over 16 values held by one thread.
+__device__ __forceinline__ void two_stages(float (&v)[16]) {
+#pragma unroll
+  for (int b = 0; b < 4; ++b) h4(v[4 * b], v[4 * b + 1], v[4 * b + 2], v[4 * b + 3]);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h4(v[i], v[i + 4], v[i + 8], v[i + 12]);
+}
+
+__device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16(f)); }
+
+template <int MODE>
+__global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  // [tile: 17 floats per thread][partials: 256 + 8 + 8 floats][raw row: dim bf16 when the norm is on]
+  float* tile = reinterpret_cast<float*>(smem);
+  float* partial = tile + size_t(blockDim.x) * 17;
+  float* warp_tot = partial + 256;
+  float* bcast = warp_tot + 8;
+  uint4* raw = reinterpret_cast<uint4*>(bcast + 8);
+
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int chunks = a.dim >> 4;
+  const bool active = tid < chunks;
+
+  if constexpr (MODE == kModeFp4Feed) {
+    if (row >= a.rows) {  // padding rows of the last 128-row scale tile: zero scales
+      if (active) a.scales[nvfp4_scale_offset(row, tid, chunks)] = 0;
+      return;
+    }
+  }
+
+  float v[16];
+  {
+    uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
+    if (active) {
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + size_t(row) * a.dim) + tid * 2;
+      r0 = __ldg(src);
+      r1 = __ldg(src + 1);
+    }
+    const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
+    const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f0 = __bfloat1622float2(h0[i]), f1 = __bfloat1622float2(h1[i]);
+      v[2 * i] = f0.x, v[2 * i + 1] = f0.y, v[8 + 2 * i] = f1.x, v[8 + 2 * i + 1] = f1.y;
+    }
+    if (a.norm_w != nullptr && active) {
+      raw[tid * 2] = r0;
+      raw[tid * 2 + 1] = r1;
+    }
+  }
+
+  // ---------------------------------------------------------------- RMSNorm [+ modulate]
+  if (a.norm_w != nullptr) {
+    __syncthreads();
+    const int packs = a.dim >> 3;
+    for (int vt = tid; vt < 256; vt += blockDim.x) {  // virtual thread vt of the 256-thread block kernel
+      float s = 0.0f;
+      for (int p = vt; p < packs; p += 256) {
+        const uint4 pk = raw[p];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          s = __fmaf_rn(f.x, f.x, s);
+          s = __fmaf_rn(f.y, f.y, s);
+        }
+      }
+      partial[vt] = s;
+    }
+    __syncthreads();
+    if (tid < 32) {
+      for (int w = 0; w < 8; ++w) {  // shfl_down tree of each virtual warp
+        float s = partial[w * 32 + lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, s, off));
+        if (lane == 0) warp_tot[w] = s;
+      }
+      __syncwarp();
+      float s = lane < 8 ? warp_tot[lane] : 0.0f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, s, off));
+      if (lane == 0) bcast[0] = norm_rsqrt(s, a.dim, a.eps);
+    }
+    __syncthreads();
+    const float inv = bcast[0];
+    if (active) {
+      const uint4* wp = reinterpret_cast<const uint4*>(a.norm_w) + tid * 2;
+      const uint4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+      const __nv_bfloat162* wh0 = reinterpret_cast<const __nv_bfloat162*>(&w0);
+      const __nv_bfloat162* wh1 = reinterpret_cast<const __nv_bfloat162*>(&w1);
+      float w[16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f0 = __bfloat1622float2(wh0[i]), f1 = __bfloat1622float2(wh1[i]);
+        w[2 * i] = f0.x, w[2 * i + 1] = f0.y, w[8 + 2 * i] = f1.x, w[8 + 2 * i + 1] = f1.y;
+      }
+      if (a.mod_scale != nullptr) {
+        const size_t mod = size_t(a.mod_index[row]) * a.dim + size_t(tid) * 16;
+        const float4* sc = reinterpret_cast<const float4*>(a.mod_scale + mod);
+        const float4* sh = reinterpret_cast<const float4*>(a.mod_shift + mod);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 s4 = __ldg(sc + j), h4v = __ldg(sh + j);
+          const float ss[4] = {s4.x, s4.y, s4.z, s4.w}, hh[4] = {h4v.x, h4v.y, h4v.z, h4v.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float n = __fmul_rn(__fmul_rn(v[4 * j + i], inv), w[4 * j + i]);
+            v[4 * j + i] = round_bf16(__fmaf_rn(n, __fadd_rn(1.0f, ss[i]), hh[i]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = round_bf16(__fmul_rn(__fmul_rn(v[i], inv), w[i]));
+      }
+    }
+    if (a.bf16_out != nullptr && MODE != kModeRotOnly && active) {
+      uint4 o[2];
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) op[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      uint4* dst = reinterpret_cast<uint4*>(a.bf16_out + size_t(row) * a.dim) + tid * 2;
+      dst[0] = o[0];
+      dst[1] = o[1];
+    }
+  }
+  if constexpr (MODE == kModeNormOnly) return;
+
+  if constexpr (MODE == kModeInt8 || MODE == kModeRotOnly) {
+    // ------------------------------------------------------------ ConvRot-256
+    if (a.apply_convrot) {
+      // Element i = 16*T + e of the group sits at word 17*T + e of the group's tile: a thread's own 16
+      // words are consecutive, and the 16 threads' words for a fixed e fall in 16 distinct banks.
+      float* grp = tile + (tid >> 4) * 272;
+      const int T = tid & 15;
+      two_stages(v);  // strides 1 and 4
+#pragma unroll
+      for (int e = 0; e < 16; ++e) grp[17 * T + e] = v[e];
+      __syncwarp();
+#pragma unroll
+      for (int t = 0; t < 16; ++t) v[t] = grp[17 * t + T];  // now v[t] = element 16*t + T
+      two_stages(v);  // strides 16 and 64
+      __syncwarp();
+#pragma unroll
+      for (int t = 0; t < 16; ++t) grp[17 * t + T] = round_bf16(v[t] * 0.0625f);  // 1/16, then the bf16 store
+      __syncwarp();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) v[e] = grp[17 * T + e];
+    }
+    if constexpr (MODE == kModeRotOnly) {
+      if (active) {
+        uint4 o[2];
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) op[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        uint4* dst = reinterpret_cast<uint4*>(a.bf16_out + size_t(row) * a.dim) + tid * 2;
+        dst[0] = o[0];
+        dst[1] = o[1];
+      }
+      return;
+    }
+    // ------------------------------------------------------------ per-token int8 (src/cuda/w4a8.cu:193-216)
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    __syncthreads();  // `partial` may still be read by slow warps of the norm phase
+    if (lane == 0) partial[tid >> 5] = amax;
+    __syncthreads();
+    if (tid < 32) {
+      float m = tid < int(blockDim.x >> 5) ? partial[tid] : 0.0f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+      if (tid == 0) {
+        const float scale = fmaxf(__fdiv_rn(m, 127.0f), 1e-30f);
+        bcast[1] = scale;
+        a.row_scale[row] = scale;
+      }
+    }
+    __syncthreads();
+    const float divisor = round_bf16(bcast[1]);
+    if (active) {
+      uint32_t o[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float quo = round_bf16(__fdiv_rn(v[4 * w + j], divisor));
+          const int q = max(-128, min(127, __float2int_rn(quo)));
+          acc |= uint32_t(uint8_t(q)) << (8 * j);
+        }
+        o[w] = acc;
+      }
+      reinterpret_cast<uint4*>(a.q + size_t(row) * a.dim)[tid] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  } else {
+    // ------------------------------------------------------------ per-16 fp4 (src/cuda/nvfp4_gemm.cu:107-158)
+    if (!active) return;
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const uint8_t s8 = __nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
+    const float decoded = e4m3_decode(s8);
+    const float inv = decoded > 0.0f ? __fdiv_rn(1.0f, decoded) : 0.0f;
+    uint32_t words[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float even = v[2 * i] * inv, odd = v[2 * i + 1] * inv;
+      // The conversion puts its first component in the low nibble. The reference layout wants the even
+      // element there; the GEMM feed wants it in the high nibble, like the weight files.
+      const __nv_fp4x2_storage_t b = MODE == kModeFp4Ref
+                                         ? __nv_cvt_float2_to_fp4x2(make_float2(even, odd), __NV_E2M1, cudaRoundNearest)
+                                         : __nv_cvt_float2_to_fp4x2(make_float2(odd, even), __NV_E2M1, cudaRoundNearest);
+      words[i >> 2] |= uint32_t(b) << (8 * (i & 3));
+    }
+    reinterpret_cast<uint2*>(a.packed + size_t(row) * (a.dim >> 1))[tid] = make_uint2(words[0], words[1]);
+    if constexpr (MODE == kModeFp4Ref)
+      a.scales[size_t(row) * chunks + tid] = s8;
+    else
+      a.scales[nvfp4_scale_offset(row, tid, chunks)] = s8;
+  }
+}
+
+// Generic rotation for the other power-of-four groups (4, 16, 64): not on the hot path (the INT8
+// weight-only format of the text encoder); one block of 64 threads per 256 columns.
+__global__ void __launch_bounds__(64)
+convrot_small_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int dim, int stages,
+                     float norm) {
+  __shared__ float v[256 + 64];
+  const int row = blockIdx.x, c0 = blockIdx.y * 256, t = threadIdx.x;
+  const int n = min(256, dim - c0);
+  const size_t base = size_t(row) * dim + c0;
+  for (int i = t; i < n; i += 64) v[i + (i >> 2)] = __bfloat162float(in[base + i]);
+  __syncthreads();
+  int stride = 1;
+  for (int s = 0; s < stages; ++s) {
+    const int i = (t / stride) * 4 * stride + (t % stride);
+    const bool live = i + 3 * stride < n;
+    const int j0 = i, j1 = i + stride, j2 = i + 2 * stride, j3 = i + 3 * stride;
+    float a = 0, b = 0, c = 0, d = 0;
+    if (live) a = v[j0 + (j0 >> 2)], b = v[j1 + (j1 >> 2)], c = v[j2 + (j2 >> 2)], d = v[j3 + (j3 >> 2)];
+    __syncthreads();
+    if (live) {
+      h4(a, b, c, d);
+      v[j0 + (j0 >> 2)] = a, v[j1 + (j1 >> 2)] = b, v[j2 + (j2 >> 2)] = c, v[j3 + (j3 >> 2)] = d;
+    }
+    __syncthreads();
+    stride *= 4;
+  }
+  for (int i = t; i < n; i += 64) out[base + i] = __float2bfloat16(v[i + (i >> 2)] * norm);
+}
+
+inline void check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+template <int MODE> void launch_fused(const FusedArgs& a, int grid_rows, cudaStream_t stream, const char* what) {
+  if (a.dim % 16 != 0 || a.dim > 16384)
+    throw std::invalid_argument(std::string(what) + ": dim must be a multiple of 16 and at most 16384");
+  if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0)
+    throw std::invalid_argument(std::string(what) + ": activation pointer must be 16-byte aligned");
+  if (a.norm_w != nullptr && a.mod_scale != nullptr && (a.mod_shift == nullptr || a.mod_index == nullptr))
+    throw std::invalid_argument(std::string(what) + ": modulation needs scale, shift and the row index");
+  const int threads = ((a.dim / 16 + 31) / 32) * 32;
+  const size_t smem = size_t(threads) * 17 * 4 + (256 + 16) * 4 + (a.norm_w ? size_t(a.dim) * 2 : 0);
+  static size_t reserved = 0;  // per-instantiation high-water mark
+  if (smem > 48 * 1024 && smem > reserved) {
+    const cudaError_t e = cudaFuncSetAttribute(fused_act_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    reserved = smem;
+  }
+  fused_act_kernel<MODE><<<grid_rows, threads, smem, stream>>>(a);
+  check_launch(what);
+}
+
+FusedArgs base_args(const __nv_bfloat16* x, const NormArgs& n, int rows, int dim) {
+  FusedArgs a{};
+  a.x = x;
+  a.norm_w = n.weight;
+  a.mod_scale = n.weight ? n.scale : nullptr;
+  a.mod_shift = n.weight ? n.shift : nullptr;
+  a.mod_index = n.weight ? n.index : nullptr;
+  a.eps = n.eps;
+  a.rows = rows;
+  a.dim = dim;
+  return a;
+}
+
+}  // namespace
+
+void rmsnorm(const __nv_bfloat16* x, const NormArgs& norm, __nv_bfloat16* out, int rows, int dim, cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) throw std::invalid_argument("rmsnorm: rows and dim must be positive");
+  if (!x || !out || !norm.weight) throw std::invalid_argument("rmsnorm: null buffer");
+  FusedArgs a = base_args(x, norm, rows, dim);
+  a.bf16_out = out;
+  launch_fused<kModeNormOnly>(a, rows, stream, "rmsnorm");
+}
+
+void convrot(const __nv_bfloat16* x, __nv_bfloat16* out, int rows, int dim, int group, cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) return;
+  if (!x || !out) throw std::invalid_argument("convrot: null buffer");
+  int stages = 0, n = 1;
+  while (n < group) n *= 4, ++stages;
+  if (n != group) throw std::runtime_error("convrot: group size must be a power of four, got " + std::to_string(group));
+  if (dim % group != 0) throw std::runtime_error("convrot: dim must be a multiple of the group size");
+  if (group == 256 && dim <= 16384) {
+    FusedArgs a = base_args(x, NormArgs{}, rows, dim);
+    a.apply_convrot = 1;
+    a.bf16_out = out;
+    launch_fused<kModeRotOnly>(a, rows, stream, "convrot");
+    return;
+  }
+  if (group > 256) throw std::runtime_error("convrot: groups above 256 are not supported");
+  convrot_small_kernel<<<dim3(rows, (dim + 255) / 256), 64, 0, stream>>>(x, out, dim, stages, 1.0f / float(1 << stages));
+  check_launch("convrot");
+}
+
+void quantize_int8_token(const __nv_bfloat16* x, const NormArgs& norm, int8_t* q, float* row_scale,
+                         __nv_bfloat16* normed_out, int rows, int dim, bool apply_convrot, cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) throw std::invalid_argument("W4A8 activation shape");
+  if (!x || !q || !row_scale) throw std::invalid_argument("quantize_int8_token: null buffer");
+  if (apply_convrot && dim % 256 != 0) throw std::invalid_argument("W4A8 activation requires K divisible by 256");
+  if (reinterpret_cast<uintptr_t>(q) % 16 != 0) throw std::invalid_argument("quantize_int8_token: output must be 16-byte aligned");
+  FusedArgs a = base_args(x, norm, rows, dim);
+  a.q = q;
+  a.row_scale = row_scale;
+  a.apply_convrot = apply_convrot ? 1 : 0;
+  a.bf16_out = norm.weight ? normed_out : nullptr;
+  launch_fused<kModeInt8>(a, rows, stream, "quantize_int8_token");
+}
+
+size_t nvfp4_act_scale_bytes(int rows, int dim) {
+  if (rows <= 0 || dim <= 0) return 0;
+  return size_t((rows + 127) / 128) * 128 * size_t(dim / 16);
+}
+
+void quantize_nvfp4_block(const __nv_bfloat16* x, const NormArgs& norm, uint8_t* packed, uint8_t* scales,
+                          __nv_bfloat16* normed_out, int rows, int dim, int layout, cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) return;
+  if (!x || !packed || !scales) throw std::invalid_argument("quantize_nvfp4_block: null buffer");
+  if (dim % 16 != 0)
+    throw std::runtime_error("nvfp4: activation dim must be a multiple of 16, got " + std::to_string(dim));
+  if (reinterpret_cast<uintptr_t>(packed) % 8 != 0) throw std::invalid_argument("quantize_nvfp4_block: output must be 8-byte aligned");
+  FusedArgs a = base_args(x, norm, rows, dim);
+  a.packed = packed;
+  a.scales = scales;
+  a.bf16_out = norm.weight ? normed_out : nullptr;
+  if (layout == SFQ_NVFP4_ACT_REFERENCE) {
+    launch_fused<kModeFp4Ref>(a, rows, stream, "quantize_nvfp4_block");
+  } else if (layout == SFQ_NVFP4_ACT_GEMM_FEED) {
+    if (dim % 64 != 0) throw std::invalid_argument("quantize_nvfp4_block: the tiled scale layout needs dim % 64 == 0");
+    launch_fused<kModeFp4Feed>(a, (rows + 127) / 128 * 128, stream, "quantize_nvfp4_block");
+  } else {
+    throw std::invalid_argument("quantize_nvfp4_block: unknown layout");
+  }
+}
+
+}  // namespace sfq

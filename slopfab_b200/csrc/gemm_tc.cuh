@@ -1,0 +1,40 @@
+// Host interface of the tcgen05 GEMM kernels (gemm_tc.cu).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/sfq.h"
+
+namespace sfq {
+
+struct GemmArgs {
+  int M = 0, N = 0, K = 0;        // y[M,N] = A[M,K] * W[N,K]^T, K in elements
+  __nv_bfloat16* y = nullptr;     // row-major, leading dimension ldy (elements)
+  int ldy = 0;
+  // epilogue
+  const float* row_scale = nullptr;  // int8: per-token activation scale [M]
+  const float* col_scale = nullptr;  // int8: per-output-channel weight scale [N]
+  float global_scale = 1.0f;         // nvfp4: second-level weight scale
+  const void* bias = nullptr;        // [N] fp32 or bf16, optional
+  int bias_is_bf16 = 0;
+  int act = SFQ_ACT_NONE;
+  // nvfp4 block scales, both in the 128x4-tiled layout (512-byte tiles, row tile major)
+  const uint8_t* a_scale_tiled = nullptr;
+  const uint8_t* w_scale_tiled = nullptr;
+  // bookkeeping
+  int* status = nullptr;  // device word; a kernel that gives up waiting stores a non-zero code
+  int band_m = 0;         // row tiles per raster band (0 = default)
+  int max_ctas = 0;       // 0 = one CTA per SM
+  int tile_n = 0;         // 128 or 256 (0 = default 256)
+};
+
+// All three throw std::invalid_argument / std::runtime_error before launching on a contract violation.
+void gemm_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t stream);
+void gemm_nvfp4(const uint8_t* a_packed, const uint8_t* w_packed, const GemmArgs& g, cudaStream_t stream);
+void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream);
+
+}  // namespace sfq

@@ -1,0 +1,51 @@
+// Host launchers of the non-GEMM kernels (unpack.cu, act_quant.cu, pointwise.cu).
+// Every launcher validates before launching and throws std::invalid_argument /
+// std::runtime_error on a contract violation, like the reference's launchers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/sfq.h"
+
+namespace sfq {
+
+// ---- unpack.cu
+void unpack_nvfp4_bf16(const uint8_t* data, const uint8_t* scale_tiled, float global, __nv_bfloat16* out,
+                       int out_features, int in_features, cudaStream_t stream);
+void unpack_w4a8_int8(const int8_t* packed, const uint8_t* group_scale, const float* codebook, int8_t* out,
+                      int out_features, int in_features, int group, cudaStream_t stream);
+void unpack_w6a8_int8(const int8_t* packed, const uint8_t* group_scale, int8_t* out, int out_features,
+                      int in_features, int group, cudaStream_t stream);
+void unpack_int8_bf16(const int8_t* codes, const float* scale, __nv_bfloat16* out, int out_features, int in_features,
+                      cudaStream_t stream);
+void unpack_int8_f16(const int8_t* codes, const float* scale, __half* out, int out_features, int in_features,
+                     int rotation_group, int canonicalize_subnormals, cudaStream_t stream);
+
+// ---- act_quant.cu
+struct NormArgs {  // null weight = stage disabled
+  const __nv_bfloat16* weight = nullptr;
+  const float* scale = nullptr;  // adaLN tables, fp32 [*, dim]; null = plain RMSNorm
+  const float* shift = nullptr;
+  const int32_t* index = nullptr;  // a[r]
+  float eps = 1e-5f;
+};
+void rmsnorm(const __nv_bfloat16* x, const NormArgs& norm, __nv_bfloat16* out, int rows, int dim, cudaStream_t stream);
+void convrot(const __nv_bfloat16* x, __nv_bfloat16* out, int rows, int dim, int group, cudaStream_t stream);
+void quantize_int8_token(const __nv_bfloat16* x, const NormArgs& norm, int8_t* q, float* row_scale,
+                         __nv_bfloat16* normed_out, int rows, int dim, bool apply_convrot, cudaStream_t stream);
+void quantize_nvfp4_block(const __nv_bfloat16* x, const NormArgs& norm, uint8_t* packed, uint8_t* scales,
+                          __nv_bfloat16* normed_out, int rows, int dim, int layout, cudaStream_t stream);
+size_t nvfp4_act_scale_bytes(int rows, int dim);
+
+// ---- pointwise.cu
+void gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream);
+void swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int inner, cudaStream_t stream);
+void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate, const int32_t* index, int rows,
+               int dim, cudaStream_t stream);
+
+}  // namespace sfq

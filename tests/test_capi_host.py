@@ -1,0 +1,127 @@
+"""CPU-side checks of libsfq.so: it loads, exports every symbol include/sfq.h declares, its host
+packers produce the reference's bytes (NVFP4) or bytes the reference's decode rules accept
+(W4A8 / W6A8 / INT8), and device entry points fail loudly without a GPU."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import slopfab_b200 as sfq
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+P = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "sfq.h")).read()
+    declared = set(re.findall(r"SFQ_API\s+[\w\s\*]+?\b(sfq_\w+)\s*\(", header))
+    assert len(declared) >= 36
+    assert declared == set(sfq.EXPORTS)
+    raw = C.CDLL(sfq.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), name
+    assert sfq.lib.sfq_version() == 100
+
+
+def test_weight_descriptor_defaults_match_reference():
+    # include/slopfab/cuda/linear.cuh:80-152 defaults
+    w = sfq.new_weight()
+    assert (w.format, w.packed_group_size, w.global_scale, w.convrot, w.convrot_group) == (sfq.BF16, 16, 1.0, 0, 256)
+    assert (w.nf4_block_size, w.nf4_nested_block_size, w.bias_format, w.input_scale) == (64, 256, sfq.F32, 0.0)
+
+
+def test_pack_nvfp4_is_byte_identical_to_reference_fixture(golden):
+    rng = np.random.default_rng(0)
+    w = (0.02 * rng.standard_normal((256, 192))).astype(np.float32)
+    w[3, 16:32] = 0.0  # a zero block
+    g = float(np.abs(w).max() / (6 * 448))
+    data = np.zeros((256, 96), np.uint8)
+    scale = np.zeros(256 * 12, np.uint8)
+    sfq.check(sfq.lib.sfq_pack_nvfp4(P(w), 256, 192, g, P(data), P(scale)))
+    od, os_, _ = oracle.nvfp4_pack(w, g)
+    assert np.array_equal(data, od) and np.array_equal(scale, os_)
+    # and against the bytes the reference's own packer wrote for the golden weight
+    gw = golden["pack_w"]
+    gg = float(golden["pack_global"])
+    sfq.check(sfq.lib.sfq_pack_nvfp4(P(gw), 256, 192, gg, P(data), P(scale)))
+    assert np.array_equal(data.ravel(), golden["pack_data_11"]) and np.array_equal(scale, golden["pack_scale_11"])
+    # shapes the tile map cannot address are refused (launch_dequant_nvfp4 refuses 200x128 and 256x96)
+    for n, k in ((200, 128), (256, 96)):
+        assert sfq.lib.sfq_pack_nvfp4(P(w), n, k, g, P(data), P(scale)) == sfq.ERR_INVALID_ARGUMENT
+    assert b"128" in sfq.lib.sfq_last_error()
+
+
+def _rotate(w):
+    return oracle.convrot_dense(w.astype(np.float32))
+
+
+@pytest.mark.parametrize("bits,group", [(4, 16), (6, 16), (6, 32), (6, 64)])
+def test_packed_int8_encoders_obey_the_decode_contract(bits, group):
+    rng = np.random.default_rng(bits * 100 + group)
+    n, k = 48, 512
+    w = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    w[5] = 0.0  # a zero row
+    packed = np.zeros((n, k * bits // 8), np.int8)
+    s_rel = np.zeros(n * k // group, np.uint8)
+    s_ch = np.zeros(n, np.float32)
+    book = np.zeros(16, np.float32)
+    if bits == 4:
+        sfq.check(sfq.lib.sfq_pack_w4a8(P(w), n, k, P(packed), P(s_rel), P(s_ch), P(book)))
+        assert np.array_equal(book, np.arange(16, dtype=np.float32) - 8)
+        w8 = oracle.w4a8_decode(packed.view(np.uint8), s_rel, book, n, k)
+    else:
+        sfq.check(sfq.lib.sfq_pack_w6a8(P(w), n, k, group, P(packed), P(s_rel), P(s_ch)))
+        w8 = oracle.w6a8_decode(packed.view(np.uint8), s_rel, n, k, group)
+    # validate_packed_int8_weight (src/core/w4a8.cpp:127-162): scale bytes non-negative and not 0x7F,
+    # channel scales finite and positive
+    assert not (s_rel & 0x80).any() and not ((s_rel & 0x7F) == 0x7F).any()
+    assert np.isfinite(s_ch).all() and (s_ch > 0).all()
+    # decode(encode(W)) reproduces the rotated weight to quantization accuracy
+    approx = w8.astype(np.float32) * s_ch[:, None]
+    target = _rotate(w)
+    err = np.sqrt(((approx - target) ** 2).sum() / (target ** 2).sum())
+    assert err < (0.12 if bits == 4 else 0.03), err
+    assert not w8[5].any()
+    # deterministic
+    packed2 = np.zeros_like(packed)
+    s2 = np.zeros_like(s_rel)
+    c2 = np.zeros_like(s_ch)
+    if bits == 4:
+        sfq.check(sfq.lib.sfq_pack_w4a8(P(w), n, k, P(packed2), P(s2), P(c2), P(book)))
+    else:
+        sfq.check(sfq.lib.sfq_pack_w6a8(P(w), n, k, group, P(packed2), P(s2), P(c2)))
+    assert np.array_equal(packed, packed2) and np.array_equal(s_rel, s2) and np.array_equal(s_ch, c2)
+
+
+def test_pack_int8_round_trips_through_the_reference_unpack():
+    rng = np.random.default_rng(9)
+    for g in (0, 4, 16, 64, 256):
+        cols = 512
+        w = (0.05 * rng.standard_normal((6, cols))).astype(np.float32)
+        codes = np.zeros((6, cols), np.int8)
+        scale = np.zeros(6, np.float32)
+        sfq.check(sfq.lib.sfq_pack_int8(P(w), 6, cols, g, P(codes), P(scale)))
+        out = np.empty((6, cols), np.uint16)
+        oracle.lib.orc_int8_unpack_f16(P(codes), P(scale), 6, cols, max(g, 1), 0, P(out))
+        back = out.view(np.float16).astype(np.float32)
+        assert np.abs(back - w).max() < 2.5 * scale.max(), g  # one int8 step per element, spread by the rotation
+    assert sfq.lib.sfq_pack_int8(P(w), 6, cols, 8, P(codes), P(scale)) == sfq.ERR_INVALID_ARGUMENT
+    # ragged rows skip the rotation, as the third-party quantizer does (src/core/int8_weight.cpp:47-49)
+    w = (0.05 * rng.standard_normal((2, 267))).astype(np.float32)
+    codes = np.zeros((2, 267), np.int8)
+    scale = np.zeros(2, np.float32)
+    sfq.check(sfq.lib.sfq_pack_int8(P(w), 2, 267, 256, P(codes), P(scale)))
+    assert np.abs(codes.astype(np.float32) * scale[:, None] - w).max() <= 0.51 * scale.max()
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="only meaningful without a GPU")
+def test_device_entry_points_fail_loudly_without_a_gpu():
+    handle = C.c_void_p()
+    assert sfq.lib.sfq_runner_create(None, C.byref(handle)) == sfq.ERR_RUNTIME
+    assert b"CUDA" in sfq.lib.sfq_last_error() or b"device" in sfq.lib.sfq_last_error()
+    ep = sfq.Epilogue()
+    assert sfq.lib.sfq_gemm_int8(1, 1, C.byref(ep), 1, 128, 128, 256, None) != sfq.OK
