@@ -1,0 +1,276 @@
+"""GPU parity of the streaming kernels (unpack, norm, rotation, quantizers, pointwise) through the C ABI.
+
+Bar: bit-exact against the CPU oracle and, when the compiled reference is present, against the
+reference's own kernels running on the same device buffers.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import slopfab_b200 as sfq
+from helpers import (P, bf16_tensor, bits, dev, gaussian_bf16, ref_check, ref_dev, synthetic_packed_int8)
+
+pytestmark = pytest.mark.gpu
+S = None  # default stream
+
+
+def _u8(t):
+    return t.cpu().numpy()
+
+
+def test_unpack_nvfp4_golden_and_tile_shapes(golden):
+    # nn_dequant_nvfp4 / nn_dequant_nvfp4_tile_shapes (tests/test_nn_kernels_nvfp4_synthetic.cu:4-128)
+    cases = [("nvfp4_256x128", 256, 128, np.float32(1.3580322e-3))]
+    cases += [(f"nvfp4_tile{i}", n, k, np.float32(0.0021)) for i, (n, k) in
+              enumerate([(128, 64), (128, 512), (384, 128), (256, 320), (512, 64)])]
+    ref = ref_dev()
+    for name, n, k, g in cases:
+        packed, stored = dev(golden[name + "_packed"]), dev(golden[name + "_stored"])
+        out = torch.empty((n, k), dtype=torch.bfloat16, device="cuda")
+        sfq.check(sfq.lib.sfq_unpack_nvfp4_bf16(sfq.ptr(packed), sfq.ptr(stored), float(g), sfq.ptr(out), n, k, S))
+        assert np.array_equal(bits(out).ravel(), golden[name + "_ref"]), name
+        if ref is not None:
+            out2 = torch.empty_like(out)
+            ref_check(ref, ref.ref_dev_dequant_nvfp4(sfq.ptr(packed), sfq.ptr(stored), float(g), sfq.ptr(out2), n, k))
+            assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), name
+    # wrong form must differ: scales read row-major
+    plain = dev(golden["nvfp4_256x128_plain"])
+    packed = dev(golden["nvfp4_256x128_packed"])
+    bad = torch.empty((256, 128), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_unpack_nvfp4_bf16(sfq.ptr(packed), sfq.ptr(plain), 1.3580322e-3, sfq.ptr(bad), 256, 128, S))
+    assert (bad.float() - bf16_tensor(golden["nvfp4_256x128_ref"]).float().view(256, 128)).abs().max() > 1e-4
+    # shapes the tile map cannot address are refused
+    for n, k in ((200, 128), (256, 96)):
+        assert sfq.lib.sfq_unpack_nvfp4_bf16(sfq.ptr(packed), sfq.ptr(plain), 1.0, sfq.ptr(bad), n, k, S) == sfq.ERR_RUNTIME
+
+
+@pytest.mark.parametrize("bits_,group,n,k", [(4, 16, 96, 512), (6, 16, 64, 256), (6, 32, 40, 1024), (6, 64, 8, 512)])
+def test_unpack_packed_int8_weights(bits_, group, n, k):
+    packed, s_rel, s_ch, book = synthetic_packed_int8(bits_, group, n, k, seed=bits_ + group)
+    # every scale byte class of the reference's tests, including zero and the largest
+    s_rel[:5] = np.array([0, 0x30, 0x38, 0x48, 0x78], np.uint8)
+    dp, ds = dev(packed), dev(s_rel)
+    out = torch.empty((n, k), dtype=torch.int8, device="cuda")
+    ref = ref_dev()
+    if bits_ == 4:
+        db = dev(book)
+        sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(dp), sfq.ptr(ds), sfq.ptr(db), sfq.ptr(out), n, k, 16, S))
+        want = oracle.w4a8_decode(packed.view(np.uint8), s_rel, book, n, k)
+    else:
+        sfq.check(sfq.lib.sfq_unpack_w6a8_int8(sfq.ptr(dp), sfq.ptr(ds), sfq.ptr(out), n, k, group, S))
+        want = oracle.w6a8_decode(packed.view(np.uint8), s_rel, n, k, group)
+    assert np.array_equal(out.cpu().numpy(), want)
+    if ref is not None:
+        out2 = torch.empty_like(out)
+        if bits_ == 4:
+            ref_check(ref, ref.ref_dev_dequant_w4a8(sfq.ptr(dp), sfq.ptr(ds), sfq.ptr(db), sfq.ptr(out2), n, k, 16))
+        else:
+            ref_check(ref, ref.ref_dev_dequant_w6a8(sfq.ptr(dp), sfq.ptr(ds), sfq.ptr(out2), n, k, group))
+        assert torch.equal(out, out2)
+
+
+def test_unpack_int8_weight_only(golden):
+    rng = np.random.default_rng(3)
+    for n, k in ((16, 512), (3, 267)):
+        codes = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        scale = (rng.random(n, dtype=np.float32) * 0.01 + 1e-4).astype(np.float32)
+        out = torch.empty((n, k), dtype=torch.bfloat16, device="cuda")
+        dc, dsc = dev(codes), dev(scale)
+        sfq.check(sfq.lib.sfq_unpack_int8_bf16(sfq.ptr(dc), sfq.ptr(dsc), sfq.ptr(out), n, k, S))
+        want = np.empty((n, k), np.uint16)
+        oracle.lib.orc_int8_dequant_bf16(P(codes), P(scale), n, k, P(want))
+        assert np.array_equal(bits(out), want)
+    # int8_vae_weights_match_dense_hadamard (tests/test_int8_weight.cu:95-141): fp16, bit-exact
+    for g in (1, 4, 16, 64, 256):
+        for cols in (2 * g, 267):
+            grp = g if cols % g == 0 else 1
+            codes, scales = golden[f"i8_{g}_{cols}_codes"], golden[f"i8_{g}_{cols}_scales"]
+            for canon in (0, 1):
+                out = torch.empty((5, cols), dtype=torch.float16, device="cuda")
+                dc, dsc = dev(codes), dev(scales)
+                sfq.check(sfq.lib.sfq_unpack_int8_f16(sfq.ptr(dc), sfq.ptr(dsc), sfq.ptr(out), 5, cols, grp, canon, S))
+                assert np.array_equal(bits(out), golden[f"i8_{g}_{cols}_{canon}"]), (g, cols, canon)
+
+
+@pytest.mark.parametrize("rows,dim", [(9, 5120), (5, 1024), (3, 13824), (2, 256)])
+@pytest.mark.parametrize("modulate", [False, True])
+def test_rmsnorm_and_modulate_bit_exact(rows, dim, modulate):
+    rng = np.random.default_rng(rows * dim)
+    x = gaussian_bf16((rows, dim), seed=dim + rows)
+    w = oracle.to_bf16((1.0 + 0.1 * rng.standard_normal(dim)).astype(np.float32))
+    scale = (0.1 * rng.standard_normal((3, dim))).astype(np.float32)
+    shift = (0.1 * rng.standard_normal((3, dim))).astype(np.float32)
+    a = (np.arange(rows) % 3).astype(np.int32)
+    dx, dw, dsc, dsh, da = bf16_tensor(x), bf16_tensor(w), dev(scale), dev(shift), dev(a)
+    norm = sfq.Norm(sfq.ptr(dw), sfq.ptr(dsc) if modulate else None, sfq.ptr(dsh) if modulate else None,
+                    sfq.ptr(da) if modulate else None, 1e-5)
+    out = torch.empty((rows, dim), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_rmsnorm(sfq.ptr(dx), C.byref(norm), sfq.ptr(out), rows, dim, S))
+    want = oracle.rmsnorm_bf16(x, w, 1e-5, *((scale, shift, a) if modulate else ()))
+    diff = int((bits(out) != want).sum())
+    assert diff == 0, f"{diff} of {rows * dim} bf16 words differ from the oracle"
+    ref = ref_dev()
+    if ref is not None:
+        out2 = torch.empty_like(out)
+        ref_check(ref, ref.ref_dev_rmsnorm(sfq.ptr(dx), sfq.ptr(dw), sfq.ptr(dsc) if modulate else None,
+                                           sfq.ptr(dsh) if modulate else None, sfq.ptr(da) if modulate else None,
+                                           sfq.ptr(out2), rows, dim, 1e-5))
+        diff = int((out.view(torch.int16) != out2.view(torch.int16)).sum())
+        assert diff == 0, f"{diff} words differ from the reference kernel"
+
+
+@pytest.mark.parametrize("rows,dim,group", [(5, 256, 256), (2, 768, 256), (7, 5120, 256), (3, 64, 16), (4, 512, 64), (3, 64, 4)])
+def test_convrot_bit_exact(rows, dim, group):
+    x = oracle.to_bf16(oracle.make_data(rows * dim, 131 + dim, 1.0).reshape(rows, dim))
+    dx = bf16_tensor(x)
+    out = torch.empty_like(dx)
+    sfq.check(sfq.lib.sfq_convrot(sfq.ptr(dx), sfq.ptr(out), rows, dim, group, S))
+    assert np.array_equal(bits(out), oracle.convrot_bf16(x, group))
+    # against the explicit Kronecker product, and not Sylvester's matrix
+    dense = oracle.convrot_dense(oracle.from_bf16(x), group)
+    assert np.abs(out.float().cpu().numpy() - dense).max() < 1e-2
+    ref = ref_dev()
+    if ref is not None:
+        out2 = torch.empty_like(out)
+        ref_check(ref, ref.ref_dev_convrot(sfq.ptr(dx), sfq.ptr(out2), rows, dim, group))
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    assert sfq.lib.sfq_convrot(sfq.ptr(dx), sfq.ptr(out), rows, dim, 8, S) == sfq.ERR_RUNTIME  # not a power of four
+
+
+@pytest.mark.parametrize("rows,dim,outliers", [(3, 256, False), (33, 5120, True), (5, 13824, False), (4, 1024, True)])
+def test_fused_convrot_int8_quantizer_bit_exact(rows, dim, outliers):
+    x = gaussian_bf16((rows, dim), seed=rows + dim, outliers=outliers)
+    x[0] = 0  # a zero row: scale floors at 1e-30, codes all zero
+    if rows > 2:
+        x[1] = 0
+        x[1, 0] = oracle.to_bf16(np.float32(1.0))  # unit impulse
+        x[2] = oracle.to_bf16(np.float32(1.0))      # all ones
+    dx = bf16_tensor(x)
+    q = torch.empty((rows, dim), dtype=torch.int8, device="cuda")
+    s = torch.empty(rows, dtype=torch.float32, device="cuda")
+    sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(dx), None, sfq.ptr(q), sfq.ptr(s), None, rows, dim, 1, S))
+    rot = oracle.convrot_bf16(x)
+    wq, ws = oracle.quantize_int8_token(rot)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+    bad = int((q.cpu().numpy() != wq).sum())
+    assert bad == 0, f"{bad} int8 activations differ"
+    ref = ref_dev()
+    if ref is not None:
+        r = torch.empty_like(dx)
+        q2, s2 = torch.empty_like(q), torch.empty_like(s)
+        ref_check(ref, ref.ref_dev_convrot(sfq.ptr(dx), sfq.ptr(r), rows, dim, 256))
+        ref_check(ref, ref.ref_dev_quantize_int8_bf16(sfq.ptr(r), sfq.ptr(q2), sfq.ptr(s2), rows, dim))
+        assert torch.equal(q, q2) and torch.equal(s.view(torch.int32), s2.view(torch.int32))
+    # without the rotation it is launch_quantize_w4a8_bf16 on its own
+    sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(dx), None, sfq.ptr(q), sfq.ptr(s), None, rows, dim, 0, S))
+    wq, ws = oracle.quantize_int8_token(x)
+    assert np.array_equal(q.cpu().numpy(), wq) and np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+    assert sfq.lib.sfq_quantize_int8_token(sfq.ptr(dx), None, sfq.ptr(q), sfq.ptr(s), None, rows, dim + 8, 1, S) \
+        == sfq.ERR_INVALID_ARGUMENT
+
+
+def test_fused_norm_modulate_convrot_int8_chain():
+    rows, dim = 21, 5120
+    rng = np.random.default_rng(77)
+    x = gaussian_bf16((rows, dim), seed=4, outliers=True)
+    w = oracle.to_bf16(np.ones(dim, np.float32))
+    scale = (0.1 * rng.standard_normal((3, dim))).astype(np.float32)
+    shift = (0.1 * rng.standard_normal((3, dim))).astype(np.float32)
+    a = (np.arange(rows) % 3).astype(np.int32)
+    dx, dw, dsc, dsh, da = bf16_tensor(x), bf16_tensor(w), dev(scale), dev(shift), dev(a)
+    norm = sfq.Norm(sfq.ptr(dw), sfq.ptr(dsc), sfq.ptr(dsh), sfq.ptr(da), 1e-5)
+    q = torch.empty((rows, dim), dtype=torch.int8, device="cuda")
+    s = torch.empty(rows, dtype=torch.float32, device="cuda")
+    normed = torch.empty((rows, dim), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(dx), C.byref(norm), sfq.ptr(q), sfq.ptr(s), sfq.ptr(normed),
+                                              rows, dim, 1, S))
+    n = oracle.rmsnorm_bf16(x, w, 1e-5, scale, shift, a)
+    assert np.array_equal(bits(normed), n)
+    wq, ws = oracle.quantize_int8_token(oracle.convrot_bf16(n))
+    assert np.array_equal(q.cpu().numpy(), wq) and np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+
+
+def test_nvfp4_activation_quantizer_reference_layout(golden):
+    # nvfp4_activation_quantisation (tests/test_nn_kernels_nvfp4_synthetic.cu:380-453), byte-exact
+    x = golden["act_x_bf16"]
+    dx = bf16_tensor(x)
+    packed = torch.empty((7, 32), dtype=torch.uint8, device="cuda")
+    scales = torch.empty((7, 4), dtype=torch.uint8, device="cuda")
+    sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(packed), sfq.ptr(scales), None, 7, 64,
+                                               sfq.NVFP4_ACT_REFERENCE, S))
+    wp, ws, _ = oracle.nvfp4_quantize_act(x)
+    assert np.array_equal(_u8(packed), wp) and np.array_equal(_u8(scales), ws)
+    hs, hq = _u8(scales), _u8(packed)
+    assert hs[0, 0] == 0 and not hq[0, :8].any() and hs[1, 1] == 0
+    assert oracle.lib.orc_e4m3_to_f32(int(hs[2, 2])) == 448.0 and (hq[2, 16:24] == 0x77).all()
+    ref = ref_dev()
+    for rows, dim in ((7, 64), (130, 5120), (3, 1024)):
+        x = gaussian_bf16((rows, dim), seed=rows, sigma=0.7)
+        dx = bf16_tensor(x)
+        packed = torch.empty((rows, dim // 2), dtype=torch.uint8, device="cuda")
+        scales = torch.empty((rows, dim // 16), dtype=torch.uint8, device="cuda")
+        sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(packed), sfq.ptr(scales), None, rows, dim,
+                                                   sfq.NVFP4_ACT_REFERENCE, S))
+        wp, ws, _ = oracle.nvfp4_quantize_act(x)
+        assert np.array_equal(_u8(packed), wp) and np.array_equal(_u8(scales), ws), (rows, dim)
+        if ref is not None:
+            p2, s2 = torch.empty_like(packed), torch.empty_like(scales)
+            ref_check(ref, ref.ref_dev_quantize_nvfp4_act(sfq.ptr(dx), sfq.ptr(p2), sfq.ptr(s2), rows, dim))
+            assert torch.equal(packed, p2) and torch.equal(scales, s2)
+        # GEMM-feed layout: same codes with the nibbles of every byte swapped, scales through the tile map,
+        # padding rows of the last 128-row tile zeroed
+        nb = sfq.lib.sfq_nvfp4_act_scale_bytes(rows, dim)
+        assert nb == ((rows + 127) // 128) * 128 * (dim // 16)
+        if dim % 64 == 0:
+            fp = torch.empty_like(packed)
+            fs = torch.full((nb,), 0xAA, dtype=torch.uint8, device="cuda")
+            sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(fp), sfq.ptr(fs), None, rows, dim,
+                                                       sfq.NVFP4_ACT_GEMM_FEED, S))
+            swapped = ((wp << 4) | (wp >> 4)).astype(np.uint8)
+            assert np.array_equal(_u8(fp), swapped)
+            tiled = np.zeros(nb, np.uint8)
+            for r in range(rows):
+                for b in range(dim // 16):
+                    tiled[oracle.lib.orc_nvfp4_scale_slot(r, b, dim // 16)] = ws[r, b]
+            assert np.array_equal(_u8(fs), tiled)
+    assert sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(packed), sfq.ptr(scales), None, 3, 1000,
+                                            sfq.NVFP4_ACT_REFERENCE, S) == sfq.ERR_RUNTIME
+
+
+def test_pointwise_kernels_match_reference():
+    rng = np.random.default_rng(1)
+    rows, inner = 6, 512
+    y = oracle.to_bf16((2.0 * rng.standard_normal((rows, 2 * inner))).astype(np.float32))
+    ref = ref_dev()
+    g = bf16_tensor(y)
+    sfq.check(sfq.lib.sfq_gelu_tanh(sfq.ptr(g), g.numel(), S))
+    want = y.copy()
+    oracle.lib.orc_gelu_tanh_bf16(P(want), want.size)
+    # host tanh may differ from the device's in the last place: one bf16 ulp against the CPU oracle ...
+    assert np.abs(bits(g).astype(np.int32) - want.astype(np.int32)).max() <= 1
+    if ref is not None:  # ... and exact against the reference kernel
+        g2 = bf16_tensor(y)
+        ref_check(ref, ref.ref_dev_gelu_tanh(sfq.ptr(g2), g2.numel()))
+        assert torch.equal(g.view(torch.int16), g2.view(torch.int16))
+    fused = bf16_tensor(y)
+    out = torch.empty((rows, inner), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_swiglu(sfq.ptr(fused), sfq.ptr(out), rows, inner, S))
+    want = np.empty((rows, inner), np.uint16)
+    oracle.lib.orc_swiglu_bf16(P(y), rows, inner, P(want))
+    assert np.abs(bits(out).astype(np.int32) - want.astype(np.int32)).max() <= 1
+    if ref is not None:
+        out2 = torch.empty_like(out)
+        ref_check(ref, ref.ref_dev_swiglu(sfq.ptr(fused), sfq.ptr(out2), rows, inner))
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    x = oracle.to_bf16(rng.standard_normal((rows, inner)).astype(np.float32))
+    br = oracle.to_bf16(rng.standard_normal((rows, inner)).astype(np.float32))
+    gate = rng.standard_normal((3, inner)).astype(np.float32)
+    a = (np.arange(rows) % 3).astype(np.int32)
+    dx, dbr, dg, da = bf16_tensor(x), bf16_tensor(br), dev(gate), dev(a)
+    sfq.check(sfq.lib.sfq_add_gated(sfq.ptr(dx), sfq.ptr(dbr), sfq.ptr(dg), sfq.ptr(da), rows, inner, S))
+    want = x.copy()
+    oracle.lib.orc_add_gated_bf16(P(want), P(br), P(gate), P(a), rows, inner)
+    assert np.array_equal(bits(dx), want)
