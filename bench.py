@@ -1,0 +1,426 @@
+"""Benchmark of the quantized-Linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--extra]
+
+Workload (config.workload): BASELINE config 2 -- the W4A8 attention projection, M=4096 tokens,
+K=N=5120, weights ~N(0,0.02) packed by the library's W4A8 packer, activations bf16 ~N(0,1) with
+0.1 % outliers x20, fp32 bias, seed 1. A step is one LinearRunner.forward: expand the packed weight,
+fused ConvRot + per-token int8, tcgen05 int8 GEMM with the scale/bias epilogue (3 launches).
+
+value  whole-job TFLOP/s (2*M*N*K per step per GPU) with inputs resident in HBM, K steps between CUDA
+       events, max over ranks. Inputs rotate over several distinct buffers whose total exceeds L2.
+e2e    the same metric through the same call with HOST buffers: pinned x -> device, forward, y -> host,
+       both copies inside the timed region.
+roofline   the dominant kernel (the int8 GEMM) timed alone with CUDA events; tensor-bound.
+cpu_baseline / --impl reference   the reference's host path (decode to dense fp32, x * W^T) restated in
+       oracle/ and timed on the host cores over a bounded row sample.
+Multi-GPU: tokens are sharded, weights replicated, no collective on the data path (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+M, N, K = 4096, 5120, 5120
+SEED = 1
+WORKLOAD = "config2: W4A8 attention projection M=4096 K=N=5120, bf16 in/out, fp32 bias"
+METRIC = "quantized_linear_tflops"
+UNIT = "TFLOP/s"
+CPU_SAMPLE_ROWS = 256
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def make_inputs(np, rows, seed, rank=0):
+    import oracle
+    from helpers import pack_w4a8
+
+    rng = np.random.default_rng(seed)
+    w = (0.02 * rng.standard_normal((N, K))).astype(np.float32)
+    packed, s_rel, s_ch, book = pack_w4a8(w)
+    bias = (0.01 * rng.standard_normal(N)).astype(np.float32)
+    if rank:
+        rng = np.random.default_rng(seed + 1000 * rank)  # same weights on every rank, its own rows of tokens
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    x = np.where(rng.random((rows, K)) < 1e-3, x * 20.0, x).astype(np.float32)
+    return dict(packed=packed, s_rel=s_rel, s_ch=s_ch, book=book, bias=bias, x=oracle.to_bf16(x))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [m for m in mhz if m >= 0.5 * mx] or mhz
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def cpu_baseline(np, data, steps=1, warmup=0):
+    """Reference host path on a bounded sample: decode W to dense fp32, rotate x, y = x W^T, all host threads."""
+    import ctypes as C
+
+    import oracle
+
+    rows = CPU_SAMPLE_ROWS
+    x = np.ascontiguousarray(data["x"][:rows])
+    y = np.empty((rows, N), np.float32)
+    P = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+
+    def once():
+        oracle.lib.orc_host_dequant_matmul(4, P(x), rows, P(data["packed"]), P(data["s_rel"]), P(data["s_ch"]),
+                                           P(data["book"]), 1.0, 16, N, K, P(y))
+
+    for _ in range(warmup):
+        once()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        once()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": UNIT, "cores": oracle.lib.orc_num_threads(),
+            "kind": "port", "sample": f"{rows} of {M} rows of the workload, weight decode included, per step",
+            "ms_per_sample": dt * 1e3}
+
+
+def run_reference(args):
+    import numpy as np
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    data = make_inputs(np, CPU_SAMPLE_ROWS, SEED)
+    base = cpu_baseline(np, data, steps=max(1, args.steps), warmup=min(args.warmup, 2))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_sample"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "seed": SEED}, "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def time_region(torch, fn, iters):
+    """CUDA-event time of `iters` calls on the current stream, in milliseconds."""
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn(i)
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b)
+
+
+def run_ours(args):
+    import ctypes as C
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import slopfab_b200 as sfq
+    from helpers import bf16_tensor, dev
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = load_peaks()
+    data = make_inputs(np, M, SEED, rank)  # every rank owns M rows of the token axis; weights replicated
+
+    # ---- device-resident inputs, rotated so that consecutive steps never find their operands in L2
+    ROT = 4  # 4 x (42 MB activations + 13 MB packed weight + 42 MB output) >> 126 MB of L2
+    xs = [bf16_tensor(np.roll(data["x"], i, axis=0)) for i in range(ROT)]
+    ys = [torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(ROT)]
+    weights, keep = [], []
+    for i in range(ROT):
+        t = [dev(data["packed"]), dev(data["s_rel"]), dev(data["s_ch"]), dev(data["book"]), dev(data["bias"])]
+        keep.append(t)
+        weights.append(sfq.new_weight(format=sfq.W4A8, data=sfq.ptr(t[0]), out_features=N, in_features=K,
+                                      block_scale=sfq.ptr(t[1]), weight_scale=sfq.ptr(t[2]), w4_codebook=sfq.ptr(t[3]),
+                                      packed_group_size=16, convrot=1, convrot_group=256, bias=sfq.ptr(t[4])))
+    runner = sfq.LinearRunner()
+    runner.reserve(runner.workspace_bytes(weights[0], M))
+
+    def step(i):
+        runner.forward(weights[i % ROT], xs[i % ROT], ys[i % ROT])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    with ClockSampler(local) as clocks:
+        barrier()
+        ms = time_region(torch, step, args.steps)
+        barrier()
+        # ---- end to end: host buffers, copies inside the timed region
+        hx = [torch.from_numpy(np.roll(data["x"], i, axis=0).view(np.int16)).view(torch.bfloat16).pin_memory()
+              for i in range(2)]
+        hy = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+
+        def e2e_step(i):
+            xs[i % ROT].copy_(hx[i % 2], non_blocking=True)
+            step(i)
+            hy[i % 2].copy_(ys[i % ROT], non_blocking=True)
+
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        e2e_steps = max(3, min(args.steps, 20))
+        e2e_ms = time_region(torch, e2e_step, e2e_steps)
+        barrier()
+        # ---- the dominant kernel alone: int8 GEMM on pre-quantized operands
+        q = torch.empty((M, K), dtype=torch.int8, device="cuda")
+        rs = torch.empty(M, dtype=torch.float32, device="cuda")
+        w8 = [torch.empty((N, K), dtype=torch.int8, device="cuda") for _ in range(ROT)]
+        qs = [torch.empty_like(q) for _ in range(ROT)]
+        for i in range(ROT):
+            t = keep[i]
+            sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(t[0]), sfq.ptr(t[1]), sfq.ptr(t[3]), sfq.ptr(w8[i]), N, K, 16,
+                                                   sfq.stream_ptr()))
+            sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(xs[i]), None, sfq.ptr(qs[i]), sfq.ptr(rs), None, M, K, 1,
+                                                      sfq.stream_ptr()))
+        eps = [sfq.Epilogue(sfq.ptr(rs), sfq.ptr(keep[i][2]), 1.0, sfq.ptr(keep[i][4]), sfq.F32, sfq.ACT_NONE)
+               for i in range(ROT)]
+
+        def gemm_only(i):
+            j = i % ROT
+            sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(qs[j]), sfq.ptr(w8[j]), C.byref(eps[j]), sfq.ptr(ys[j]), M, N, K,
+                                            sfq.stream_ptr()))
+
+        def quant_only(i):
+            j = i % ROT
+            sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(xs[j]), None, sfq.ptr(qs[j]), sfq.ptr(rs), None, M, K, 1,
+                                                      sfq.stream_ptr()))
+
+        def unpack_only(i):
+            j = i % ROT
+            t = keep[j]
+            sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(t[0]), sfq.ptr(t[1]), sfq.ptr(t[3]), sfq.ptr(w8[j]), N, K, 16,
+                                                   sfq.stream_ptr()))
+
+        kern = {}
+        for name, fn in (("gemm_int8", gemm_only), ("quantize_int8_token", quant_only), ("unpack_w4a8", unpack_only)):
+            for i in range(3):
+                fn(i)
+            torch.cuda.synchronize()
+            kern[name] = time_region(torch, fn, max(args.steps, 10)) / max(args.steps, 10)
+        barrier()
+    status = sfq.device_status()
+
+    times = torch.tensor([ms, e2e_ms / e2e_steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_max, e2e_ms_step = times[0].item(), times[1].item()
+    flops_step = 2.0 * M * N * K
+    value = world * flops_step * args.steps / (ms_max * 1e-3) / 1e12
+    e2e_value = world * flops_step / (e2e_ms_step * 1e-3) / 1e12
+
+    if rank == 0:
+        int8_peak = 2.0 * peaks["bf16_tflops"]
+        gemm_tflops = flops_step / (kern["gemm_int8"] * 1e-3) / 1e12
+        quant_bytes = 2.0 * M * K + M * K + 4.0 * M
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_max / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "seed": SEED, "rows_per_gpu": M,
+                       "l2": f"inputs rotate over {ROT} distinct buffer sets (~{ROT * 97} MB) larger than the 126 MB L2",
+                       "parallelism": f"token-sharded x{world}, weights replicated, no collective"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N,
+                    "ms_per_step": e2e_ms_step},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<int8,128x256>", "achieved": gemm_tflops,
+                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / int8_peak, "traffic": None,
+                         "peak_note": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s); "
+                                      "nominal dense int8 is 4500",
+                         "ms_per_launch": kern["gemm_int8"]},
+            "kernels_ms": kern,
+            "streaming": {"quantize_int8_token_GBps": quant_bytes / (kern["quantize_int8_token"] * 1e-3) / 1e9,
+                          "unpack_w4a8_GBps": (N * K / 2 + N * K / 16 + N * K) / (kern["unpack_w4a8"] * 1e-3) / 1e9,
+                          "hbm_peak_GBps": peaks["hbm_gbs"], "peak_source": peaks["source"]},
+            "device_status": status,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(np, data, steps=2, warmup=1)
+        if args.extra and world == 1:
+            del xs, ys, w8, qs
+            torch.cuda.empty_cache()
+            line["extra"] = extra_measurements(torch, np, sfq, peaks)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extra_measurements(torch, np, sfq, peaks):
+    """GEMM-only throughput at the other DiT shapes (random operands, GEMM timed alone)."""
+    import ctypes as C
+
+    out = {}
+    shapes = [("ffn_up_M32760", 32760, 13824, 5120), ("ffn_down_M32760", 32760, 5120, 13824),
+              ("attn_proj_M32760", 32760, 5120, 5120)]
+    for name, m, n, k in shapes:
+        a8 = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
+        w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
+        rs = torch.rand(m, device="cuda") * 0.01
+        cs = torch.rand(n, device="cuda") * 0.01
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
+        fn = lambda i: sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(a8), sfq.ptr(w8), C.byref(ep), sfq.ptr(y), m, n, k,  # noqa: E731
+                                                       sfq.stream_ptr()))
+        for i in range(2):
+            fn(i)
+        torch.cuda.synchronize()
+        ms = time_region(torch, fn, 5) / 5
+        out["int8_" + name] = {"ms": ms, "tflops": 2.0 * m * n * k / ms / 1e9, "frac_of_2x_bf16": 2.0 * m * n * k / ms / 1e9 / (2 * peaks["bf16_tflops"])}
+        # nvfp4 at the same shape: random nibbles, scales near 1
+        aq = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda")
+        wq = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+        asf = torch.randint(0x30, 0x40, (sfq.lib.sfq_nvfp4_act_scale_bytes(m, k),), dtype=torch.uint8, device="cuda")
+        wsf = torch.randint(0x30, 0x40, (n * k // 16,), dtype=torch.uint8, device="cuda")
+        ep4 = sfq.Epilogue(None, None, 1e-3, None, sfq.F32, sfq.ACT_NONE)
+        fn4 = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
+                                                         C.byref(ep4), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
+        for i in range(2):
+            fn4(i)
+        torch.cuda.synchronize()
+        ms = time_region(torch, fn4, 5) / 5
+        out["nvfp4_" + name] = {"ms": ms, "tflops": 2.0 * m * n * k / ms / 1e9, "frac_of_4x_bf16": 2.0 * m * n * k / ms / 1e9 / (4 * peaks["bf16_tflops"])}
+        del a8, w8, aq, wq, asf, wsf, y
+        torch.cuda.empty_cache()
+    out["device_status"] = sfq.device_status()
+    return out
+
+
+def run_case(name):
+    """One kernel, three launches, on operands larger than L2: the target of an ncu capture."""
+    import ctypes as C
+
+    import torch
+
+    import slopfab_b200 as sfq
+
+    torch.cuda.set_device(0)
+    m, n, k = 16384, 5120, 5120
+    y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    if name == "gemm_int8":
+        a8 = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
+        w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
+        rs, cs = torch.rand(m, device="cuda") * 0.01, torch.rand(n, device="cuda") * 0.01
+        ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
+        fn = lambda i: sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(a8), sfq.ptr(w8), C.byref(ep), sfq.ptr(y), m, n, k,  # noqa: E731
+                                                       sfq.stream_ptr()))
+        work = 2.0 * m * n * k
+    elif name == "gemm_nvfp4":
+        aq = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda")
+        wq = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+        asf = torch.randint(0x30, 0x40, (sfq.lib.sfq_nvfp4_act_scale_bytes(m, k),), dtype=torch.uint8, device="cuda")
+        wsf = torch.randint(0x30, 0x40, (n * k // 16,), dtype=torch.uint8, device="cuda")
+        ep = sfq.Epilogue(None, None, 1e-3, None, sfq.F32, sfq.ACT_NONE)
+        fn = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
+                                                        C.byref(ep), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
+        work = 2.0 * m * n * k
+    elif name in ("quantize_int8", "quantize_nvfp4"):
+        m = 32768
+        x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+        q = torch.empty((m, k), dtype=torch.int8, device="cuda")
+        rs = torch.empty(m, device="cuda")
+        sc = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(m, k), dtype=torch.uint8, device="cuda")
+        if name == "quantize_int8":
+            fn = lambda i: sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(x), None, sfq.ptr(q), sfq.ptr(rs), None, m, k,  # noqa: E731
+                                                                     1, sfq.stream_ptr()))
+            work = 3.0 * m * k + 4 * m
+        else:
+            fn = lambda i: sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(x), None, sfq.ptr(q), sfq.ptr(sc), None, m,  # noqa: E731
+                                                                      k, sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
+            work = 2.0 * m * k + m * k / 2 + m * k / 16
+    else:
+        raise SystemExit("unknown case " + name)
+    fn(0)
+    torch.cuda.synchronize()
+    ms = time_region(torch, fn, 3) / 3
+    print(json.dumps({"case": name, "ms_per_launch": ms, "work_per_second": work / (ms * 1e-3),
+                      "device_status": sfq.device_status()}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu) and exit: gemm_int8, "
+                    "gemm_nvfp4, quantize_int8, quantize_nvfp4")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--extra", action="store_true", help="also time the GEMMs at the other DiT shapes (1 GPU)")
+    args = ap.parse_args()
+    if args.case:
+        run_case(args.case)
+        return
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
