@@ -1,0 +1,72 @@
+"""Multi-GPU execution of the quantized Linear: one process per GPU, torch.distributed for the plumbing.
+
+Every output row of the path depends on one input row, and weights are read-only, so:
+
+* token sharding (primary): rank r owns a contiguous block of token rows and a full replica of the packed
+  weights; there is no collective on the data path.
+* FFN-up column split (secondary): rank r owns output columns [c0, c1) of the weight. The *quantized*
+  activation -- the smallest representation of x (int8 + one fp32 scale per row) -- is exchanged with ONE
+  all-gather, landing in ordinary local memory, and each rank then computes y[:, c0:c1] for all tokens.
+
+The reference is single-GPU (no collective exists in its tree); this file is new behaviour.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def token_shard(rows: int, world: int, rank: int) -> tuple[int, int]:
+    """(first row, row count) of rank's contiguous block; the first rows % world ranks take one extra row."""
+    if rows < 0 or world <= 0 or not 0 <= rank < world:
+        raise ValueError("token_shard: bad arguments")
+    base, extra = divmod(rows, world)
+    start = rank * base + min(rank, extra)
+    return start, base + (1 if rank < extra else 0)
+
+
+def column_shard(cols: int, world: int, rank: int, multiple: int = 128) -> tuple[int, int]:
+    """(first column, column count) in units of `multiple` columns (128 keeps NVFP4 scale tiles whole)."""
+    if cols % multiple != 0:
+        raise ValueError(f"column_shard: {cols} columns are not a multiple of {multiple}")
+    start, count = token_shard(cols // multiple, world, rank)
+    return start * multiple, count * multiple
+
+
+def all_gather_rows(local: torch.Tensor, group=None) -> torch.Tensor:
+    """Concatenates every rank's rows (ragged counts allowed) with a single all-gather of padded blocks."""
+    if local.dtype != torch.uint8:  # move bytes: every backend gathers uint8, not every backend gathers int16/bf16
+        width = local.shape[1:]
+        flat = local.contiguous().view(local.shape[0], -1).view(torch.uint8)
+        return all_gather_rows(flat, group).view(local.dtype).view((-1,) + tuple(width))
+    world = dist.get_world_size(group)
+    counts = torch.zeros(world, dtype=torch.int64, device=local.device)
+    counts[dist.get_rank(group)] = local.shape[0]
+    dist.all_reduce(counts, group=group)
+    counts = counts.tolist()
+    most = max(counts)
+    padded = local
+    if local.shape[0] != most:
+        padded = torch.zeros((most,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        padded[: local.shape[0]] = local
+    out = torch.empty((world * most,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    if all(c == most for c in counts):
+        return out
+    return torch.cat([out[r * most: r * most + counts[r]] for r in range(world)], dim=0)
+
+
+def column_split_int8_forward(quantize, gemm, x_local: torch.Tensor, group=None) -> torch.Tensor:
+    """y[:, local columns] for ALL tokens.
+
+    quantize(x_local) -> (q int8 [m, K], row_scale fp32 [m]) runs on the local token rows;
+    gemm(q_all, row_scale_all) -> y_all_tokens[:, local columns] runs against the local weight columns.
+    The one collective is the all-gather of q with the row scales appended as four extra int8 columns.
+    """
+    q, s = quantize(x_local)
+    packed = torch.cat([q, s.view(-1, 1).contiguous().view(torch.int8).view(-1, 4)], dim=1)
+    gathered = all_gather_rows(packed, group)
+    k = q.shape[1]
+    q_all = gathered[:, :k].contiguous()
+    s_all = gathered[:, k:].contiguous().view(torch.float32).view(-1)
+    return gemm(q_all, s_all)
