@@ -259,6 +259,38 @@ SFQ_API int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w
                                         const void* d_x_bf16, int rows, void* d_y_bf16, void* d_workspace,
                                         size_t workspace_bytes);
 
+/* ---- for callers that cannot allocate ------------------------------------------ */
+
+/* Bytes of scratch built into the library image for sfq_linear_nvfp4_forward_static (16 MiB, plus a
+ * 256-byte status area). Every GPU that loads libsfq.so holds this much until the process exits. */
+#define SFQ_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+
+/* The native NVFP4 Linear, y[rows,out] = epilogue(x[rows,in] W^T), without any allocation and without a
+ * caller workspace. (No counterpart in the reference: its runner always carves scratch from a
+ * Workspace arena.) It is meant for hosts that may not allocate when they call us -- an embedder that has
+ * handed out all device memory up front, a plugin invoked inside a frame or audio callback, a serving loop
+ * that freezes its allocator after start-up -- and for whom even passing a workspace is not possible
+ * because they own no spare device buffer. The quantized activation lives in a fixed array inside the
+ * library instead; inputs and outputs are still the caller's.
+ *   - Limit: align256(rows * in_features / 2) + ceil(rows/128)*128 * in_features/16 must not exceed
+ *     SFQ_STATIC_SCRATCH_BYTES (e.g. 2048 rows x 13824, or 5800 rows x 5120). Larger calls are refused with
+ *     SFQ_ERR_INVALID_ARGUMENT and a message; split the rows or use sfq_linear_forward.
+ *   - No cudaMalloc / cudaFree / allocating library call is made, on any call.
+ *   - The first call on each device looks up the device address of the array (a host-side query, no
+ *     allocation). Make that first call outside of any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels can overlap on the GPU (different
+ *     streams, or graph branches) race on it. Serialise them on one stream.
+ *   - The array keeps the previous call's bytes; the call rewrites everything it later reads and clears its
+ *     status word, so earlier calls never leak into the result.
+ *   - A kernel that abandons a bounded wait records it in the array's own status word, not in the word
+ *     sfq_device_status reads.
+ * Weight layout, bias, activation and numerics are those of sfq_gemm_nvfp4 fed by
+ * sfq_quantize_nvfp4_block(GEMM_FEED); results are bit-identical to the runner's native NVFP4 path. */
+SFQ_API int sfq_linear_nvfp4_forward_static(const void* d_x_bf16, int rows, const uint8_t* d_w_packed,
+                                            const uint8_t* d_w_scale_tiled, float global_scale, const void* d_bias,
+                                            int bias_format, int activation, void* d_y_bf16, int out_features,
+                                            int in_features, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

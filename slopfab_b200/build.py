@@ -1,6 +1,6 @@
 """Builds slopfab_b200/libsfq.so (the CUDA kernels + C++ runner + C ABI) in-tree for sm_100a.
 
-    python -m slopfab_b200.build [--force]
+    python slopfab_b200/build.py [--force]      (run by path: importing the package needs the library)
 
 nvcc cross-compiles without a GPU. Objects go to slopfab_b200/build/, the library next to this file.
 """
@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libsfq.so")
 SOURCES = ["gemm_tc.cu", "unpack.cu", "act_quant.cu", "pointwise.cu", "runtime.cu", "linear_runner.cu", "capi.cu",
-           "capi_runner.cu", "packers.cpp"]
+           "capi_runner.cu", "static_scratch.cu", "packers.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden,-fopenmp"]
 

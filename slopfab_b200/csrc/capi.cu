@@ -119,6 +119,7 @@ int run_guarded(void (*fn)(void*), void* ctx) {
   return guarded([&] { fn(ctx); });
 }
 sc::QuantWeight weight_from_c(const sfq_quant_weight* w) { return to_weight(w); }
+void set_error(const char* text) { g_error = text ? text : ""; }  // for entry points in other files
 }  // namespace sfq_capi
 
 extern "C" {
