@@ -317,8 +317,8 @@ def extra_measurements(torch, np, sfq, peaks):
     import ctypes as C
 
     out = {}
-    shapes = [("ffn_up_M32760", 32760, 13824, 5120), ("ffn_down_M32760", 32760, 5120, 13824),
-              ("attn_proj_M32760", 32760, 5120, 5120)]
+    shapes = [("attn_proj_M4096", 4096, 5120, 5120), ("ffn_up_M32760", 32760, 13824, 5120),
+              ("ffn_down_M32760", 32760, 5120, 13824), ("attn_proj_M32760", 32760, 5120, 5120)]
     for name, m, n, k in shapes:
         a8 = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
         w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
@@ -328,11 +328,6 @@ def extra_measurements(torch, np, sfq, peaks):
         ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
         fn = lambda i: sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(a8), sfq.ptr(w8), C.byref(ep), sfq.ptr(y), m, n, k,  # noqa: E731
                                                        sfq.stream_ptr()))
-        for i in range(2):
-            fn(i)
-        torch.cuda.synchronize()
-        ms = time_region(torch, fn, 5) / 5
-        out["int8_" + name] = {"ms": ms, "tflops": 2.0 * m * n * k / ms / 1e9, "frac_of_2x_bf16": 2.0 * m * n * k / ms / 1e9 / (2 * peaks["bf16_tflops"])}
         # nvfp4 at the same shape: random nibbles, scales near 1
         aq = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda")
         wq = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
@@ -341,11 +336,18 @@ def extra_measurements(torch, np, sfq, peaks):
         ep4 = sfq.Epilogue(None, None, 1e-3, None, sfq.F32, sfq.ACT_NONE)
         fn4 = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
                                                          C.byref(ep4), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
-        for i in range(2):
-            fn4(i)
-        torch.cuda.synchronize()
-        ms = time_region(torch, fn4, 5) / 5
-        out["nvfp4_" + name] = {"ms": ms, "tflops": 2.0 * m * n * k / ms / 1e9, "frac_of_4x_bf16": 2.0 * m * n * k / ms / 1e9 / (4 * peaks["bf16_tflops"])}
+        reps = 20 if m <= 4096 else 5
+        for tile_n in (256, 128):
+            sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
+            for kind, f, mult in (("int8", fn, 2), ("nvfp4", fn4, 4)):
+                for i in range(2):
+                    f(i)
+                torch.cuda.synchronize()
+                ms = time_region(torch, f, reps) / reps
+                tf = 2.0 * m * n * k / ms / 1e9
+                out[f"{kind}_{name}_bn{tile_n}"] = {"ms": round(ms, 4), "tflops": round(tf, 1),
+                                                    f"frac_of_{mult}x_bf16": round(tf / (mult * peaks["bf16_tflops"]), 3)}
+        sfq.lib.sfq_gemm_tuning(0, 0, 0)
         del a8, w8, aq, wq, asf, wsf, y
         torch.cuda.empty_cache()
     out["device_status"] = sfq.device_status()
@@ -361,6 +363,7 @@ def run_case(name):
     import slopfab_b200 as sfq
 
     torch.cuda.set_device(0)
+    sfq.lib.sfq_gemm_tuning(int(os.environ.get("SFQ_TILE_N", "0")), 0, 0)  # experiments: 128 or 256
     m, n, k = 16384, 5120, 5120
     y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     if name == "gemm_int8":

@@ -293,18 +293,29 @@ __global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
     }
     __syncthreads();
     const float divisor = round_bf16(bcast[1]);
+    // x / divisor, correctly rounded, without a division per element: with r = RN(1/d) exactly rounded,
+    // q0 = RN(x r), e = x - d q0 (exact in one fused multiply-add) and q = RN(q0 + e r) is the IEEE quotient.
+    const float rcp = __frcp_rn(divisor);
     if (active) {
       uint32_t o[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        uint32_t acc = 0;
+        int q[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float quo = round_bf16(__fdiv_rn(v[4 * w + j], divisor));
-          const int q = max(-128, min(127, __float2int_rn(quo)));
-          acc |= uint32_t(uint8_t(q)) << (8 * j);
+        for (int j = 0; j < 4; j += 2) {
+          const float x0 = v[4 * w + j], x1 = v[4 * w + j + 1];
+          const float a0 = __fmul_rn(x0, rcp), a1 = __fmul_rn(x1, rcp);
+          const float q0 = __fmaf_rn(__fmaf_rn(-a0, divisor, x0), rcp, a0);
+          const float q1 = __fmaf_rn(__fmaf_rn(-a1, divisor, x1), rcp, a1);
+          const float2 f = __bfloat1622float2(__floats2bfloat162_rn(q0, q1));  // the quotient is rounded to bf16 first
+          q[j] = __float2int_rn(f.x);
+          q[j + 1] = __float2int_rn(f.y);
         }
-        o[w] = acc;
+        // saturating pack to int8 = clamp to [-128, 127]
+        uint32_t hi, all;
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q[3]), "r"(q[2]), "r"(0));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(all) : "r"(q[1]), "r"(q[0]), "r"(hi));
+        o[w] = all;
       }
       reinterpret_cast<uint4*>(a.q + size_t(row) * a.dim)[tid] = make_uint4(o[0], o[1], o[2], o[3]);
     }

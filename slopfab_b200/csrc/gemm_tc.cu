@@ -12,7 +12,7 @@
 // Warp 0 (one lane) streams K-slabs of 128 bytes per row into a ring of shared
 // memory stages with TMA (128-byte swizzle, no multicast). Warp 1 (one lane)
 // issues tcgen05.mma from shared-memory descriptors into a TMEM accumulator;
-// a commit releases each stage back to the producer. Warps 2-5 drain a finished
+// a commit releases each stage back to the producer. Warps 2-9 drain a finished
 // accumulator with tcgen05.ld, apply the fused epilogue and store bf16, while
 // the MMA warp already fills the other accumulator buffer.
 //
@@ -38,7 +38,7 @@ using namespace ptx;
 constexpr int kBM = 128;             // rows of a tile = TMEM lanes
 constexpr int kSlabBytes = 128;      // bytes of K per row per stage (one swizzle atom)
 constexpr int kMmaKBytes = 32;       // bytes of K one tcgen05.mma consumes, every kind
-constexpr int kThreads = 192;        // producer warp, MMA warp, four epilogue warps
+constexpr int kThreads = 320;        // producer warp, MMA warp, eight epilogue warps
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s: far above any legitimate wait
 
 enum Kind { kI8 = 0, kNvfp4 = 1, kBf16 = 2 };
@@ -54,7 +54,7 @@ template <int KIND, int BN, int ACC> struct Cfg {
   static constexpr int kAccCols = BN * ACC;
   static constexpr int kSfSlotCols = KIND == kNvfp4 ? 4 * 4 + 4 * (BN / 32) : 0;  // SFA 4 cols, SFB BN/32 cols per k-block
   static constexpr int kTmemCols = 512;
-  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kBarrierBytes = 5120;  // barriers + the epilogue's column operands
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 alignment slack
   static_assert(kAccCols + 2 * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kStages >= 2, "pipeline needs at least two stages");
@@ -67,6 +67,8 @@ struct Shared {  // lives after the stage ring
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort;
+  alignas(16) float col_scale[2][256];  // per-column epilogue operands of the tile being drained
+  alignas(16) float bias[2][256];
 };
 
 // Bounded wait. Returns false when the CTA is aborting.
@@ -114,6 +116,51 @@ __device__ __forceinline__ float finish(uint32_t raw, float row_scale, float col
   return v;
 }
 
+// 32 consecutive columns of one row: scale, round to bf16, [add bias, re-round], [GELU, re-round], and four
+// 16-byte stores. `cs`/`bs` point at this chunk's column operands in shared memory (same address for every
+// lane: broadcast reads). The rounding points are those of `finish`.
+template <int KIND, bool BIAS, bool GELU>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], float rs, const float* cs, const float* bs,
+                                            __nv_bfloat16* dst, bool row_ok) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + v * 8), c1 = *reinterpret_cast<const float4*>(cs + v * 8 + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if constexpr (BIAS) {
+      const float4 b0 = *reinterpret_cast<const float4*>(bs + v * 8), b1 = *reinterpret_cast<const float4*>(bs + v * 8 + 4);
+      b[0] = b0.x, b[1] = b0.y, b[2] = b0.z, b[3] = b0.w, b[4] = b1.x, b[5] = b1.y, b[6] = b1.z, b[7] = b1.w;
+    }
+    uint4 packed;
+    __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      float lo, hi;
+      if constexpr (KIND == kI8) {
+        lo = (float(int32_t(r[v * 8 + 2 * h])) * rs) * c[2 * h];
+        hi = (float(int32_t(r[v * 8 + 2 * h + 1])) * rs) * c[2 * h + 1];
+      } else if constexpr (KIND == kNvfp4) {
+        lo = __uint_as_float(r[v * 8 + 2 * h]) * c[2 * h];
+        hi = __uint_as_float(r[v * 8 + 2 * h + 1]) * c[2 * h + 1];
+      } else {
+        lo = __uint_as_float(r[v * 8 + 2 * h]);
+        hi = __uint_as_float(r[v * 8 + 2 * h + 1]);
+      }
+      __nv_bfloat162 o = __floats2bfloat162_rn(lo, hi);  // the GEMM's own bf16 store
+      if constexpr (BIAS) {
+        const float2 f = __bfloat1622float2(o);
+        o = __floats2bfloat162_rn(f.x + b[2 * h], f.y + b[2 * h + 1]);  // add_bias re-rounds
+      }
+      if constexpr (GELU) {
+        const float2 f = __bfloat1622float2(o);
+        o = __floats2bfloat162_rn(gelu_tanh_ref(f.x), gelu_tanh_ref(f.y));
+      }
+      pp[h] = o;
+    }
+    if (row_ok) *reinterpret_cast<uint4*>(dst + v * 8) = packed;
+  }
+}
+
 template <int KIND, int BN, int ACC>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
@@ -149,7 +196,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int a = 0; a < ACC; ++a) {
       mbar_init(smem_u32(&sh->acc_full[a]), 1);
-      mbar_init(smem_u32(&sh->acc_empty[a]), 4);
+      mbar_init(smem_u32(&sh->acc_empty[a]), 8);
     }
     sh->abort = 0;
     fence_barrier_init();
@@ -173,7 +220,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       int tm, tn;
       tile_coords(t, tm, tn);
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
-        const int s = it % C::kStages;
+        const int s = it % C::kStages;  // kStages is a compile-time constant
         const uint32_t ph = (it / C::kStages) & 1;
         if (!(ok = wait_barrier(smem_u32(&sh->empty[s]), ph ^ 1, sh, g.status, 1))) break;
         uint8_t* stage = smem + s * C::kStageBytes;
@@ -213,122 +260,125 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = KIND == kI8 ? idesc_i8(kBM, BN) : (KIND == kNvfp4 ? idesc_nvfp4(kBM, BN) : idesc_bf16(kBM, BN));
-    uint32_t it = 0, tile_it = 0;
+    // The issuing thread is a single lane: every instruction between two MMAs is serial latency on the
+    // tensor pipe's critical path. So: running counters instead of divisions, descriptor low words derived
+    // by one add per stage, and a fully unrolled four-MMA body for full stages.
     bool ok = true;
+    const uint32_t a_base = smem_u32(smem) >> 4;                       // start-address fields, 16-byte units
+    const uint32_t b_base = smem_u32(smem + C::kStageA) >> 4;
+    constexpr uint32_t kStageStep = C::kStageBytes >> 4;
+    constexpr uint64_t kDescHi = (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+    const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
+    int s = 0;
+    uint32_t ph = 0, it = 0, tile_it = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
       const int a = tile_it % ACC;
-      const uint32_t aph = (tile_it / ACC) & 1;
-      if (!(ok = wait_barrier(smem_u32(&sh->acc_empty[a]), aph ^ 1, sh, g.status, 2))) break;
+      if (!(ok = wait_barrier(smem_u32(&sh->acc_empty[a]), ((tile_it / ACC) & 1) ^ 1, sh, g.status, 2))) break;
       tc_fence_after_sync();
       const uint32_t d = tmem + a * BN;
       for (int ks = 0; ks < k_stages; ++ks, ++it) {
-        const int s = it % C::kStages;
-        const uint32_t ph = (it / C::kStages) & 1;
         if (!(ok = wait_barrier(smem_u32(&sh->full[s]), ph, sh, g.status, 3))) break;
         tc_fence_after_sync();
-        uint8_t* stage = smem + s * C::kStageBytes;
-        const uint64_t da = smem_desc_sw128(smem_u32(stage));
-        const uint64_t db = smem_desc_sw128(smem_u32(stage + C::kStageA));
-        const int kb_valid = min(4, (row_bytes - ks * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
+        const uint64_t da = kDescHi | uint64_t(a_base + s * kStageStep);
+        const uint64_t db = kDescHi | uint64_t(b_base + s * kStageStep);
+        const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
         uint32_t sf_cols = 0;
         if constexpr (KIND == kNvfp4) {
-          // Scales for this stage: one 32x128b copy per (128-row tile, k-block) into the slot for this parity.
+          // Scales of this stage: one 32x128b copy per (128-row tile, k-block) into the slot of this parity.
           sf_cols = tmem + C::kAccCols + (it & 1) * C::kSfSlotCols;
-          const uint32_t sfa_s = smem_u32(stage + C::kStageA + C::kStageB);
-          const uint32_t sfb_s = sfa_s + C::kStageSfa;
-          for (int kb = 0; kb < kb_valid; ++kb) {
-            tc_copy_32x128b_x4(sf_cols + kb * 4, smem_desc_sf(sfa_s + kb * 512));
-            for (int rt = 0; rt < BN / 128; ++rt)
-              tc_copy_32x128b_x4(sf_cols + 16 + kb * (BN / 32) + rt * 4, smem_desc_sf(sfb_s + (rt * 4 + kb) * 512));
+          constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+          const uint32_t sfa = a_base + s * kStageStep + ((C::kStageA + C::kStageB) >> 4);
+          const uint32_t sfb = sfa + (C::kStageSfa >> 4);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            if (kb < kb_valid) {
+              tc_copy_32x128b_x4(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
+#pragma unroll
+              for (int rt = 0; rt < BN / 128; ++rt)
+                tc_copy_32x128b_x4(sf_cols + 16 + kb * (BN / 32) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
+            }
           }
         }
-        for (int kb = 0; kb < kb_valid; ++kb) {
-          const uint32_t acc = (ks | kb) ? 1u : 0u;
-          const uint64_t adv = uint64_t(kb * kMmaKBytes >> 4);  // start-address field is in 16-byte units
-          if constexpr (KIND == kI8)
-            mma_i8(d, da + adv, db + adv, idesc, acc);
-          else if constexpr (KIND == kBf16)
-            mma_f16(d, da + adv, db + adv, idesc, acc);
-          else
-            mma_nvfp4(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * (BN / 32));
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          if (kb < kb_valid) {
+            const uint32_t acc = (ks | kb) ? 1u : 0u;
+            const uint64_t adv = uint64_t(kb * (kMmaKBytes >> 4));
+            if constexpr (KIND == kI8)
+              mma_i8(d, da + adv, db + adv, idesc, acc);
+            else if constexpr (KIND == kBf16)
+              mma_f16(d, da + adv, db + adv, idesc, acc);
+            else
+              mma_nvfp4(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * (BN / 32));
+          }
         }
         tc_commit(smem_u32(&sh->empty[s]));  // stage is free once these MMAs have read it
+        if (++s == C::kStages) s = 0, ph ^= 1;
       }
       if (ok) tc_commit(smem_u32(&sh->acc_full[a]));
     }
   } else if (warp >= 2) {
-    // ------------------------------------------------------------ epilogue
-    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    // ------------------------------------------------------------ epilogue (8 warps)
+    // Warp w may only read TMEM lanes [32*(w%4), +32). Two warps share each lane quadrant and split the
+    // tile's columns in halves, so every scheduler holds two epilogue warps and their latencies overlap.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
     uint32_t tile_it = 0;
     bool ok = true;
     const bool vec_ok = (g.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(g.y) & 15) == 0) && (g.ldy % 8 == 0);
+    const bool has_bias = g.bias != nullptr;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
       int tm, tn;
       tile_coords(t, tm, tn);
       const int a = tile_it % ACC;
       const uint32_t aph = (tile_it / ACC) & 1;
+      // Per-column epilogue operands of this tile go to shared memory once (two buffers: the previous tile's
+      // may still be in use by a slower warp until it reaches the named barrier below).
+      float* cs_s = sh->col_scale[tile_it & 1];
+      float* bs_s = sh->bias[tile_it & 1];
+      if (et < BN) {
+        const int col = tn * BN + et;
+        float cs = g.global_scale, bs = 0.0f;
+        if (col < g.N) {
+          if constexpr (KIND == kI8) cs = __ldg(g.col_scale + col);
+          if (has_bias)
+            bs = g.bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[col])
+                                : __ldg(static_cast<const float*>(g.bias) + col);
+        }
+        cs_s[et] = cs;
+        bs_s[et] = bs;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (!(ok = wait_barrier(smem_u32(&sh->acc_full[a]), aph, sh, g.status, 4))) break;
       tc_fence_after_sync();
       const int row = tm * kBM + quad * 32 + lane;
       const bool row_ok = row < g.M;
-      const float rs = (KIND == kI8 && row_ok) ? g.row_scale[row] : 1.0f;
+      const float rs = (KIND == kI8 && row_ok) ? __ldg(g.row_scale + row) : 1.0f;
       __nv_bfloat16* yrow = g.y + size_t(row_ok ? row : 0) * g.ldy;
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + a * BN + c * 32 + (uint32_t(quad * 32) << 16), r);
+      constexpr int kChunks = BN / 64;  // 32-column chunks per warp
+      const uint32_t tbase = tmem + a * BN + half * (BN / 2) + (uint32_t(quad * 32) << 16);
+      uint32_t r[2][32];
+      tmem_ld_32x32(tbase, r[0]);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
         tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
+        if (c + 1 < kChunks) tmem_ld_32x32(tbase + (c + 1) * 32, r[(c + 1) & 1]);  // overlaps the math below
+        const int lc0 = half * (BN / 2) + c * 32;  // column inside the tile
+        const int col0 = tn * BN + lc0;
         if (col0 >= g.N) continue;  // warp-uniform
         if (vec_ok && col0 + 32 <= g.N) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            float cs[8], bs[8];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              float4 c4 = make_float4(g.global_scale, g.global_scale, g.global_scale, g.global_scale);
-              if constexpr (KIND == kI8) c4 = __ldg(reinterpret_cast<const float4*>(g.col_scale + col0 + v * 8 + h * 4));
-              cs[h * 4 + 0] = c4.x, cs[h * 4 + 1] = c4.y, cs[h * 4 + 2] = c4.z, cs[h * 4 + 3] = c4.w;
-            }
-            if (g.bias != nullptr) {
-              if (g.bias_is_bf16) {
-                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.bias) + col0 + v * 8));
-                const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b4);
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                  const float2 f = __bfloat1622float2(bp[h]);
-                  bs[2 * h] = f.x, bs[2 * h + 1] = f.y;
-                }
-              } else {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  const float4 b4 = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(g.bias) + col0 + v * 8 + h * 4));
-                  bs[h * 4 + 0] = b4.x, bs[h * 4 + 1] = b4.y, bs[h * 4 + 2] = b4.z, bs[h * 4 + 3] = b4.w;
-                }
-              }
-            } else {
-#pragma unroll
-              for (int h = 0; h < 8; ++h) bs[h] = 0.0f;
-            }
-            uint4 packed;
-            __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const float lo = finish<KIND>(r[v * 8 + 2 * h], rs, cs[2 * h], bs[2 * h], g.bias != nullptr, g.act);
-              const float hi = finish<KIND>(r[v * 8 + 2 * h + 1], rs, cs[2 * h + 1], bs[2 * h + 1], g.bias != nullptr, g.act);
-              pp[h] = __floats2bfloat162_rn(lo, hi);
-            }
-            if (row_ok) *reinterpret_cast<uint4*>(yrow + col0 + v * 8) = packed;
-          }
+          if (!has_bias && g.act == SFQ_ACT_NONE)
+            store_chunk<KIND, false, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, yrow + col0, row_ok);
+          else if (g.act == SFQ_ACT_NONE)
+            store_chunk<KIND, true, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, yrow + col0, row_ok);
+          else
+            store_chunk<KIND, true, true>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, yrow + col0, row_ok);
         } else {
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
             if (col >= g.N) break;
-            const float cs = KIND == kI8 ? g.col_scale[col] : g.global_scale;
-            float b = 0.0f;
-            if (g.bias != nullptr)
-              b = g.bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[col])
-                                 : static_cast<const float*>(g.bias)[col];
-            const float v = finish<KIND>(r[j], rs, cs, b, g.bias != nullptr, g.act);
+            const float v = finish<KIND>(r[c & 1][j], rs, cs_s[lc0 + j], bs_s[lc0 + j], has_bias, g.act);
             if (row_ok) yrow[col] = __float2bfloat16(v);
           }
         }
@@ -428,10 +478,12 @@ void gemm_nvfp4(const uint8_t* a, const uint8_t* w, const GemmArgs& g, cudaStrea
     throw std::invalid_argument("sfq gemm nvfp4: needs K % 64 == 0 and N % 128 == 0 (the scale tiling has no padded form)");
   if (!a || !w || !g.a_scale_tiled || !g.w_scale_tiled || !g.y || !g.status)
     throw std::invalid_argument("sfq gemm nvfp4: null operand");
-  if (g.tile_n == 128)
-    launch<kNvfp4, 128, 2>(a, w, size_t(g.K) / 2, g, stream);
-  else
+  // 128-wide tiles leave TMEM room for two accumulators, so the epilogue overlaps the next main loop; a
+  // 256-wide tile has one accumulator (256 columns + the scale slots) and is kept for comparison.
+  if (g.tile_n == 256)
     launch<kNvfp4, 256, 1>(a, w, size_t(g.K) / 2, g, stream);
+  else
+    launch<kNvfp4, 128, 2>(a, w, size_t(g.K) / 2, g, stream);
 }
 
 void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream) {

@@ -29,7 +29,8 @@ struct GemmArgs {
   int* status = nullptr;  // device word; a kernel that gives up waiting stores a non-zero code
   int band_m = 0;         // row tiles per raster band (0 = default)
   int max_ctas = 0;       // 0 = one CTA per SM
-  int tile_n = 0;         // 128 or 256 (0 = default 256)
+  int tile_n = 0;         // 128 or 256 (0 = default)
+  int debug = 0;          // experiment switches (environment SFQ_GEMM_DEBUG); 0 in normal use
 };
 
 // All three throw std::invalid_argument / std::runtime_error before launching on a contract violation.

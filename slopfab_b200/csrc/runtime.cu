@@ -1,5 +1,6 @@
 #include "runtime.h"
 
+#include <cstdlib>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -61,6 +62,11 @@ void apply_tuning(GemmArgs& g) {
   g.tile_n = g_tile_n;
   g.band_m = g_band_m;
   g.max_ctas = g_max_ctas;
+  static const int debug = [] {
+    const char* e = std::getenv("SFQ_GEMM_DEBUG");
+    return e ? std::atoi(e) : 0;
+  }();
+  g.debug = debug;
 }
 
 }  // namespace sfq
