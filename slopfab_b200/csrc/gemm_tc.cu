@@ -38,7 +38,7 @@ using namespace ptx;
 constexpr int kBM = 128;             // rows of a tile = TMEM lanes
 constexpr int kSlabBytes = 128;      // bytes of K per row per stage (one swizzle atom)
 constexpr int kMmaKBytes = 32;       // bytes of K one tcgen05.mma consumes, every kind
-constexpr int kThreads = 320;        // producer warp, MMA warp, eight epilogue warps
+constexpr int kThreads = 384;        // producer warp, MMA warp, eight epilogue warps, two scale-copy warps (nvfp4)
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s: far above any legitimate wait
 
 enum Kind { kI8 = 0, kNvfp4 = 1, kBf16 = 2 };
@@ -50,12 +50,14 @@ template <int KIND, int BN, int ACC> struct Cfg {
   static constexpr int kStageSfa = KIND == kNvfp4 ? 4 * 512 : 0;
   static constexpr int kStageSfb = KIND == kNvfp4 ? (BN / 128) * 4 * 512 : 0;
   static constexpr int kStageBytes = kStageA + kStageB + kStageSfa + kStageSfb;
-  static constexpr int kStages = (220 * 1024) / kStageBytes > 8 ? 8 : (220 * 1024) / kStageBytes;
+  static constexpr int kBarrierBytes = 5120;   // barriers + the epilogue's column operands
+  static constexpr int kStagingBytes = 8 * 2048;  // one 32x32 bf16 transpose block per epilogue warp
+  static constexpr int kRingBudget = 227 * 1024 - 1024 - kBarrierBytes - kStagingBytes;
+  static constexpr int kStages = kRingBudget / kStageBytes > 8 ? 8 : kRingBudget / kStageBytes;
   static constexpr int kAccCols = BN * ACC;
   static constexpr int kSfSlotCols = KIND == kNvfp4 ? 4 * 4 + 4 * (BN / 32) : 0;  // SFA 4 cols, SFB BN/32 cols per k-block
   static constexpr int kTmemCols = 512;
-  static constexpr int kBarrierBytes = 5120;  // barriers + the epilogue's column operands
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;  // +1024 alignment slack
   static_assert(kAccCols + 2 * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kStages >= 2, "pipeline needs at least two stages");
 };
@@ -65,6 +67,8 @@ struct Shared {  // lives after the stage ring
   uint64_t empty[8];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t sf_full[2];   // nvfp4: scale factors of a stage are in TMEM slot (stage & 1)
+  uint64_t sf_empty[2];  // nvfp4: the MMAs that read that slot have completed
   uint32_t tmem_base;
   volatile int abort;
   alignas(16) float col_scale[2][256];  // per-column epilogue operands of the tile being drained
@@ -116,12 +120,17 @@ __device__ __forceinline__ float finish(uint32_t raw, float row_scale, float col
   return v;
 }
 
-// 32 consecutive columns of one row: scale, round to bf16, [add bias, re-round], [GELU, re-round], and four
-// 16-byte stores. `cs`/`bs` point at this chunk's column operands in shared memory (same address for every
-// lane: broadcast reads). The rounding points are those of `finish`.
+// One warp's 32 rows x 32 columns: scale, round to bf16, [add bias, re-round], [GELU, re-round], then a
+// transpose through a 2 KB shared-memory block so that every store instruction writes 64 contiguous bytes of
+// 8 rows (a thread owns a ROW in TMEM; storing straight from registers would scatter each instruction over 32
+// rows). `cs`/`bs` point at this chunk's column operands in shared memory (broadcast reads). The 16-byte
+// units of a staged row are XOR-swizzled with the row index so both phases are bank-conflict free.
+// `dst` is the global address of (first row of this warp, first column of the chunk); `rows_ok` is how many
+// of the warp's 32 rows exist.
 template <int KIND, bool BIAS, bool GELU>
 __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], float rs, const float* cs, const float* bs,
-                                            __nv_bfloat16* dst, bool row_ok) {
+                                            uint4* stage, __nv_bfloat16* dst, size_t ldy, int rows_ok, int lane,
+                                            bool skip_store) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     const float4 c0 = *reinterpret_cast<const float4*>(cs + v * 8), c1 = *reinterpret_cast<const float4*>(cs + v * 8 + 4);
@@ -157,8 +166,18 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], float rs, c
       }
       pp[h] = o;
     }
-    if (row_ok) *reinterpret_cast<uint4*>(dst + v * 8) = packed;
+    stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = packed;  // row `lane`, 16-byte unit v
   }
+  __syncwarp();
+  if (!skip_store) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = 8 * i + (lane >> 2), unit = lane & 3;
+      const uint4 val = stage[row * 4 + (unit ^ ((row >> 1) & 3))];
+      if (row < rows_ok) *reinterpret_cast<uint4*>(dst + size_t(row) * ldy + unit * 8) = val;
+    }
+  }
+  __syncwarp();  // the block is reused by the next chunk
 }
 
 template <int KIND, int BN, int ACC>
@@ -197,6 +216,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int a = 0; a < ACC; ++a) {
       mbar_init(smem_u32(&sh->acc_full[a]), 1);
       mbar_init(smem_u32(&sh->acc_empty[a]), 8);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh->sf_full[i]), 2);
+      mbar_init(smem_u32(&sh->sf_empty[i]), 1);
     }
     sh->abort = 0;
     fence_barrier_init();
@@ -284,20 +307,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
         uint32_t sf_cols = 0;
         if constexpr (KIND == kNvfp4) {
-          // Scales of this stage: one 32x128b copy per (128-row tile, k-block) into the slot of this parity.
+          // The scale-copy warps filled TMEM slot (it & 1) for this stage. A single lane issues one tcgen05
+          // instruction every ~45 cycles, so the 12 copies of a stage cannot share a thread with its 4 MMAs.
           sf_cols = tmem + C::kAccCols + (it & 1) * C::kSfSlotCols;
-          constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
-          const uint32_t sfa = a_base + s * kStageStep + ((C::kStageA + C::kStageB) >> 4);
-          const uint32_t sfb = sfa + (C::kStageSfa >> 4);
-#pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (kb < kb_valid) {
-              tc_copy_32x128b_x4(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
-#pragma unroll
-              for (int rt = 0; rt < BN / 128; ++rt)
-                tc_copy_32x128b_x4(sf_cols + 16 + kb * (BN / 32) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
-            }
-          }
+          if (!(ok = wait_barrier(smem_u32(&sh->sf_full[it & 1]), (it >> 1) & 1, sh, g.status, 5))) break;
+          tc_fence_after_sync();
         }
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
@@ -313,9 +327,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
         tc_commit(smem_u32(&sh->empty[s]));  // stage is free once these MMAs have read it
+        if constexpr (KIND == kNvfp4) tc_commit(smem_u32(&sh->sf_empty[it & 1]));
         if (++s == C::kStages) s = 0, ph ^= 1;
       }
       if (ok) tc_commit(smem_u32(&sh->acc_full[a]));
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------ scale-factor copies (nvfp4 only)
+    // Warp 10 handles k-blocks 0,1 of every stage, warp 11 k-blocks 2,3: shared memory -> TMEM with one
+    // 32x128b copy per (128-row tile, k-block), then a commit that arrives on sf_full when they have landed.
+    if constexpr (KIND == kNvfp4) {
+      if (lane == 0) {
+        const int part = warp - 10;
+        constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+        constexpr uint32_t kStageStep = C::kStageBytes >> 4;
+        const uint32_t sfa0 = (smem_u32(smem) + C::kStageA + C::kStageB) >> 4;
+        const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
+        int s = 0;
+        uint32_t ph = 0, it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+          for (int ks = 0; ks < k_stages; ++ks, ++it) {
+            if (!(ok = wait_barrier(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
+            if (!(ok = wait_barrier(smem_u32(&sh->sf_empty[it & 1]), ((it >> 1) & 1) ^ 1, sh, g.status, 7))) break;
+            tc_fence_after_sync();
+            const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
+            const uint32_t sf_cols = tmem + C::kAccCols + (it & 1) * C::kSfSlotCols;
+            const uint32_t sfa = sfa0 + s * kStageStep;
+            const uint32_t sfb = sfa + (C::kStageSfa >> 4);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int kb = part * 2 + j;
+              if (kb < kb_valid) {
+                tc_copy_32x128b_x4(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
+#pragma unroll
+                for (int rt = 0; rt < BN / 128; ++rt)
+                  tc_copy_32x128b_x4(sf_cols + 16 + kb * (BN / 32) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
+              }
+            }
+            tc_commit(smem_u32(&sh->sf_full[it & 1]));
+            if (++s == C::kStages) s = 0, ph ^= 1;
+          }
+        }
+      }
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue (8 warps)
@@ -356,6 +410,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const bool row_ok = row < g.M;
       const float rs = (KIND == kI8 && row_ok) ? __ldg(g.row_scale + row) : 1.0f;
       __nv_bfloat16* yrow = g.y + size_t(row_ok ? row : 0) * g.ldy;
+      const int warp_row0 = tm * kBM + quad * 32;
+      const int rows_ok = max(0, min(32, g.M - warp_row0));
+      __nv_bfloat16* ywarp = g.y + size_t(min(warp_row0, g.M - 1)) * g.ldy;
+      uint4* stage_w = reinterpret_cast<uint4*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes) + (warp - 2) * 128;
       constexpr int kChunks = BN / 64;  // 32-column chunks per warp
       const uint32_t tbase = tmem + a * BN + half * (BN / 2) + (uint32_t(quad * 32) << 16);
       uint32_t r[2][32];
@@ -367,13 +425,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int lc0 = half * (BN / 2) + c * 32;  // column inside the tile
         const int col0 = tn * BN + lc0;
         if (col0 >= g.N) continue;  // warp-uniform
+        if (g.debug & 8) continue;  // experiment: drain only
         if (vec_ok && col0 + 32 <= g.N) {
           if (!has_bias && g.act == SFQ_ACT_NONE)
-            store_chunk<KIND, false, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, yrow + col0, row_ok);
+            store_chunk<KIND, false, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, (g.debug & 4) != 0);
           else if (g.act == SFQ_ACT_NONE)
-            store_chunk<KIND, true, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, yrow + col0, row_ok);
+            store_chunk<KIND, true, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, false);
           else
-            store_chunk<KIND, true, true>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, yrow + col0, row_ok);
+            store_chunk<KIND, true, true>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, false);
         } else {
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
@@ -478,12 +537,12 @@ void gemm_nvfp4(const uint8_t* a, const uint8_t* w, const GemmArgs& g, cudaStrea
     throw std::invalid_argument("sfq gemm nvfp4: needs K % 64 == 0 and N % 128 == 0 (the scale tiling has no padded form)");
   if (!a || !w || !g.a_scale_tiled || !g.w_scale_tiled || !g.y || !g.status)
     throw std::invalid_argument("sfq gemm nvfp4: null operand");
-  // 128-wide tiles leave TMEM room for two accumulators, so the epilogue overlaps the next main loop; a
-  // 256-wide tile has one accumulator (256 columns + the scale slots) and is kept for comparison.
-  if (g.tile_n == 256)
-    launch<kNvfp4, 256, 1>(a, w, size_t(g.K) / 2, g, stream);
-  else
+  // A 256-wide tile has one accumulator (256 columns + the scale slots); 128-wide tiles have two but feed the
+  // tensor pipe less efficiently and measured slower at every DiT shape.
+  if (g.tile_n == 128)
     launch<kNvfp4, 128, 2>(a, w, size_t(g.K) / 2, g, stream);
+  else
+    launch<kNvfp4, 256, 1>(a, w, size_t(g.K) / 2, g, stream);
 }
 
 void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream) {
