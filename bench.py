@@ -337,7 +337,7 @@ def extra_measurements(torch, np, sfq, peaks):
         fn4 = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
                                                          C.byref(ep4), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
         reps = 20 if m <= 4096 else 5
-        for tile_n in (256, 128):
+        for tile_n in (256,):
             sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
             for kind, f, mult in (("int8", fn, 2), ("nvfp4", fn4, 4)):
                 for i in range(2):

@@ -98,39 +98,17 @@ __device__ __forceinline__ float gelu_tanh_ref(float v) {
   return 0.5f * v * (1.0f + tanhf(k * (v + 0.044715f * v * v * v)));
 }
 
-__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
+// Rounding points of the epilogue, as in the reference: the GEMM result is rounded to bf16 (output_bf16 /
+// the GEMM's own store), the bias is added to that bf16 value and re-rounded (add_bias_kernel,
+// src/cuda/linear_weights.cu:483-491), and GELU runs in place on the bf16 result.
 
-// One output element, with the reference's rounding points: the GEMM result is
-// rounded to bf16 (output_bf16 / the GEMM's own store), the bias is added to
-// that bf16 value and re-rounded (add_bias_kernel, src/cuda/linear_weights.cu:483-491),
-// and GELU runs in place on the bf16 result.
-template <int KIND>
-__device__ __forceinline__ float finish(uint32_t raw, float row_scale, float col_scale, float bias, bool has_bias,
-                                        int act) {
-  float v;
-  if constexpr (KIND == kI8)
-    v = (float(int32_t(raw)) * row_scale) * col_scale;  // output_bf16, src/cuda/w4a8.cu:218-223
-  else if constexpr (KIND == kNvfp4)
-    v = __uint_as_float(raw) * col_scale;  // global scale once, src/cuda/nvfp4_gemm.cu:480-481
-  else
-    v = __uint_as_float(raw);
-  v = bf16_round(v);
-  if (has_bias) v = bf16_round(v + bias);
-  if (act == SFQ_ACT_GELU_TANH) v = bf16_round(gelu_tanh_ref(v));
-  return v;
-}
-
-// One warp's 32 rows x 32 columns: scale, round to bf16, [add bias, re-round], [GELU, re-round], then a
-// transpose through a 2 KB shared-memory block so that every store instruction writes 64 contiguous bytes of
-// 8 rows (a thread owns a ROW in TMEM; storing straight from registers would scatter each instruction over 32
-// rows). `cs`/`bs` point at this chunk's column operands in shared memory (broadcast reads). The 16-byte
-// units of a staged row are XOR-swizzled with the row index so both phases are bank-conflict free.
-// `dst` is the global address of (first row of this warp, first column of the chunk); `rows_ok` is how many
-// of the warp's 32 rows exist.
+// Epilogue arithmetic for 32 consecutive columns of one row (a thread owns a ROW in TMEM): scale, round to
+// bf16, [add bias, re-round], [GELU, re-round]; the result stays in registers as four 16-byte units.
+// `cs`/`bs` point at this chunk's column operands in shared memory (broadcast reads). The rounding points
+// are those of `finish`.
 template <int KIND, bool BIAS, bool GELU>
-__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], float rs, const float* cs, const float* bs,
-                                            uint4* stage, __nv_bfloat16* dst, size_t ldy, int rows_ok, int lane,
-                                            bool skip_store) {
+__device__ __forceinline__ void pack_chunk(const uint32_t (&r)[32], float rs, const float* cs, const float* bs,
+                                           uint4 (&out)[4]) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     const float4 c0 = *reinterpret_cast<const float4*>(cs + v * 8), c1 = *reinterpret_cast<const float4*>(cs + v * 8 + 4);
@@ -140,8 +118,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], float rs, c
       const float4 b0 = *reinterpret_cast<const float4*>(bs + v * 8), b1 = *reinterpret_cast<const float4*>(bs + v * 8 + 4);
       b[0] = b0.x, b[1] = b0.y, b[2] = b0.z, b[3] = b0.w, b[4] = b1.x, b[5] = b1.y, b[6] = b1.z, b[7] = b1.w;
     }
-    uint4 packed;
-    __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&packed);
+    __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&out[v]);
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
       float lo, hi;
@@ -166,16 +143,23 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], float rs, c
       }
       pp[h] = o;
     }
-    stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = packed;  // row `lane`, 16-byte unit v
   }
-  __syncwarp();
-  if (!skip_store) {
+}
+
+// Writes one warp's 32 rows x 32 bf16 columns. Storing straight from registers would scatter every store
+// instruction over 32 rows, so the block goes through a 2 KB shared-memory transpose (16-byte units
+// XOR-swizzled with the row, both phases bank-conflict free) and each instruction then writes 64 contiguous
+// bytes of 8 rows. `dst` = global address of (first row of the warp, first column of the chunk).
+__device__ __forceinline__ void flush_chunk(const uint4 (&packed)[4], uint4* stage, __nv_bfloat16* dst, size_t ldy,
+                                            int rows_ok, int lane) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = 8 * i + (lane >> 2), unit = lane & 3;
-      const uint4 val = stage[row * 4 + (unit ^ ((row >> 1) & 3))];
-      if (row < rows_ok) *reinterpret_cast<uint4*>(dst + size_t(row) * ldy + unit * 8) = val;
-    }
+  for (int v = 0; v < 4; ++v) stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = packed[v];
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), unit = lane & 3;
+    const uint4 val = stage[row * 4 + (unit ^ ((row >> 1) & 3))];
+    if (row < rows_ok) *reinterpret_cast<uint4*>(dst + size_t(row) * ldy + unit * 8) = val;
   }
   __syncwarp();  // the block is reused by the next chunk
 }
@@ -373,8 +357,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue (8 warps)
-    // Warp w may only read TMEM lanes [32*(w%4), +32). Two warps share each lane quadrant and split the
-    // tile's columns in halves, so every scheduler holds two epilogue warps and their latencies overlap.
+    // Warp w may only read TMEM lanes [32*(w%4), +32). Two warps share each lane quadrant and take alternate
+    // 32-column chunks, so every scheduler holds two epilogue warps and their latencies overlap.
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
@@ -414,37 +398,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const int rows_ok = max(0, min(32, g.M - warp_row0));
       __nv_bfloat16* ywarp = g.y + size_t(min(warp_row0, g.M - 1)) * g.ldy;
       uint4* stage_w = reinterpret_cast<uint4*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes) + (warp - 2) * 128;
-      constexpr int kChunks = BN / 64;  // 32-column chunks per warp
-      const uint32_t tbase = tmem + a * BN + half * (BN / 2) + (uint32_t(quad * 32) << 16);
+      // This warp takes the 32-column chunks half, half+2, ... of the tile. Phase 1 drains them from TMEM and
+      // does the arithmetic, keeping packed bf16 in registers; the accumulator is then handed back to the MMA
+      // warp BEFORE phase 2 writes to global memory, so stores never sit on the tensor pipe's critical path.
+      constexpr int kTileChunks = BN / 32;
+      constexpr int kMaxJ = (kTileChunks + 1) / 2;
+      const uint32_t tbase = tmem + a * BN + (uint32_t(quad * 32) << 16);
       uint32_t r[2][32];
-      tmem_ld_32x32(tbase, r[0]);
+      uint4 packed[kMaxJ][4];
+      if (half < kTileChunks) tmem_ld_32x32(tbase + half * 32, r[0]);
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        tmem_ld_wait();
-        if (c + 1 < kChunks) tmem_ld_32x32(tbase + (c + 1) * 32, r[(c + 1) & 1]);  // overlaps the math below
-        const int lc0 = half * (BN / 2) + c * 32;  // column inside the tile
-        const int col0 = tn * BN + lc0;
-        if (col0 >= g.N) continue;  // warp-uniform
-        if (g.debug & 8) continue;  // experiment: drain only
-        if (vec_ok && col0 + 32 <= g.N) {
+      for (int j = 0; j < kMaxJ; ++j) {
+        const int c = half + 2 * j;
+        if (c < kTileChunks) {
+          tmem_ld_wait();
+          if (j + 1 < kMaxJ && c + 2 < kTileChunks) tmem_ld_32x32(tbase + (c + 2) * 32, r[(j + 1) & 1]);  // overlaps the math
+          const int lc0 = c * 32;
           if (!has_bias && g.act == SFQ_ACT_NONE)
-            store_chunk<KIND, false, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, (g.debug & 4) != 0);
+            pack_chunk<KIND, false, false>(r[j & 1], rs, cs_s + lc0, bs_s + lc0, packed[j]);
           else if (g.act == SFQ_ACT_NONE)
-            store_chunk<KIND, true, false>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, false);
+            pack_chunk<KIND, true, false>(r[j & 1], rs, cs_s + lc0, bs_s + lc0, packed[j]);
           else
-            store_chunk<KIND, true, true>(r[c & 1], rs, cs_s + lc0, bs_s + lc0, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, false);
-        } else {
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            if (col >= g.N) break;
-            const float v = finish<KIND>(r[c & 1][j], rs, cs_s[lc0 + j], bs_s[lc0 + j], has_bias, g.act);
-            if (row_ok) yrow[col] = __float2bfloat16(v);
-          }
+            pack_chunk<KIND, true, true>(r[j & 1], rs, cs_s + lc0, bs_s + lc0, packed[j]);
         }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[a]));
+#pragma unroll
+      for (int j = 0; j < kMaxJ; ++j) {
+        const int c = half + 2 * j;
+        const int col0 = tn * BN + c * 32;
+        if (c >= kTileChunks || col0 >= g.N) continue;  // warp-uniform
+        if (vec_ok && col0 + 32 <= g.N) {
+          flush_chunk(packed[j], stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane);
+        } else if (row_ok) {  // ragged N or unaligned output: element stores from this thread's own row
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t w4[4] = {packed[j][v].x, packed[j][v].y, packed[j][v].z, packed[j][v].w};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int col = col0 + v * 8 + q;
+              if (col < g.N) yrow[col] = __ushort_as_bfloat16((unsigned short)((w4[q >> 1] >> (16 * (q & 1))) & 0xFFFFu));
+            }
+          }
+        }
+      }
     }
   }
 
@@ -525,6 +524,8 @@ void gemm_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t
   if (g.K <= 0 || g.K % 16 != 0) throw std::invalid_argument("sfq gemm int8: K must be a positive multiple of 16");
   if (!a || !w || !g.row_scale || !g.col_scale || !g.y || !g.status)
     throw std::invalid_argument("sfq gemm int8: null operand");
+  // 256-wide tiles measured fastest at every DiT shape, small M included (192- and 160-wide tiles fill the
+  // last wave better but feed the tensor pipe worse); 128 stays selectable for experiments.
   if (g.tile_n == 128)
     launch<kI8, 128, 2>(a, w, size_t(g.K), g, stream);
   else
