@@ -23,6 +23,7 @@
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <stdexcept>
 #include <string>
 
@@ -119,9 +120,10 @@ __device__ __forceinline__ void two_stages(float (&v)[16]) {
 
 __device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16(f)); }
 
+// One token row. `r0`, `r1` are this thread's 16 bf16 elements, already loaded (zero for an inactive thread).
+// A thread may return early only where no block-wide barrier follows in this function.
 template <int MODE>
-__global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
+__device__ __forceinline__ void process_row(const FusedArgs& a, const int row, uint4 r0, uint4 r1, uint8_t* smem) {
   // [tile: 17 floats per thread][partials: 256 + 8 + 8 floats][raw row: dim bf16 when the norm is on]
   float* tile = reinterpret_cast<float*>(smem);
   float* partial = tile + size_t(blockDim.x) * 17;
@@ -129,7 +131,6 @@ __global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
   float* bcast = warp_tot + 8;
   uint4* raw = reinterpret_cast<uint4*>(bcast + 8);
 
-  const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int chunks = a.dim >> 4;
@@ -144,12 +145,6 @@ __global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
 
   float v[16];
   {
-    uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
-    if (active) {
-      const uint4* src = reinterpret_cast<const uint4*>(a.x + size_t(row) * a.dim) + tid * 2;
-      r0 = __ldg(src);
-      r1 = __ldg(src + 1);
-    }
     const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
     const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
 #pragma unroll
@@ -347,6 +342,36 @@ __global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
   }
 }
 
+// The kernel: a CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and loads the NEXT row's 32 bytes per
+// thread before working on the current one, so every resident warp always has a load in flight (one row per
+// CTA without prefetch keeps too few bytes in flight to cover HBM latency).
+template <int MODE>
+__global__ void __launch_bounds__(1024, 1) fused_act_kernel(FusedArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int chunks = a.dim >> 4;
+  const bool active = int(threadIdx.x) < chunks;
+  const int total_rows = MODE == kModeFp4Feed ? (a.rows + 127) / 128 * 128 : a.rows;
+  auto load = [&](int row, uint4& r0, uint4& r1) {
+    r0 = make_uint4(0, 0, 0, 0);
+    r1 = r0;
+    if (active && row < a.rows) {
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + size_t(row) * a.dim) + threadIdx.x * 2;
+      r0 = __ldg(src);
+      r1 = __ldg(src + 1);
+    }
+  };
+  uint4 r0, r1, n0, n1;
+  int row = blockIdx.x;
+  load(row, r0, r1);
+  for (; row < total_rows; row += gridDim.x) {
+    load(row + gridDim.x, n0, n1);
+    process_row<MODE>(a, row, r0, r1, smem);
+    __syncthreads();  // shared memory is reused by the next row
+    r0 = n0;
+    r1 = n1;
+  }
+}
+
 // Generic rotation for the other power-of-four groups (4, 16, 64): not on the hot path (the INT8
 // weight-only format of the text encoder); one block of 64 threads per 256 columns.
 __global__ void __launch_bounds__(64)
@@ -396,7 +421,15 @@ template <int MODE> void launch_fused(const FusedArgs& a, int grid_rows, cudaStr
     if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
     reserved = smem;
   }
-  fused_act_kernel<MODE><<<grid_rows, threads, smem, stream>>>(a);
+  // As many CTAs as stay resident at once; each walks rows with a stride of the grid size.
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_act_kernel<MODE>, threads, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = std::min(grid_rows, per_sm * sms);
+  fused_act_kernel<MODE><<<grid, threads, smem, stream>>>(a);
   check_launch(what);
 }
 
