@@ -406,8 +406,47 @@ def run_case(name):
                       "device_status": sfq.device_status()}))
 
 
+def run_block_stack(blocks=40, rows=75600, hidden=5120, heads=40, ffn=13824):
+    """BASELINE config 4: NVFP4 DiT block stack, random init, 21x45x80 = 75600 tokens. Reports the Linear-path
+    milliseconds (norm+quant, GEMMs, gated residuals) and the whole-block milliseconds; attention is torch SDPA."""
+    import torch
+
+    from slopfab_b200.block import BlockWeights, Nvfp4Block, Nvfp4Linear
+    import slopfab_b200 as sfq
+
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((rows, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    names = ["scale_msa", "shift_msa", "gate_msa", "scale_mlp", "shift_mlp", "gate_mlp"]
+    mod = {n: 0.1 * torch.randn((3, hidden), device="cuda", generator=g) for n in names}
+    index = torch.zeros(rows, dtype=torch.int32, device="cuda")  # all video rows: tag 0 of timestep 0
+    ones = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    ws = [BlockWeights(Nvfp4Linear.random(3 * hidden, hidden, seed=4 * b), Nvfp4Linear.random(hidden, hidden, seed=4 * b + 1),
+                       Nvfp4Linear.random(ffn, hidden, seed=4 * b + 2), Nvfp4Linear.random(hidden, ffn, seed=4 * b + 3),
+                       ones, ones) for b in range(blocks)]
+    blk = Nvfp4Block(rows, hidden, heads, ffn)
+    blk.forward(x.clone(), ws[0], mod, index)  # warm-up
+    torch.cuda.synchronize()
+    blk.linear_ms = 0.0
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for w in ws:
+        blk.forward(x, w, mod, index, time_linears=True)
+    b.record()
+    b.synchronize()
+    total = a.elapsed_time(b)
+    flops_linear = 2.0 * rows * hidden * (3 * hidden + hidden + 2 * ffn)
+    print(json.dumps({"case": "config4_block_stack", "blocks": blocks, "tokens": rows, "block_ms": total / blocks,
+                      "linear_path_ms_per_block": blk.linear_ms / blocks,
+                      "linear_path_tflops": flops_linear / (blk.linear_ms / blocks * 1e-3) / 1e12,
+                      "attention": "torch.nn.functional.scaled_dot_product_attention (library, bf16)",
+                      "finite": bool(torch.isfinite(x.float()).all().item()), "device_status": sfq.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--block-stack", type=int, default=0, metavar="BLOCKS",
+                    help="run BASELINE config 4 (NVFP4 DiT block stack at 75600 tokens) with this many blocks and exit")
     ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu) and exit: gemm_int8, "
                     "gemm_nvfp4, quantize_int8, quantize_nvfp4")
     ap.add_argument("--gpus", type=int, default=1)
@@ -418,6 +457,9 @@ def main():
     args = ap.parse_args()
     if args.case:
         run_case(args.case)
+        return
+    if args.block_stack:
+        run_block_stack(args.block_stack)
         return
     if args.impl == "reference":
         run_reference(args)
