@@ -70,3 +70,36 @@ def column_split_int8_forward(quantize, gemm, x_local: torch.Tensor, group=None)
     q_all = gathered[:, :k].contiguous()
     s_all = gathered[:, k:].contiguous().view(torch.float32).view(-1)
     return gemm(q_all, s_all)
+
+
+def column_split_w4a8_forward(x_local: torch.Tensor, w8_cols: torch.Tensor, col_scale: torch.Tensor,
+                              bias: torch.Tensor | None = None, activation: int = 0, group=None) -> torch.Tensor:
+    """FFN-up column split on GPUs, W4A8/W6A8 flavour.
+
+    x_local  bf16 [m_local, K]   this rank's token rows
+    w8_cols  int8 [n_local, K]   this rank's output columns of the expanded weight (sfq_unpack_w4a8_int8 / w6a8)
+    col_scale fp32 [n_local], bias fp32 [n_local] or None
+    Returns bf16 [M_total, n_local]: this rank's columns for ALL tokens. One NCCL all-gather (of the int8
+    activation with its row scales appended) is the only collective; the GEMM reads local memory only.
+    """
+    import ctypes as C
+
+    from . import F32, Epilogue, check, lib, ptr, stream_ptr
+
+    m, k = x_local.shape
+    n = w8_cols.shape[0]
+
+    def quantize(x):
+        q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+        s = torch.empty(m, dtype=torch.float32, device=x.device)
+        check(lib.sfq_quantize_int8_token(ptr(x), None, ptr(q), ptr(s), None, m, k, 1, stream_ptr()))
+        return q, s
+
+    def gemm(q_all, s_all):
+        rows = q_all.shape[0]
+        y = torch.empty((rows, n), dtype=torch.bfloat16, device=q_all.device)
+        ep = Epilogue(ptr(s_all), ptr(col_scale), 1.0, ptr(bias), F32, activation)
+        check(lib.sfq_gemm_int8(ptr(q_all), ptr(w8_cols), C.byref(ep), ptr(y), rows, n, k, stream_ptr()))
+        return y
+
+    return column_split_int8_forward(quantize, gemm, x_local.contiguous(), group)

@@ -173,3 +173,47 @@ def test_runner_error_contract():
     wf8 = sfq.new_weight(format=sfq.F8E4M3, data=sfq.ptr(x), out_features=4, in_features=256)
     with pytest.raises(sfq.SfqError):
         runner.forward(wf8, x)
+
+
+@pytest.mark.parametrize("group", [256, 64, 0])
+def test_int8_weight_only_arm(group):
+    # linear_int8_convrot (tests/test_nn_kernels_linear_synthetic.cu:609-709): INT8 per-channel weight, online
+    # ConvRot of the activation, dequantize + bf16 GEMM; 2e-3 abs / 2e-2 rel against the fp64 product.
+    import ctypes as C
+    M, N, K = 70, 256, 512
+    rng = np.random.default_rng(31 + group)
+    wf = (0.05 * rng.standard_normal((N, K))).astype(np.float32)
+    codes = np.zeros((N, K), np.int8)
+    scale = np.zeros(N, np.float32)
+    P = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+    sfq.check(sfq.lib.sfq_pack_int8(P(wf), N, K, group, P(codes), P(scale)))
+    bias = oracle.to_bf16((0.01 * rng.standard_normal(N)).astype(np.float32))
+    xb = gaussian_bf16((M, K), seed=32)
+    keep = [dev(codes), dev(scale), bf16_tensor(bias)]
+    w = sfq.new_weight(format=sfq.I8, data=sfq.ptr(keep[0]), out_features=N, in_features=K, weight_scale=sfq.ptr(keep[1]),
+                       per_channel_scale=1, convrot=1 if group else 0, convrot_group=group or 256, bias=sfq.ptr(keep[2]),
+                       bias_format=sfq.BF16)
+    y = sfq.LinearRunner().forward(w, bf16_tensor(xb))
+    assert sfq.device_status() == 0
+    wdq = np.empty((N, K), np.uint16)
+    oracle.lib.orc_int8_dequant_bf16(P(codes), P(scale), N, K, P(wdq))
+    xr = oracle.convrot_bf16(xb, group) if group else xb
+    want = oracle.from_bf16(xr).astype(np.float64) @ oracle.from_bf16(wdq).astype(np.float64).T + oracle.from_bf16(bias)
+    got = oracle.from_bf16(bits(y))
+    assert np.all(np.abs(got - want) <= 2e-3 + 2e-2 * np.abs(want))
+    # and it really is the rotated product: without rotating x the result is far away (x H W^T is noise)
+    if group:
+        wrong = oracle.from_bf16(xb).astype(np.float64) @ oracle.from_bf16(wdq).astype(np.float64).T
+        assert np.sqrt(((got - wrong) ** 2).sum() / (wrong ** 2).sum()) > 0.5
+
+
+def test_bf16_weight_arm():
+    M, N, K = 65, 384, 520
+    x = gaussian_bf16((M, K), seed=40)
+    wb = gaussian_bf16((N, K), seed=41, sigma=0.05)
+    keep = [bf16_tensor(wb)]
+    w = sfq.new_weight(format=sfq.BF16, data=sfq.ptr(keep[0]), out_features=N, in_features=K)
+    y = sfq.LinearRunner().forward(w, bf16_tensor(x))
+    want = oracle.from_bf16(x).astype(np.float64) @ oracle.from_bf16(wb).astype(np.float64).T
+    got = oracle.from_bf16(bits(y))
+    assert np.all(np.abs(got - want) <= 1e-3 + 1e-2 * np.abs(want))

@@ -1,0 +1,74 @@
+"""Two-GPU runs of the multi-GPU variants (skipped on a single GPU): token sharding and the FFN-up column
+split with its single NCCL all-gather must reproduce the one-GPU result bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import oracle
+    import slopfab_b200 as sfq
+    from helpers import bf16_tensor, dev, gaussian_bf16, synthetic_packed_int8
+    from slopfab_b200.parallel import column_shard, column_split_w4a8_forward, token_shard
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        M, N, K = 1000, 1536, 1024  # ragged token split, column blocks of 768
+        packed, s_rel, s_ch, book = synthetic_packed_int8(4, 16, N, K, seed=5)
+        bias = (0.01 * np.random.default_rng(6).standard_normal(N)).astype(np.float32)
+        x = gaussian_bf16((M, K), seed=7, outliers=True)
+        keep = [dev(packed), dev(s_rel), dev(s_ch), dev(book), dev(bias)]
+        w = sfq.new_weight(format=sfq.W4A8, data=sfq.ptr(keep[0]), out_features=N, in_features=K, block_scale=sfq.ptr(keep[1]),
+                           weight_scale=sfq.ptr(keep[2]), w4_codebook=sfq.ptr(keep[3]), packed_group_size=16, convrot=1,
+                           convrot_group=256, bias=sfq.ptr(keep[4]))
+        full = sfq.LinearRunner().forward(w, bf16_tensor(x))          # what one GPU computes
+        r0, rc = token_shard(M, world, rank)
+        c0, cc = column_shard(N, world, rank)
+        w8 = torch.empty((N, K), dtype=torch.int8, device="cuda")
+        sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(keep[0]), sfq.ptr(keep[1]), sfq.ptr(keep[3]), sfq.ptr(w8), N, K, 16,
+                                               sfq.stream_ptr()))
+        y_cols = column_split_w4a8_forward(bf16_tensor(np.ascontiguousarray(x[r0:r0 + rc])), w8[c0:c0 + cc].contiguous(),
+                                           keep[2][c0:c0 + cc].contiguous(), keep[4][c0:c0 + cc].contiguous())
+        torch.cuda.synchronize()
+        ok = torch.equal(y_cols.view(torch.int16), full[:, c0:c0 + cc].contiguous().view(torch.int16))
+        # token sharding: this rank's rows through the ordinary runner equal the same rows of the full result
+        mine = sfq.LinearRunner().forward(w, bf16_tensor(np.ascontiguousarray(x[r0:r0 + rc])))
+        ok = ok and torch.equal(mine.view(torch.int16), full[r0:r0 + rc].view(torch.int16))
+        ok = ok and sfq.device_status() == 0
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            out.put(bool(flag.item()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_column_split_and_token_sharding_on_two_gpus():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    assert out.get(timeout=5) is True
