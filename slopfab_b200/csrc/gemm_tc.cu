@@ -58,7 +58,8 @@ template <int KIND, int BN, int ACC> struct Cfg {
   static constexpr int kSfSlotCols = KIND == kNvfp4 ? 4 * 4 + 4 * (BN / 32) : 0;  // SFA 4 cols, SFB BN/32 cols per k-block
   static constexpr int kTmemCols = 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;  // +1024 alignment slack
-  static_assert(kAccCols + 2 * kSfSlotCols <= 512, "TMEM budget");
+  static constexpr int kSfSlots = 4;  // scale slots in flight: copies of stage it+3 may run while stage it multiplies
+  static_assert(kAccCols + kSfSlots * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kStages >= 2, "pipeline needs at least two stages");
 };
 
@@ -67,8 +68,8 @@ struct Shared {  // lives after the stage ring
   uint64_t empty[8];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t sf_full[2];   // nvfp4: scale factors of a stage are in TMEM slot (stage & 1)
-  uint64_t sf_empty[2];  // nvfp4: the MMAs that read that slot have completed
+  uint64_t sf_full[4];   // nvfp4: scale factors of a stage are in TMEM slot (stage % 4)
+  uint64_t sf_empty[4];  // nvfp4: the MMAs that read that slot have completed
   uint32_t tmem_base;
   volatile int abort;
   alignas(16) float col_scale[2][256];  // per-column epilogue operands of the tile being drained
@@ -201,7 +202,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       mbar_init(smem_u32(&sh->acc_full[a]), 1);
       mbar_init(smem_u32(&sh->acc_empty[a]), 8);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&sh->sf_full[i]), 2);
       mbar_init(smem_u32(&sh->sf_empty[i]), 1);
     }
@@ -293,8 +294,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if constexpr (KIND == kNvfp4) {
           // The scale-copy warps filled TMEM slot (it & 1) for this stage. A single lane issues one tcgen05
           // instruction every ~45 cycles, so the 12 copies of a stage cannot share a thread with its 4 MMAs.
-          sf_cols = tmem + C::kAccCols + (it & 1) * C::kSfSlotCols;
-          if (!(ok = wait_barrier(smem_u32(&sh->sf_full[it & 1]), (it >> 1) & 1, sh, g.status, 5))) break;
+          sf_cols = tmem + C::kAccCols + (it & 3) * C::kSfSlotCols;
+          if (!(ok = wait_barrier(smem_u32(&sh->sf_full[it & 3]), (it >> 2) & 1, sh, g.status, 5))) break;
           tc_fence_after_sync();
         }
 #pragma unroll
@@ -311,7 +312,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
         tc_commit(smem_u32(&sh->empty[s]));  // stage is free once these MMAs have read it
-        if constexpr (KIND == kNvfp4) tc_commit(smem_u32(&sh->sf_empty[it & 1]));
+        if constexpr (KIND == kNvfp4) tc_commit(smem_u32(&sh->sf_empty[it & 3]));
         if (++s == C::kStages) s = 0, ph ^= 1;
       }
       if (ok) tc_commit(smem_u32(&sh->acc_full[a]));
@@ -333,10 +334,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
           for (int ks = 0; ks < k_stages; ++ks, ++it) {
             if (!(ok = wait_barrier(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
-            if (!(ok = wait_barrier(smem_u32(&sh->sf_empty[it & 1]), ((it >> 1) & 1) ^ 1, sh, g.status, 7))) break;
+            if (!(ok = wait_barrier(smem_u32(&sh->sf_empty[it & 3]), ((it >> 2) & 1) ^ 1, sh, g.status, 7))) break;
             tc_fence_after_sync();
             const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
-            const uint32_t sf_cols = tmem + C::kAccCols + (it & 1) * C::kSfSlotCols;
+            const uint32_t sf_cols = tmem + C::kAccCols + (it & 3) * C::kSfSlotCols;
             const uint32_t sfa = sfa0 + s * kStageStep;
             const uint32_t sfb = sfa + (C::kStageSfa >> 4);
 #pragma unroll
@@ -349,7 +350,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                   tc_copy_32x128b_x4(sf_cols + 16 + kb * (BN / 32) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
               }
             }
-            tc_commit(smem_u32(&sh->sf_full[it & 1]));
+            tc_commit(smem_u32(&sh->sf_full[it & 3]));
             if (++s == C::kStages) s = 0, ph ^= 1;
           }
         }
