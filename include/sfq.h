@@ -259,6 +259,19 @@ SFQ_API int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w
                                         const void* d_x_bf16, int rows, void* d_y_bf16, void* d_workspace,
                                         size_t workspace_bytes);
 
+/* ---- caller side: row -> adaLN table index ------------------------------------- */
+
+/* build_indices + build_row_timesteps (include/slopfab/dit/packing.h:81-176, src/dit/packing.cpp:213-248,407-489)
+ * reduced to what the norm kernel consumes. Rows are [text | condition video | condition audio | audio | video];
+ * outputs have num_text + num_condition_video + num_condition_audio + num_audio_rows + num_video_rows entries:
+ * h_tags (video 0, text 1, audio 2), h_indices (position of the row's timestep in the ascending unique set),
+ * h_adaln = index * 3 + tag (the d_adaln_index of sfq_norm), h_unique2 (up to two values), *h_num_unique.
+ * Any output except h_adaln may be null. Host only. */
+SFQ_API int sfq_build_adaln_index(int num_text, int num_condition_video, int num_condition_audio,
+                                  int condition_audio_is_explicit, int num_audio_rows, int num_video_rows,
+                                  float video_t, float audio_t, int32_t* h_tags, int32_t* h_indices,
+                                  int32_t* h_adaln, float* h_unique2, int* h_num_unique);
+
 /* ---- for callers that cannot allocate ------------------------------------------ */
 
 /* Bytes of scratch built into the library image for sfq_linear_nvfp4_forward_static (16 MiB, plus a

@@ -125,3 +125,47 @@ def test_device_entry_points_fail_loudly_without_a_gpu():
     assert b"CUDA" in sfq.lib.sfq_last_error() or b"device" in sfq.lib.sfq_last_error()
     ep = sfq.Epilogue()
     assert sfq.lib.sfq_gemm_int8(1, 1, C.byref(ep), 1, 128, 128, 256, None) != sfq.OK
+
+
+def _adaln(L, C_, Ca, explicit, Sa, V, vt, at):
+    total = L + C_ + Ca + Sa + V
+    tags, idx, ada = (np.zeros(total, np.int32) for _ in range(3))
+    uniq = np.zeros(2, np.float32)
+    n = C.c_int(0)
+    sfq.check(sfq.lib.sfq_build_adaln_index(L, C_, Ca, explicit, Sa, V, vt, at, P(tags), P(idx), P(ada), P(uniq), C.byref(n)))
+    return tags, idx, ada, uniq[:n.value]
+
+
+def test_adaln_index_known_answers():
+    # packing_row_timesteps (tests/test_packing.cpp:416-466) on the reference t2va layout: 4 text rows,
+    # no conditioning, audio rows then video rows
+    L, Sa, V = 4, 500, 2000
+    audio_start, video_start = L, L + Sa
+    tags, idx, ada, uniq = _adaln(L, 0, 0, 0, Sa, V, 0.25, 0.75)
+    assert list(uniq) == [0.25, 0.75]
+    assert (idx[0], idx[audio_start], idx[video_start]) == (0, 1, 0)
+    assert (ada[0], ada[audio_start], ada[video_start]) == (0 * 3 + 1, 1 * 3 + 2, 0 * 3 + 0)
+    tags, idx, ada, uniq = _adaln(L, 0, 0, 0, Sa, V, 0.75, 0.25)   # schedules crossed: index 0 flips
+    assert uniq[0] == np.float32(0.25) and idx[0] == 1 and idx[audio_start] == 0
+    assert (ada[0], ada[audio_start]) == (1 * 3 + 1, 0 * 3 + 2)
+    tags, idx, ada, uniq = _adaln(L, 0, 0, 0, Sa, V, 0.5, 0.5)     # equal timesteps collapse
+    assert len(uniq) == 1 and (ada[0], ada[audio_start], ada[video_start]) == (1, 2, 0)
+    tags, idx, ada, uniq = _adaln(L, 0, 0, 0, Sa, V, 0.9, 0.1)
+    assert ada.min() >= 0 and ada.max() < 6
+    # against numpy's unique over the per-row timestep vector, several layouts incl. conditioning prefixes
+    rng = np.random.default_rng(3)
+    for L, C_, Ca, explicit, Sa, V in ((3, 0, 0, 0, 10, 7), (5, 6, 0, 0, 12, 9), (2, 4, 3, 1, 8, 5), (0, 0, 0, 0, 0, 11),
+                                       (1, 0, 0, 0, 6, 0), (2, 9, 0, 0, 4, 3)):
+        for vt, at in ((0.3, 0.6), (0.6, 0.3), (0.4, 0.4)):
+            tags, idx, ada, uniq = _adaln(L, C_, Ca, explicit, Sa, V, vt, at)
+            a0 = L + C_ + Ca
+            row_t = np.full(a0 + Sa + V, vt, np.float32)
+            prefix = min(Ca if explicit else C_, Sa)
+            row_t[a0 + prefix:a0 + Sa] = at
+            want_u, want_i = np.unique(row_t, return_inverse=True)
+            want_tag = np.ones_like(idx)
+            want_tag[L:a0] = 0
+            want_tag[a0:a0 + Sa] = 2
+            want_tag[a0 + Sa:] = 0
+            assert np.array_equal(uniq, want_u) and np.array_equal(idx, want_i) and np.array_equal(tags, want_tag)
+            assert np.array_equal(ada, want_i * 3 + want_tag)
