@@ -367,7 +367,7 @@ def extra_measurements(torch, np, sfq, peaks):
         fn4 = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
                                                          C.byref(ep4), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
         reps = 20 if m <= 4096 else 5
-        for tile_n in (256,):
+        for tile_n in (0, 256):  # 0 = default (CTA pairs on 256x256 tiles), 256 = one CTA per 128x256 tile
             sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
             for kind, f, mult in (("int8", fn, 2), ("nvfp4", fn4, 4)):
                 for i in range(2):
@@ -375,7 +375,7 @@ def extra_measurements(torch, np, sfq, peaks):
                 torch.cuda.synchronize()
                 ms = time_region(torch, f, reps) / reps
                 tf = 2.0 * m * n * k / ms / 1e9
-                out[f"{kind}_{name}_bn{tile_n}"] = {"ms": round(ms, 4), "tflops": round(tf, 1),
+                out[f"{kind}_{name}_{'pair' if tile_n == 0 else 'bn%d' % tile_n}"] = {"ms": round(ms, 4), "tflops": round(tf, 1),
                                                     f"frac_of_{mult}x_bf16": round(tf / (mult * peaks["bf16_tflops"]), 3)}
         sfq.lib.sfq_gemm_tuning(0, 0, 0)
         del a8, w8, aq, wq, asf, wsf, y

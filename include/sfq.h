@@ -171,6 +171,20 @@ SFQ_API int sfq_unpack_w6a8_int8(const int8_t* d_packed, const uint8_t* d_group_
 /* launch_dequant_i8_per_channel, include/slopfab/cuda/linear.cuh:264-265 (bit-exact). */
 SFQ_API int sfq_unpack_int8_bf16(const int8_t* d_codes, const float* d_scale, void* d_out_bf16,
                                  int out_features, int in_features, void* stream);
+/* launch_dequant_f8e4m3, include/slopfab/cuda/linear.cuh:259-260: bf16(e4m3(v) * *d_scale), one device
+ * scalar scale (bit-exact). */
+SFQ_API int sfq_unpack_f8e4m3_bf16(const uint8_t* d_codes, const float* d_scale, void* d_out_bf16, size_t n,
+                                   void* stream);
+/* launch_dequant_nf4, include/slopfab/cuda/linear.cuh:293-296: bitsandbytes NF4 with double-quantized
+ * block scales, high nibble = even element (bit-exact). */
+SFQ_API int sfq_unpack_nf4_bf16(const uint8_t* d_packed, const uint8_t* d_absmax, const float* d_quant_map,
+                                const float* d_nested_quant_map, const float* d_nested_absmax, int block_size,
+                                int nested_block_size, float nested_offset, void* d_out_bf16, int out_features,
+                                int in_features, void* stream);
+/* launch_pre_quant_scale, include/slopfab/cuda/linear.cuh:305-306: the AWQ activation pre-scale
+ * dst[r, i] = bf16(src[r, i] * scale[i]) (bit-exact). */
+SFQ_API int sfq_pre_quant_scale(const void* d_src_bf16, const void* d_scale_bf16, void* d_dst_bf16, int rows, int dim,
+                                void* stream);
 /* F16Weight::materialize for INT8 ConvRot weights (src/cuda/nf4_weight.cu:20-51; host twin
  * unpack_int8_weight, src/core/int8_weight.cpp:66-100): inverse rotation into fp16 (bit-exact). */
 SFQ_API int sfq_unpack_int8_f16(const int8_t* d_codes, const float* d_scale, void* d_out_f16, int out_features,

@@ -157,6 +157,12 @@ private:
 void launch_convrot(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int dim, int group, cudaStream_t stream);
 void launch_dequant_i8_per_channel(const int8_t* src, const float* scale, __nv_bfloat16* dst, int out_features,
                                    int in_features, cudaStream_t stream);
+void launch_dequant_f8e4m3(const uint8_t* src, const float* scale, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
+void launch_dequant_nf4(const uint8_t* src, const uint8_t* absmax, const float* quant_map, const float* nested_quant_map,
+                        const float* nested_absmax, int block_size, int nested_block_size, float nested_offset,
+                        __nv_bfloat16* dst, int out_features, int in_features, cudaStream_t stream);
+void launch_pre_quant_scale(const __nv_bfloat16* src, const __nv_bfloat16* scale, __nv_bfloat16* dst, int rows, int dim,
+                            cudaStream_t stream);
 void launch_dequant_nvfp4(const uint8_t* src, const uint8_t* block_scale, float global_scale, __nv_bfloat16* dst,
                           int out_features, int in_features, cudaStream_t stream);
 void launch_dequant_w6a8_weight(const int8_t* packed, const uint8_t* group_scale, int8_t* output, int out_features,

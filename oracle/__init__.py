@@ -74,6 +74,10 @@ _sig(lib.orc_w4a8_decode, None, V, V, V, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_w6a8_decode, None, V, V, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_int8_dequant_bf16, None, V, V, C.c_int, C.c_int, V)
 _sig(lib.orc_int8_unpack_f16, None, V, V, C.c_int, C.c_int, C.c_int, C.c_int, V)
+_sig(lib.orc_f8_dequant_bf16, None, V, C.c_float, C.c_size_t, V)
+_sig(lib.orc_nf4_dequant_bf16, None, V, V, V, V, V, C.c_int, C.c_int, C.c_float, C.c_size_t, V)
+_sig(lib.orc_f16_to_bf16_n, None, V, V, C.c_size_t)
+_sig(lib.orc_pre_quant_scale_bf16, None, V, V, C.c_int, C.c_int, V)
 _sig(lib.orc_convrot_bf16, None, V, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_convrot_dense_f32, None, V, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_quantize_int8_token, None, V, C.c_int, C.c_int, V, V)

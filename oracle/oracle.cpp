@@ -496,6 +496,39 @@ ORC_API void orc_int8_unpack_f16(const int8_t* codes, const float* scales, int r
     }
 }
 
+// src/cuda/linear_weights.cu:150-162: bf16(f8_e4m3(v) * scale), one fp32 scale for the tensor.
+ORC_API void orc_f8_dequant_bf16(const uint8_t* src, float scale, size_t n, uint16_t* out) {
+  for (size_t i = 0; i < n; ++i) out[i] = f32_to_bf16(e4m3_to_f32(src[i]) * scale);
+}
+
+// src/cuda/linear_weights.cu:273-315: bitsandbytes NF4 with double-quantized block scales. High nibble is
+// the even element; scale(block) = nested_map[absmax[block]] * nested_absmax[block / nested_block] + offset;
+// value = map[code] * scale, rounded to bf16.
+ORC_API void orc_nf4_dequant_bf16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                                  const float* nested_absmax, int block, int nested_block, float offset, size_t n,
+                                  uint16_t* out) {
+  for (size_t i = 0; i < n; ++i) {
+    const size_t b = i / size_t(block);
+    // the device compiler contracts this multiply-add into one fused operation
+    const float scale = std::fmaf(nested_map[absmax[b]], nested_absmax[b / size_t(nested_block)], offset);
+    const uint8_t byte = src[i / 2];
+    const int code = (i % 2 == 0) ? (byte >> 4) : (byte & 15);
+    out[i] = f32_to_bf16(map[code] * scale);
+  }
+}
+
+// src/cuda/linear_weights.cu:366-384: f16 -> bf16 through fp32.
+ORC_API void orc_f16_to_bf16_n(const uint16_t* in, uint16_t* out, size_t n) {
+  for (size_t i = 0; i < n; ++i) out[i] = f32_to_bf16(f16_to_f32(in[i]));
+}
+
+// src/cuda/linear_weights.cu:499-509: AWQ activation pre-scale, dst[r, i] = bf16(src[r, i] * scale[i]).
+ORC_API void orc_pre_quant_scale_bf16(const uint16_t* x, const uint16_t* scale, int rows, int dim, uint16_t* out) {
+  for (int r = 0; r < rows; ++r)
+    for (int i = 0; i < dim; ++i)
+      out[size_t(r) * dim + i] = f32_to_bf16(bf16_to_f32(x[size_t(r) * dim + i]) * bf16_to_f32(scale[i]));
+}
+
 // ===========================================================================
 // ConvRot, int8 activation quantizer, integer GEMM, epilogues
 // ===========================================================================

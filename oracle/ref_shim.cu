@@ -147,6 +147,28 @@ REF_API int ref_dev_dequant_nvfp4(const uint8_t* src, const uint8_t* scale, floa
     sync();
   });
 }
+REF_API int ref_dev_dequant_f8(const uint8_t* src, const float* scale, void* dst, size_t n) {
+  return guarded([&] {
+    sc::launch_dequant_f8e4m3(src, scale, static_cast<bf16*>(dst), n, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_dequant_nf4(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                                const float* nested_absmax, int block, int nested_block, float offset, void* dst,
+                                int out_features, int in_features) {
+  return guarded([&] {
+    sc::launch_dequant_nf4(src, absmax, map, nested_map, nested_absmax, block, nested_block, offset,
+                           static_cast<bf16*>(dst), out_features, in_features, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_pre_quant_scale(const void* src, const void* scale, void* dst, int rows, int dim) {
+  return guarded([&] {
+    sc::launch_pre_quant_scale(static_cast<const bf16*>(src), static_cast<const bf16*>(scale), static_cast<bf16*>(dst),
+                               rows, dim, nullptr);
+    sync();
+  });
+}
 REF_API int ref_dev_dequant_i8(const int8_t* src, const float* scale, void* dst, int out_features,
                                int in_features) {
   return guarded([&] {
@@ -247,6 +269,13 @@ struct RefWeight {  // plain mirror of the fields the path uses
   int convrot, convrot_group;
   const void* bias;
   int bias_format;
+  const void* pre_quant_scale;
+  const uint8_t* nf4_absmax;
+  const float* nf4_quant_map;
+  const float* nf4_nested_quant_map;
+  const float* nf4_nested_absmax;
+  int nf4_block_size, nf4_nested_block_size;
+  float nf4_nested_offset;
 };
 
 namespace {
@@ -266,6 +295,14 @@ sc::QuantWeight to_weight(const RefWeight& r) {
   w.convrot_group = r.convrot_group;
   w.bias = r.bias;
   w.bias_format = static_cast<sc::QuantFormat>(r.bias_format);
+  w.pre_quant_scale = static_cast<const bf16*>(r.pre_quant_scale);
+  w.nf4_absmax = r.nf4_absmax;
+  w.nf4_quant_map = r.nf4_quant_map;
+  w.nf4_nested_quant_map = r.nf4_nested_quant_map;
+  w.nf4_nested_absmax = r.nf4_nested_absmax;
+  if (r.nf4_block_size > 0) w.nf4_block_size = r.nf4_block_size;
+  if (r.nf4_nested_block_size > 0) w.nf4_nested_block_size = r.nf4_nested_block_size;
+  w.nf4_nested_offset = r.nf4_nested_offset;
   return w;
 }
 

@@ -190,6 +190,26 @@ int sfq_unpack_int8_bf16(const int8_t* d_codes, const float* d_scale, void* d_ou
     sfq::unpack_int8_bf16(d_codes, d_scale, static_cast<bf16*>(d_out_bf16), out_features, in_features, as_stream(stream));
   });
 }
+int sfq_unpack_f8e4m3_bf16(const uint8_t* d_codes, const float* d_scale, void* d_out_bf16, size_t n, void* stream) {
+  return guarded([&] { sfq::unpack_f8e4m3_bf16(d_codes, d_scale, static_cast<bf16*>(d_out_bf16), n, as_stream(stream)); });
+}
+int sfq_unpack_nf4_bf16(const uint8_t* d_packed, const uint8_t* d_absmax, const float* d_quant_map,
+                        const float* d_nested_quant_map, const float* d_nested_absmax, int block_size,
+                        int nested_block_size, float nested_offset, void* d_out_bf16, int out_features, int in_features,
+                        void* stream) {
+  return guarded([&] {
+    sfq::unpack_nf4_bf16(d_packed, d_absmax, d_quant_map, d_nested_quant_map, d_nested_absmax, block_size,
+                         nested_block_size, nested_offset, static_cast<bf16*>(d_out_bf16), out_features, in_features,
+                         as_stream(stream));
+  });
+}
+int sfq_pre_quant_scale(const void* d_src_bf16, const void* d_scale_bf16, void* d_dst_bf16, int rows, int dim,
+                        void* stream) {
+  return guarded([&] {
+    sfq::pre_quant_scale(static_cast<const bf16*>(d_src_bf16), static_cast<const bf16*>(d_scale_bf16),
+                         static_cast<bf16*>(d_dst_bf16), rows, dim, as_stream(stream));
+  });
+}
 int sfq_unpack_int8_f16(const int8_t* d_codes, const float* d_scale, void* d_out_f16, int out_features,
                         int in_features, int rotation_group, int canonicalize_subnormals, void* stream) {
   return guarded([&] {

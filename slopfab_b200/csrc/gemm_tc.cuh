@@ -29,7 +29,7 @@ struct GemmArgs {
   int* status = nullptr;  // device word; a kernel that gives up waiting stores a non-zero code
   int band_m = 0;         // row tiles per raster band (0 = default)
   int max_ctas = 0;       // 0 = one CTA per SM
-  int tile_n = 0;         // 128 or 256 (0 = default)
+  int tile_n = 0;         // 128 or 256 select the one-CTA kernel with that tile width; 0 = default (CTA pairs, 256 x 256)
   int debug = 0;          // experiment switches (environment SFQ_GEMM_DEBUG); 0 in normal use
 };
 
@@ -37,5 +37,11 @@ struct GemmArgs {
 void gemm_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t stream);
 void gemm_nvfp4(const uint8_t* a_packed, const uint8_t* w_packed, const GemmArgs& g, cudaStream_t stream);
 void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream);
+
+// CTA-pair kernels (gemm_tc2.cu), called by the three entry points above when the shape allows. They return false
+// without launching when the device cannot co-schedule clusters of two.
+bool gemm_pair_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t stream);
+bool gemm_pair_nvfp4(const uint8_t* a_packed, const uint8_t* w_packed, const GemmArgs& g, cudaStream_t stream);
+bool gemm_pair_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream);
 
 }  // namespace sfq

@@ -1,0 +1,404 @@
+// CTA-pair form of the tcgen05 GEMMs (see gemm_tc.cu for the one-CTA form and the operand kinds).
+//
+// Two CTAs of a cluster share one 256 x 256 output tile: tcgen05.mma.cta_group::2 with M = 256. Each CTA
+// streams ITS 128 rows of the activation and ITS 128 of the 256 weight rows of the tile (32 KB per 128-byte
+// K-slab instead of 48 KB), and receives 128 x 256 of the result in its own TMEM. Per SM that is a third less
+// shared-memory fill and L2 traffic for the same tensor work, and the smaller stages make the ring six deep
+// (five for nvfp4) instead of four (three), which is what hides the load latency at K-slab granularity.
+//
+// Division of labour inside a pair:
+//   both CTAs    warp 0 loads its own operand halves with TMA (no multicast); the bytes of BOTH CTAs are counted
+//                on the leader's `full` barrier. Warps 4-11 drain the CTA's own accumulator and store its rows.
+//   leader only  warp 1 issues the MMAs for the pair; its commits arrive on `empty` / `acc_full` in both CTAs.
+//                Warps 12-15 (nvfp4) copy block scales into TMEM in both CTAs (each from its own shared memory).
+//   the peer's epilogue hands the accumulator back by arriving on the LEADER's acc_empty barrier.
+// Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before TMEM is freed, so
+// neither exits while its partner can still read its shared memory or signal its barriers.
+#include "gemm_common.cuh"
+
+namespace sfq {
+namespace {
+
+constexpr int kPairBN = 256;
+constexpr int kPairBM = 256;  // rows of a pair's tile, 128 per CTA
+
+template <int KIND, int ACC> struct PairCfg {
+  static constexpr int kStageA = kBM * kSlabBytes;            // this CTA's 128 activation rows
+  static constexpr int kStageB = (kPairBN / 2) * kSlabBytes;  // this CTA's 128 of the tile's 256 weight rows
+  static constexpr int kStageSfa = KIND == kNvfp4 ? 4 * 512 : 0;      // scales of this CTA's rows, 4 k-blocks
+  static constexpr int kStageSfb = KIND == kNvfp4 ? 2 * 4 * 512 : 0;  // scales of ALL 256 weight rows
+  static constexpr int kStageBytes = kStageA + kStageB + kStageSfa + kStageSfb;
+  static constexpr int kBarrierBytes = 5120;
+  static constexpr int kStagingBytes = 8 * 2048;
+  static constexpr int kRingBudget = 227 * 1024 - 1024 - kBarrierBytes - kStagingBytes;
+  static constexpr int kStages = kRingBudget / kStageBytes > 8 ? 8 : kRingBudget / kStageBytes;
+  static constexpr int kAccCols = kPairBN * ACC;
+  static constexpr int kSfSlotCols = KIND == kNvfp4 ? 4 * 4 + 4 * (kPairBN / 32) : 0;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;
+  static constexpr uint32_t kTxBytes = 2u * kStageBytes;  // what both CTAs land per stage (TMA counts whole boxes)
+  static_assert(kAccCols + kStages * kSfSlotCols <= 512, "TMEM budget");
+  static_assert(kStageBytes % 1024 == 0, "stage bases must keep the 1024-byte swizzle alignment");
+  static_assert(sizeof(Shared) <= kBarrierBytes, "barrier block");
+};
+
+template <int KIND, int ACC>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, GemmArgs g) {
+  using C = PairCfg<KIND, ACC>;
+  constexpr int BN = kPairBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Shared* sh = reinterpret_cast<Shared*>(smem + C::kStages * C::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int tiles_m = (g.M + kPairBM - 1) / kPairBM;
+  const int tiles_n = (g.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int row_bytes = KIND == kNvfp4 ? g.K / 2 : (KIND == kBf16 ? g.K * 2 : g.K);
+  const int k_stages = (row_bytes + kSlabBytes - 1) / kSlabBytes;
+  const int band = g.band_m > 0 ? (g.band_m + 1) / 2 : 8;  // pair tiles (256 rows) per raster band
+
+  auto tile_coords = [&](int t, int& tm, int& tn) {
+    const int per_band = band * tiles_n;
+    const int b = t / per_band;
+    const int r = t - b * per_band;
+    const int rows_in_band = min(band, tiles_m - b * band);
+    tn = r / rows_in_band;
+    tm = b * band + (r - tn * rows_in_band);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), 1);     // used in the leader: its producer's arrive + both CTAs' bytes
+      mbar_init(smem_u32(&sh->empty[s]), 1);    // in each CTA: the pair's MMAs of that stage are done
+      mbar_init(smem_u32(&sh->sf_full[s]), 4);  // leader: the four scale-copy warps
+    }
+    for (int a = 0; a < ACC; ++a) {
+      mbar_init(smem_u32(&sh->acc_full[a]), 1);    // in each CTA
+      mbar_init(smem_u32(&sh->acc_empty[a]), 16);  // leader: eight epilogue warps of each CTA
+    }
+    sh->abort = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&sh->tmem_base), C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem = sh->tmem_base;
+
+  if (warp < 4) {
+    reg_dec<kRegsLean>();
+    if (warp == 0) {
+      // ------------------------------------------------------------ producer (both CTAs)
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int tm, tn;
+        tile_coords(t, tm, tn);
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!(ok = wait_barrier_warp(smem_u32(&sh->empty[s]), ph ^ 1, sh, g.status, 1))) break;
+          if (elect_one()) {
+            uint8_t* stage = smem + s * C::kStageBytes;
+            const uint32_t bar = smem_u32(&sh->full[s]);  // the loads redirect it to the leader's copy
+            if (rank == 0) mbar_arrive_expect_tx(bar, C::kTxBytes);
+            tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
+            tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * BN + int(rank) * (BN / 2), bar);
+            if constexpr (KIND == kNvfp4) {
+              // scale arrays as [128-row tile][K/64 atoms of 512 bytes], 8-byte elements: 256 elements = 4 atoms
+              tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB), &map_sfa, ks * 256, tm * 2 + int(rank), bar);
+              tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
+            }
+          }
+          __syncwarp();
+        }
+      }
+      if (!ok) {
+        // Aborting: this CTA's loads in flight are counted on the leader's barriers, so it cannot poll for them;
+        // give them far more time than a load takes before the shared memory may be released.
+        const long long start = clock_now();
+        while (clock_now() - start < 4000000ll) {
+        }
+      }
+    } else if (warp == 1 && rank == 0) {
+      // ------------------------------------------------------------ MMA issuer (leader)
+      constexpr uint32_t idesc = KIND == kI8 ? idesc_i8(kPairBM, BN) : (KIND == kNvfp4 ? idesc_nvfp4(kPairBM, BN) : idesc_bf16(kPairBM, BN));
+      bool ok = true;
+      const uint32_t a_base = (smem_u32(smem) & 0x3FFFFu) >> 4;  // descriptor address fields: offset in the CTA's window
+      const uint32_t b_base = (smem_u32(smem + C::kStageA) & 0x3FFFFu) >> 4;
+      constexpr uint32_t kStageStep = C::kStageBytes >> 4;
+      constexpr uint64_t kDescHi = (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+      const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
+      int s = 0;
+      uint32_t ph = 0, tile_it = 0;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_it) {
+        const int a = tile_it % ACC;
+        if (!(ok = wait_barrier_warp(smem_u32(&sh->acc_empty[a]), ((tile_it / ACC) & 1) ^ 1, sh, g.status, 2))) break;
+        tc_fence_after_sync();
+        const uint32_t d = tmem + a * BN;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if constexpr (KIND == kNvfp4) {
+            if (!(ok = wait_barrier_warp(smem_u32(&sh->sf_full[s]), ph, sh, g.status, 5))) break;
+            tc_fence_after_sync();
+          } else {
+            if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 3))) break;
+          }
+          const uint64_t da = kDescHi | uint64_t(a_base + s * kStageStep);
+          const uint64_t db = kDescHi | uint64_t(b_base + s * kStageStep);
+          const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
+          const uint32_t sf_cols = tmem + C::kAccCols + s * C::kSfSlotCols;
+          if (elect_one()) {
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+              if (kb < kb_valid) {
+                const uint32_t acc = (ks | kb) ? 1u : 0u;
+                const uint64_t adv = uint64_t(kb * (kMmaKBytes >> 4));
+                if constexpr (KIND == kI8)
+                  mma_i8_pair(d, da + adv, db + adv, idesc, acc);
+                else if constexpr (KIND == kBf16)
+                  mma_f16_pair(d, da + adv, db + adv, idesc, acc);
+                else
+                  mma_nvfp4_pair(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * (BN / 32));
+              }
+            }
+            tc_commit_pair(smem_u32(&sh->empty[s]), 3);  // frees the stage (and its scale slot) in both CTAs
+            if (ks == k_stages - 1) tc_commit_pair(smem_u32(&sh->acc_full[a]), 3);
+          }
+          __syncwarp();
+          if (++s == C::kStages) s = 0, ph ^= 1;
+        }
+      }
+    }
+  } else if (warp >= 12) {
+    reg_dec<kRegsLean>();
+    // ------------------------------------------------------------ scale-factor copies (nvfp4, leader)
+    if constexpr (KIND == kNvfp4) {
+      if (rank == 0) {
+        const int kb = warp - 12;
+        constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+        constexpr uint32_t kStageStep = C::kStageBytes >> 4;
+        const uint32_t sfa0 = ((smem_u32(smem) & 0x3FFFFu) + C::kStageA + C::kStageB) >> 4;
+        const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+          for (int ks = 0; ks < k_stages; ++ks) {
+            if (!(ok = wait_barrier_warp(smem_u32(&sh->empty[s]), ph ^ 1, sh, g.status, 7))) break;
+            if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
+            tc_fence_after_sync();
+            const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
+            const uint32_t sf_cols = tmem + C::kAccCols + s * C::kSfSlotCols;
+            const uint32_t sfa = sfa0 + s * kStageStep;
+            const uint32_t sfb = sfa + (C::kStageSfa >> 4);
+            if (elect_one()) {
+              if (kb < kb_valid) {
+                tc_copy_32x128b_x4_pair(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
+#pragma unroll
+                for (int rt = 0; rt < 2; ++rt)
+                  tc_copy_32x128b_x4_pair(sf_cols + 16 + kb * (BN / 32) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
+              }
+              tc_commit_pair_local(smem_u32(&sh->sf_full[s]));
+            }
+            __syncwarp();
+            if (++s == C::kStages) s = 0, ph ^= 1;
+          }
+        }
+      }
+    }
+  } else {
+    reg_inc<kRegsEpilogue>();
+    // ------------------------------------------------------------ epilogue (8 warps, both CTAs)
+    const int quad = warp & 3;
+    const int half = (warp - 4) >> 2;
+    const int et = threadIdx.x - 128;
+    uint32_t tile_it = 0;
+    bool ok = true;
+    const bool vec_ok = (g.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(g.y) & 15) == 0) && (g.ldy % 8 == 0);
+    const bool has_bias = g.bias != nullptr;
+    const uint32_t acc_empty_leader[2] = {map_to_rank(smem_u32(&sh->acc_empty[0]), 0), map_to_rank(smem_u32(&sh->acc_empty[1]), 0)};
+    for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_it) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int a = tile_it % ACC;
+      const uint32_t aph = (tile_it / ACC) & 1;
+      float* cs_s = sh->col_scale[tile_it & 1];
+      float* bs_s = sh->bias[tile_it & 1];
+      if (et < BN) {
+        const int col = tn * BN + et;
+        float cs = g.global_scale, bs = 0.0f;
+        if (col < g.N) {
+          if constexpr (KIND == kI8) cs = __ldg(g.col_scale + col);
+          if (has_bias)
+            bs = g.bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[col])
+                                : __ldg(static_cast<const float*>(g.bias) + col);
+        }
+        cs_s[et] = cs;
+        bs_s[et] = bs;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (!(ok = wait_barrier(smem_u32(&sh->acc_full[a]), aph, sh, g.status, 4))) break;
+      tc_fence_after_sync();
+      const int tile_row0 = tm * kPairBM + int(rank) * kBM;
+      const int row = tile_row0 + quad * 32 + lane;
+      const bool row_ok = row < g.M;
+      const float rs = (KIND == kI8 && row_ok) ? __ldg(g.row_scale + row) : 1.0f;
+      __nv_bfloat16* yrow = g.y + size_t(row_ok ? row : 0) * g.ldy;
+      const int warp_row0 = tile_row0 + quad * 32;
+      const int rows_ok = max(0, min(32, g.M - warp_row0));
+      __nv_bfloat16* ywarp = g.y + size_t(min(warp_row0, g.M - 1)) * g.ldy;
+      uint4* stage_w = reinterpret_cast<uint4*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes) + (warp - 4) * 128;
+      constexpr int kTileChunks = BN / 32;
+      constexpr int kMaxJ = (kTileChunks + 1) / 2;
+      const uint32_t tbase = tmem + a * BN + (uint32_t(quad * 32) << 16);
+      uint32_t r[kMaxJ][32];
+#pragma unroll
+      for (int j = 0; j < kMaxJ; ++j)
+        if (half + 2 * j < kTileChunks) tmem_ld_32x32(tbase + (half + 2 * j) * 32, r[j]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader[a]);
+#pragma unroll
+      for (int j = 0; j < kMaxJ; ++j) {
+        const int c = half + 2 * j;
+        const int col0 = tn * BN + c * 32;
+        if (c >= kTileChunks || col0 >= g.N) continue;  // warp-uniform
+        const int lc0 = c * 32;
+        uint4 packed[4];
+        if (!has_bias && g.act == SFQ_ACT_NONE)
+          pack_chunk<KIND, false, false>(r[j], rs, cs_s + lc0, bs_s + lc0, packed);
+        else if (g.act == SFQ_ACT_NONE)
+          pack_chunk<KIND, true, false>(r[j], rs, cs_s + lc0, bs_s + lc0, packed);
+        else
+          pack_chunk<KIND, true, true>(r[j], rs, cs_s + lc0, bs_s + lc0, packed);
+        if (vec_ok && col0 + 32 <= g.N) {
+          flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane);
+        } else if (row_ok) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t w4[4] = {packed[v].x, packed[v].y, packed[v].z, packed[v].w};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int col = col0 + v * 8 + q;
+              if (col < g.N) yrow[col] = __ushort_as_bfloat16((unsigned short)((w4[q >> 1] >> (16 * (q & 1))) & 0xFFFFu));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  cluster_sync_all();  // the pair's MMAs, copies and remote arrivals are all behind both CTAs here
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem, C::kTmemCols);
+  }
+}
+
+// Scale array of one operand in the 128x4 tiling, seen as [row tiles][K/64 atoms x 512 bytes] of 8-byte elements;
+// a box is `tiles` row tiles x 4 atoms (2 KB each), unswizzled, zero beyond the array.
+CUtensorMap make_scale_map(const void* base, size_t row_tiles, size_t k_atoms, int tiles) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0) throw std::invalid_argument("sfq gemm: scale arrays must be 16-byte aligned");
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {k_atoms * 64, row_tiles};
+  const cuuint64_t strides[1] = {k_atoms * 512};
+  const cuuint32_t box[2] = {256, cuuint32_t(tiles)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("sfq gemm: cuTensorMapEncodeTiled failed for a scale array (" + std::to_string(int(r)) + ")");
+  return m;
+}
+
+template <int KIND, int ACC> int max_pairs() {
+  // Clusters of two need both CTAs in one GPC; ask the runtime how many pairs fit at once.
+  static int n = [] {
+    using C = PairCfg<KIND, ACC>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<KIND, ACC>, &cfg);
+    if (e != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      return 0;
+    }
+    return clusters;
+  }();
+  return n;
+}
+
+template <int KIND, int ACC>
+bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
+  using C = PairCfg<KIND, ACC>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_pair_kernel<KIND, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
+  const int pairs_fit = max_pairs<KIND, ACC>();
+  if (pairs_fit <= 0) return false;  // no room for clusters of two: the caller uses the one-CTA kernel
+  const CUtensorMap ma = make_map(a, size_t(g.M), row_bytes, kBM);
+  const CUtensorMap mb = make_map(w, size_t(g.N), row_bytes, kPairBN / 2);
+  CUtensorMap msa = ma, msb = mb;  // placeholders for the kinds without scales
+  if constexpr (KIND == kNvfp4) {
+    msa = make_scale_map(g.a_scale_tiled, size_t((g.M + 127) / 128), size_t(g.K / 64), 1);
+    msb = make_scale_map(g.w_scale_tiled, size_t(g.N / 128), size_t(g.K / 64), 2);
+  }
+  const int tiles = ((g.M + kPairBM - 1) / kPairBM) * ((g.N + kPairBN - 1) / kPairBN);
+  int pairs = std::min(tiles, pairs_fit);
+  if (g.max_ctas > 0) pairs = std::max(1, std::min(pairs, g.max_ctas / 2));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, ACC>, ma, mb, msa, msb, g);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: pair launch failed: ") + cudaGetErrorString(e));
+  return true;
+}
+
+}  // namespace
+
+bool gemm_pair_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t stream) {
+  return launch_pair<kI8, 2>(a, w, size_t(g.K), g, stream);
+}
+bool gemm_pair_nvfp4(const uint8_t* a, const uint8_t* w, const GemmArgs& g, cudaStream_t stream) {
+  return launch_pair<kNvfp4, 1>(a, w, size_t(g.K) / 2, g, stream);
+}
+bool gemm_pair_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream) {
+  return launch_pair<kBf16, 2>(a, w, size_t(g.K) * 2, g, stream);
+}
+
+}  // namespace sfq

@@ -26,6 +26,13 @@ void unpack_int8_bf16(const int8_t* codes, const float* scale, __nv_bfloat16* ou
 void unpack_int8_f16(const int8_t* codes, const float* scale, __half* out, int out_features, int in_features,
                      int rotation_group, int canonicalize_subnormals, cudaStream_t stream);
 
+void unpack_f8e4m3_bf16(const uint8_t* src, const float* scale, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
+void unpack_nf4_bf16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                     const float* nested_absmax, int block, int nested_block, float offset, __nv_bfloat16* dst,
+                     int out_features, int in_features, cudaStream_t stream);
+void convert_f16_bf16(const __half* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
+void convert_f32_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
+
 // ---- act_quant.cu
 struct NormArgs {  // null weight = stage disabled
   const __nv_bfloat16* weight = nullptr;
@@ -45,6 +52,8 @@ size_t nvfp4_act_scale_bytes(int rows, int dim);
 // ---- pointwise.cu
 void gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream);
 void swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int inner, cudaStream_t stream);
+void pre_quant_scale(const __nv_bfloat16* src, const __nv_bfloat16* scale, __nv_bfloat16* dst, int rows, int dim,
+                     cudaStream_t stream);
 void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate, const int32_t* index, int rows,
                int dim, cudaStream_t stream);
 

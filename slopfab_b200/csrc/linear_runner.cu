@@ -42,18 +42,16 @@ void validate_packed_int8(const QuantWeight& w) {
 
 bool has_dense_form(const QuantWeight& w) {
   switch (w.format) {
-    case QuantFormat::kBF16:
-    case QuantFormat::kNVFP4:
-    case QuantFormat::kI8:
-      return true;
-    default:
+    case QuantFormat::kW4A8:
+    case QuantFormat::kW6A8:
       return false;
+    default:
+      return true;
   }
 }
 
 [[noreturn]] void unsupported_format(const QuantWeight& w) {
-  throw std::runtime_error("linear: weight format " + std::to_string(int(w.format)) +
-                           " has no kernel in this build (supported: BF16, I8, NVFP4, W4A8, W6A8)");
+  throw std::runtime_error("linear: unhandled weight format " + std::to_string(int(w.format)));
 }
 
 sfq::GemmArgs epilogue_for(const QuantWeight& w, int rows, __nv_bfloat16* y, int activation) {
@@ -170,6 +168,7 @@ size_t linear_activation_workspace_bytes(const QuantWeight& w, int rows, Compute
   }
   if (compute != ComputeType::kBF16) throw std::runtime_error("linear: fp32 compute is not built in this library");
   size_t total = 0;
+  if (w.pre_quant_scale != nullptr) total += align_up(r * w.in_features * sizeof(__nv_bfloat16));
   if (convrot_applies(w)) total += align_up(r * w.in_features * sizeof(__nv_bfloat16));
   if (w.format == QuantFormat::kNVFP4 && nvfp4_gemm_shape_supported(w.out_features, w.in_features))
     total = std::max(total, nvfp4_gemm_workspace_bytes(rows, w.in_features));
@@ -229,15 +228,35 @@ const __nv_bfloat16* LinearRunner::prepare(const QuantWeight& w, Workspace& ws) 
   if (takes_native_nvfp4(w)) return nullptr;
   if (w.format == QuantFormat::kBF16) return static_cast<const __nv_bfloat16*>(w.data);
   if (!has_dense_form(w)) unsupported_format(w);
-  __nv_bfloat16* dst = ws.alloc_n<__nv_bfloat16>(size_t(w.out_features) * w.in_features);
-  if (w.format == QuantFormat::kNVFP4) {
-    if (w.block_scale == nullptr) throw std::runtime_error("linear: nvfp4 weight without block_scale");
-    sfq::unpack_nvfp4_bf16(static_cast<const uint8_t*>(w.data), w.block_scale, w.global_scale, dst, w.out_features,
-                           w.in_features, stream_);
-  } else {
-    if (w.weight_scale == nullptr) throw std::runtime_error("linear: int8 weight without weight_scale");
-    sfq::unpack_int8_bf16(static_cast<const int8_t*>(w.data), w.weight_scale, dst, w.out_features, w.in_features,
-                          stream_);
+  const size_t n = size_t(w.out_features) * w.in_features;
+  __nv_bfloat16* dst = ws.alloc_n<__nv_bfloat16>(n);
+  switch (w.format) {  // materialise_bf16, src/cuda/linear_weights.cu:580-634
+    case QuantFormat::kNVFP4:
+      if (w.block_scale == nullptr) throw std::runtime_error("linear: nvfp4 weight without block_scale");
+      sfq::unpack_nvfp4_bf16(static_cast<const uint8_t*>(w.data), w.block_scale, w.global_scale, dst, w.out_features,
+                             w.in_features, stream_);
+      break;
+    case QuantFormat::kI8:
+      if (w.weight_scale == nullptr) throw std::runtime_error("linear: int8 weight without weight_scale");
+      sfq::unpack_int8_bf16(static_cast<const int8_t*>(w.data), w.weight_scale, dst, w.out_features, w.in_features, stream_);
+      break;
+    case QuantFormat::kF8E4M3:
+      if (w.weight_scale == nullptr) throw std::runtime_error("linear: fp8 weight without weight_scale");
+      sfq::unpack_f8e4m3_bf16(static_cast<const uint8_t*>(w.data), w.weight_scale, dst, n, stream_);
+      break;
+    case QuantFormat::kNF4:
+      sfq::unpack_nf4_bf16(static_cast<const uint8_t*>(w.data), w.nf4_absmax, w.nf4_quant_map, w.nf4_nested_quant_map,
+                           w.nf4_nested_absmax, w.nf4_block_size, w.nf4_nested_block_size, w.nf4_nested_offset, dst,
+                           w.out_features, w.in_features, stream_);
+      break;
+    case QuantFormat::kF16:
+      sfq::convert_f16_bf16(static_cast<const __half*>(w.data), dst, n, stream_);
+      break;
+    case QuantFormat::kF32:
+      sfq::convert_f32_bf16(static_cast<const float*>(w.data), dst, n, stream_);
+      break;
+    default:
+      unsupported_format(w);
   }
   return dst;
 }
@@ -281,9 +300,13 @@ void LinearRunner::forward_prepared(const QuantWeight& w, const __nv_bfloat16* w
     sfq::gemm_nvfp4(xq, static_cast<const uint8_t*>(w.data), g, stream_);
     return;
   }
-  if (w.pre_quant_scale != nullptr)
-    throw std::runtime_error("linear: AWQ pre_quant_scale has no kernel in this build");
+  // AWQ scales the activation per input channel ahead of everything else (src/cuda/linear.cu:221-237).
   const __nv_bfloat16* xin = x;
+  if (w.pre_quant_scale != nullptr) {
+    __nv_bfloat16* xs = ws.alloc_n<__nv_bfloat16>(size_t(rows) * w.in_features);
+    sfq::pre_quant_scale(xin, w.pre_quant_scale, xs, rows, w.in_features, stream_);
+    xin = xs;
+  }
   if (convrot_applies(w)) {
     __nv_bfloat16* xr = ws.alloc_n<__nv_bfloat16>(size_t(rows) * w.in_features);
     sfq::convrot(xin, xr, rows, w.in_features, w.convrot_group, stream_);
@@ -322,6 +345,19 @@ void launch_convrot(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int d
 void launch_dequant_i8_per_channel(const int8_t* src, const float* scale, __nv_bfloat16* dst, int out_features,
                                    int in_features, cudaStream_t stream) {
   sfq::unpack_int8_bf16(src, scale, dst, out_features, in_features, stream);
+}
+void launch_dequant_f8e4m3(const uint8_t* src, const float* scale, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
+  sfq::unpack_f8e4m3_bf16(src, scale, dst, n, stream);
+}
+void launch_dequant_nf4(const uint8_t* src, const uint8_t* absmax, const float* quant_map, const float* nested_quant_map,
+                        const float* nested_absmax, int block_size, int nested_block_size, float nested_offset,
+                        __nv_bfloat16* dst, int out_features, int in_features, cudaStream_t stream) {
+  sfq::unpack_nf4_bf16(src, absmax, quant_map, nested_quant_map, nested_absmax, block_size, nested_block_size,
+                       nested_offset, dst, out_features, in_features, stream);
+}
+void launch_pre_quant_scale(const __nv_bfloat16* src, const __nv_bfloat16* scale, __nv_bfloat16* dst, int rows, int dim,
+                            cudaStream_t stream) {
+  sfq::pre_quant_scale(src, scale, dst, rows, dim, stream);
 }
 void launch_dequant_nvfp4(const uint8_t* src, const uint8_t* block_scale, float global_scale, __nv_bfloat16* dst,
                           int out_features, int in_features, cudaStream_t stream) {

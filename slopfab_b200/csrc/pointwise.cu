@@ -69,7 +69,26 @@ __global__ void add_gated_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_b
   *xp = out;
 }
 
+// dst[r, i] = bf16(src[r, i] * scale[i]): the AWQ activation pre-scale (pre_quant_scale_kernel,
+// src/cuda/linear_weights.cu:499-509).
+__global__ void pre_quant_scale_kernel(const __nv_bfloat16* __restrict__ src, const __nv_bfloat16* __restrict__ scale,
+                                       __nv_bfloat16* __restrict__ dst, int dim) {
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  if (col >= dim) return;
+  const size_t i = size_t(blockIdx.x) * dim + col;
+  dst[i] = __float2bfloat16(__bfloat162float(src[i]) * __bfloat162float(scale[col]));
+}
+
 }  // namespace
+
+void pre_quant_scale(const __nv_bfloat16* src, const __nv_bfloat16* scale, __nv_bfloat16* dst, int rows, int dim,
+                     cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) return;
+  if (scale == nullptr) throw std::runtime_error("pre_quant_scale: null scale");
+  if (!src || !dst) throw std::invalid_argument("pre_quant_scale: null buffer");
+  pre_quant_scale_kernel<<<dim3(rows, (dim + 255) / 256), 256, 0, stream>>>(src, scale, dst, dim);
+  check_launch("pre_quant_scale");
+}
 
 void gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream) {
   if (n == 0) return;

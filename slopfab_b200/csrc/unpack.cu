@@ -180,7 +180,91 @@ unpack_int8_f16_kernel(const int8_t* __restrict__ codes, const float* __restrict
   }
 }
 
+// bf16(f8_e4m3(v) * scale), scale a device scalar (dequant_f8_kernel, src/cuda/linear_weights.cu:150-172).
+__global__ void __launch_bounds__(kThreads)
+unpack_f8_kernel(const uint8_t* __restrict__ src, const float* __restrict__ scale, __nv_bfloat16* __restrict__ dst, size_t n) {
+  const size_t i = (size_t(blockIdx.x) * kThreads + threadIdx.x) * 8;
+  if (i >= n) return;
+  const float s = __ldg(scale);
+  if (i + 8 <= n && (reinterpret_cast<uintptr_t>(src) & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + i));
+    const uint32_t w[2] = {raw.x, raw.y};
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t b0 = (w[j >> 1] >> (16 * (j & 1))) & 0xFFu, b1 = (w[j >> 1] >> (16 * (j & 1) + 8)) & 0xFFu;
+      op[j] = __floats2bfloat162_rn(e4m3_decode(uint8_t(b0)) * s, e4m3_decode(uint8_t(b1)) * s);
+    }
+    *reinterpret_cast<uint4*>(dst + i) = o;
+  } else {
+    for (size_t j = i; j < n && j < i + 8; ++j) dst[j] = __float2bfloat16(e4m3_decode(src[j]) * s);
+  }
+}
+
+// bitsandbytes NF4, double-quantized block scales, high nibble = even element
+// (dequant_nf4_kernel / dequant_nf4_vec_kernel, src/cuda/linear_weights.cu:273-315):
+// value = map[code] * (nested_map[absmax[block]] * nested_absmax[block / nested_block] + offset).
+__global__ void __launch_bounds__(kThreads)
+unpack_nf4_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ absmax, const float* __restrict__ map,
+                  const float* __restrict__ nested_map, const float* __restrict__ nested_absmax, int block,
+                  int nested_block, float offset, __nv_bfloat16* __restrict__ dst, size_t n) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = map[threadIdx.x];
+  __syncthreads();
+  const size_t byte = size_t(blockIdx.x) * kThreads + threadIdx.x;
+  const size_t even = byte * 2;
+  if (even >= n) return;
+  const size_t b = even / size_t(block);
+  const float scale = __fmaf_rn(nested_map[absmax[b]], nested_absmax[b / size_t(nested_block)], offset);
+  const uint8_t packed = src[byte];
+  dst[even] = __float2bfloat16(lut[packed >> 4] * scale);
+  if (even + 1 < n) {
+    // an odd block size could put the odd element in the next block; recompute when it does
+    const size_t b1 = (even + 1) / size_t(block);
+    const float s1 = b1 == b ? scale : __fmaf_rn(nested_map[absmax[b1]], nested_absmax[b1 / size_t(nested_block)], offset);
+    dst[even + 1] = __float2bfloat16(lut[packed & 15] * s1);
+  }
+}
+
+template <class T> __global__ void __launch_bounds__(kThreads) to_bf16_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+  const size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x;
+  if (i < n) dst[i] = __float2bfloat16(float(src[i]));
+}
+
 }  // namespace
+
+void unpack_f8e4m3_bf16(const uint8_t* src, const float* scale, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  if (!src || !scale || !dst) throw std::runtime_error("linear: fp8 weight without weight_scale");
+  unpack_f8_kernel<<<blocks_for((n + 7) / 8, kThreads), kThreads, 0, stream>>>(src, scale, dst, n);
+  check_launch("unpack_f8e4m3");
+}
+
+void unpack_nf4_bf16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                     const float* nested_absmax, int block, int nested_block, float offset, __nv_bfloat16* dst,
+                     int out_features, int in_features, cudaStream_t stream) {
+  if (out_features <= 0 || in_features <= 0) return;
+  if (!src || !absmax || !map || !nested_map || !nested_absmax || !dst)
+    throw std::runtime_error("linear: nf4 weight without complete double-quant state");
+  if (block <= 0 || nested_block <= 0) throw std::invalid_argument("unpack_nf4: block sizes must be positive");
+  const size_t n = size_t(out_features) * in_features;
+  unpack_nf4_kernel<<<blocks_for((n + 1) / 2, kThreads), kThreads, 0, stream>>>(src, absmax, map, nested_map, nested_absmax,
+                                                                               block, nested_block, offset, dst, n);
+  check_launch("unpack_nf4");
+}
+
+void convert_f16_bf16(const __half* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  to_bf16_kernel<__half><<<blocks_for(n, kThreads), kThreads, 0, stream>>>(src, dst, n);
+  check_launch("convert_f16_bf16");
+}
+
+void convert_f32_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  to_bf16_kernel<float><<<blocks_for(n, kThreads), kThreads, 0, stream>>>(src, dst, n);
+  check_launch("convert_f32_bf16");
+}
 
 void unpack_nvfp4_bf16(const uint8_t* data, const uint8_t* scale, float global, __nv_bfloat16* out, int out_features,
                        int in_features, cudaStream_t stream) {

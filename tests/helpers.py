@@ -77,7 +77,10 @@ class RefWeight(C.Structure):
     _fields_ = [("format", C.c_int), ("data", C.c_void_p), ("out_features", C.c_int), ("in_features", C.c_int),
                 ("weight_scale", C.c_void_p), ("per_channel_scale", C.c_int), ("block_scale", C.c_void_p),
                 ("packed_group_size", C.c_uint32), ("w4_codebook", C.c_void_p), ("global_scale", C.c_float),
-                ("convrot", C.c_int), ("convrot_group", C.c_int), ("bias", C.c_void_p), ("bias_format", C.c_int)]
+                ("convrot", C.c_int), ("convrot_group", C.c_int), ("bias", C.c_void_p), ("bias_format", C.c_int),
+                ("pre_quant_scale", C.c_void_p), ("nf4_absmax", C.c_void_p), ("nf4_quant_map", C.c_void_p),
+                ("nf4_nested_quant_map", C.c_void_p), ("nf4_nested_absmax", C.c_void_p), ("nf4_block_size", C.c_int),
+                ("nf4_nested_block_size", C.c_int), ("nf4_nested_offset", C.c_float)]
 
 
 def ref_weight_from(w: sfq.QuantWeight) -> RefWeight:
@@ -95,7 +98,8 @@ def ref_dev():
     V, I, F, SZ = C.c_void_p, C.c_int, C.c_float, C.c_size_t
     sigs = {"ref_dev_dequant_nvfp4": [V, V, F, V, I, I], "ref_dev_dequant_i8": [V, V, V, I, I],
             "ref_dev_dequant_w4a8": [V, V, V, V, I, I, I], "ref_dev_dequant_w6a8": [V, V, V, I, I, I],
-            "ref_dev_convrot": [V, V, I, I, I], "ref_dev_quantize_int8_bf16": [V, V, V, I, I],
+            "ref_dev_dequant_f8": [V, V, V, SZ], "ref_dev_dequant_nf4": [V, V, V, V, V, I, I, F, V, I, I],
+            "ref_dev_pre_quant_scale": [V, V, V, I, I], "ref_dev_convrot": [V, V, I, I, I], "ref_dev_quantize_int8_bf16": [V, V, V, I, I],
             "ref_dev_quantize_int8_f16": [V, V, V, I, I], "ref_dev_output_bf16": [V, V, V, V, I, I],
             "ref_dev_quantize_nvfp4_act": [V, V, V, I, I], "ref_dev_rmsnorm": [V, V, V, V, V, V, I, I, F],
             "ref_dev_gelu_tanh": [V, SZ], "ref_dev_swiglu": [V, V, I, I], "ref_dev_add_gated": [V, V, V, V, I, I],

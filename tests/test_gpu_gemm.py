@@ -24,7 +24,7 @@ def _status_clean():
     assert sfq.device_status() == 0, "a kernel abandoned a bounded wait"
 
 
-@pytest.mark.parametrize("tile_n", [256, 128])
+@pytest.mark.parametrize("tile_n", [0, 256, 128])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (1, 128, 256), (200, 384, 512), (129, 34, 256), (300, 520, 1280),
                                    (257, 1024, 5120)])
 def test_gemm_int8_bit_exact(M, N, K, tile_n):
@@ -112,7 +112,7 @@ def _run_nvfp4(x, data, scale, g, M, N, K, bias=None, act=sfq.ACT_NONE):
     return y
 
 
-@pytest.mark.parametrize("tile_n", [256, 128])
+@pytest.mark.parametrize("tile_n", [0, 256, 128])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (17, 128, 128), (128, 256, 192), (200, 128, 320), (129, 256, 64),
                                    (256, 1024, 1024), (300, 384, 5120)])
 def test_gemm_nvfp4_matches_fp4_activation_oracle(M, N, K, tile_n):

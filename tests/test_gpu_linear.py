@@ -169,7 +169,7 @@ def test_runner_error_contract():
     # an arena that is too small is reported, not overrun
     rc = sfq.lib.sfq_linear_forward(runner._h, C.byref(w), sfq.ptr(x), 4, sfq.ptr(y), sfq.ptr(ws), 1024)
     assert rc == sfq.ERR_OUT_OF_MEMORY
-    # formats without a kernel in this build say so
+    # an fp8 weight without its scale is refused (materialise_bf16, src/cuda/linear_weights.cu:580-634)
     wf8 = sfq.new_weight(format=sfq.F8E4M3, data=sfq.ptr(x), out_features=4, in_features=256)
     with pytest.raises(sfq.SfqError):
         runner.forward(wf8, x)
