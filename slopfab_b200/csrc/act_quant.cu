@@ -481,6 +481,8 @@ void quantize_int8_token(const __nv_bfloat16* x, const NormArgs& norm, int8_t* q
   if (!x || !q || !row_scale) throw std::invalid_argument("quantize_int8_token: null buffer");
   if (apply_convrot && dim % 256 != 0) throw std::invalid_argument("W4A8 activation requires K divisible by 256");
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0) throw std::invalid_argument("quantize_int8_token: output must be 16-byte aligned");
+  // The Linear's own case (rotation on, nothing fused in front, K <= 6144) has a two-rows-per-step kernel.
+  if (apply_convrot && norm.weight == nullptr && quantize_int8_rot_pairs(x, q, row_scale, rows, dim, stream)) return;
   FusedArgs a = base_args(x, norm, rows, dim);
   a.q = q;
   a.row_scale = row_scale;

@@ -54,6 +54,8 @@ void gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream);
 void swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int inner, cudaStream_t stream);
 void pre_quant_scale(const __nv_bfloat16* src, const __nv_bfloat16* scale, __nv_bfloat16* dst, int rows, int dim,
                      cudaStream_t stream);
+// quant_int8_pairs.cu: ConvRot-256 + per-token int8 without a norm in front; false when the shape is not covered.
+bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, cudaStream_t stream);
 void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate, const int32_t* index, int rows,
                int dim, cudaStream_t stream);
 

@@ -140,13 +140,14 @@ def test_convrot_bit_exact(rows, dim, group):
     assert sfq.lib.sfq_convrot(sfq.ptr(dx), sfq.ptr(out), rows, dim, 8, S) == sfq.ERR_RUNTIME  # not a power of four
 
 
-@pytest.mark.parametrize("rows,dim,outliers", [(3, 256, False), (33, 5120, True), (5, 13824, False), (4, 1024, True)])
+@pytest.mark.parametrize("rows,dim,outliers", [(3, 256, False), (33, 5120, True), (5, 13824, False), (4, 1024, True),
+                                               (1, 512, False), (2, 6144, True), (1201, 5120, True), (6, 6400, False)])
 def test_fused_convrot_int8_quantizer_bit_exact(rows, dim, outliers):
     x = gaussian_bf16((rows, dim), seed=rows + dim, outliers=outliers)
     x[0] = 0  # a zero row: scale floors at 1e-30, codes all zero
     if rows > 2:
         x[1] = 0
-        x[1, 0] = oracle.to_bf16(np.float32(1.0))  # unit impulse
+        x[1, 0] = oracle.to_bf16(np.array([1.0], np.float32))[0]  # unit impulse
         x[2] = oracle.to_bf16(np.float32(1.0))      # all ones
     dx = bf16_tensor(x)
     q = torch.empty((rows, dim), dtype=torch.int8, device="cuda")
