@@ -117,6 +117,9 @@ size_t linear_activation_workspace_bytes(const QuantWeight& w, int rows, Compute
 class LinearRunner {
 public:
   LinearRunner() = default;
+  ~LinearRunner();
+  LinearRunner(const LinearRunner&) = delete;
+  LinearRunner& operator=(const LinearRunner&) = delete;
 
   // The handle is accepted for source compatibility and never used: no library GEMM is on this path.
   void init(cublasHandle_t handle, cudaStream_t stream);
@@ -139,7 +142,10 @@ public:
 
 private:
   bool takes_native_nvfp4(const QuantWeight& w) const;
-  const int8_t* expanded_weight(const QuantWeight& w, Workspace& ws, bool keep);
+  const int8_t* expanded_weight(const QuantWeight& w, Workspace& ws, bool keep, cudaStream_t stream);
+  void run_packed_int8(const QuantWeight& w, const int8_t* codes, const __nv_bfloat16* x, int rows, __nv_bfloat16* y,
+                       Workspace& ws, cudaEvent_t codes_ready);
+  void ensure_side_stream();
 
   cudaStream_t stream_ = nullptr;
   bool initialised_ = false;
@@ -151,6 +157,11 @@ private:
   const int8_t* cached_codes_ = nullptr;
   const void* cached_arena_ = nullptr;
   size_t cached_end_ = 0;
+  // A plain forward() of a W4A8/W6A8 layer expands the weight on this second stream while the activation is
+  // quantized on the caller's; the GEMM waits for both. Created on first use.
+  cudaStream_t side_ = nullptr;
+  cudaEvent_t fork_ = nullptr;
+  cudaEvent_t join_ = nullptr;
 };
 
 // ---- free launchers, reference names ------------------------------------------------------

@@ -195,17 +195,31 @@ bool LinearRunner::takes_native_nvfp4(const QuantWeight& w) const {
          nvfp4_gemm_shape_supported(w.out_features, w.in_features);
 }
 
-const int8_t* LinearRunner::expanded_weight(const QuantWeight& w, Workspace& ws, bool keep) {
+LinearRunner::~LinearRunner() {
+  if (fork_) cudaEventDestroy(fork_);
+  if (join_) cudaEventDestroy(join_);
+  if (side_) cudaStreamDestroy(side_);
+}
+
+void LinearRunner::ensure_side_stream() {
+  if (side_ != nullptr) return;
+  cudaError_t e = cudaStreamCreateWithFlags(&side_, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&fork_, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&join_, cudaEventDisableTiming);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("LinearRunner: cannot create the side stream: ") + cudaGetErrorString(e));
+}
+
+const int8_t* LinearRunner::expanded_weight(const QuantWeight& w, Workspace& ws, bool keep, cudaStream_t stream) {
   // A previous prepare() on this weight in this arena, still below the cursor: reuse it.
   if (cached_key_ == w.data && cached_arena_ == ws.base() && cached_codes_ != nullptr && ws.used() >= cached_end_)
     return cached_codes_;
   int8_t* codes = ws.alloc_n<int8_t>(size_t(w.out_features) * w.in_features);
   if (w.format == QuantFormat::kW6A8)
     sfq::unpack_w6a8_int8(static_cast<const int8_t*>(w.data), w.block_scale, codes, w.out_features, w.in_features,
-                          int(w.packed_group_size), stream_);
+                          int(w.packed_group_size), stream);
   else
     sfq::unpack_w4a8_int8(static_cast<const int8_t*>(w.data), w.block_scale, w.w4_codebook, codes, w.out_features,
-                          w.in_features, 16, stream_);
+                          w.in_features, 16, stream);
   if (keep) {
     cached_key_ = w.data;
     cached_codes_ = codes;
@@ -222,7 +236,7 @@ const __nv_bfloat16* LinearRunner::prepare(const QuantWeight& w, Workspace& ws) 
     // carved in `ws` so the chunk loop that follows does not redo it.
     validate_packed_int8(w);
     cached_key_ = nullptr;
-    expanded_weight(w, ws, /*keep=*/true);
+    expanded_weight(w, ws, /*keep=*/true, stream_);
     return nullptr;
   }
   if (takes_native_nvfp4(w)) return nullptr;
@@ -281,7 +295,20 @@ void LinearRunner::forward_prepared(const QuantWeight& w, const __nv_bfloat16* w
 
   if (is_packed_int8(w.format)) {
     validate_packed_int8(w);
-    forward_with_codes(w, expanded_weight(w, ws, /*keep=*/false), x, rows, y, ws);
+    if (cached_key_ == w.data && cached_arena_ == ws.base() && cached_codes_ != nullptr && ws.used() >= cached_end_) {
+      run_packed_int8(w, cached_codes_, x, rows, y, ws, nullptr);  // expansion kept by prepare()
+      return;
+    }
+    // No expansion at hand: decode the weight on the side stream while this one quantizes the activation.
+    ensure_side_stream();
+    auto check = [](cudaError_t e) {
+      if (e != cudaSuccess) throw std::runtime_error(std::string("LinearRunner: stream fork failed: ") + cudaGetErrorString(e));
+    };
+    check(cudaEventRecord(fork_, stream_));
+    check(cudaStreamWaitEvent(side_, fork_, 0));
+    const int8_t* codes = expanded_weight(w, ws, /*keep=*/false, side_);
+    check(cudaEventRecord(join_, side_));
+    run_packed_int8(w, codes, x, rows, y, ws, join_);
     return;
   }
   if (weight == nullptr && !takes_native_nvfp4(w))
@@ -322,11 +349,20 @@ void LinearRunner::forward_with_codes(const QuantWeight& w, const int8_t* codes,
   if (rows <= 0) return;
   validate_packed_int8(w);
   if (codes == nullptr) throw std::invalid_argument("LinearRunner::forward_with_codes: null int8 weight");
+  run_packed_int8(w, codes, x, rows, y, ws, nullptr);
+}
+
+void LinearRunner::run_packed_int8(const QuantWeight& w, const int8_t* codes, const __nv_bfloat16* x, int rows,
+                                   __nv_bfloat16* y, Workspace& ws, cudaEvent_t codes_ready) {
   Workspace::Scope scope(ws);
   int8_t* q = ws.alloc_n<int8_t>(size_t(rows) * w.in_features);
   float* scales = ws.alloc_n<float>(size_t(rows));
   sfq::quantize_int8_token(x, sfq::NormArgs{}, q, scales, nullptr, rows, w.in_features, /*apply_convrot=*/true,
                            stream_);
+  if (codes_ready != nullptr) {
+    const cudaError_t e = cudaStreamWaitEvent(stream_, codes_ready, 0);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("LinearRunner: stream join failed: ") + cudaGetErrorString(e));
+  }
   sfq::GemmArgs g = epilogue_for(w, rows, y, activation_);
   g.row_scale = scales;
   g.col_scale = w.weight_scale;
