@@ -320,7 +320,7 @@ def run_ours(args):
                     "ms_per_step": e2e_ms_step},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks.summary(),
-            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<int8,128x256>", "achieved": gemm_tflops,
+            "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<int8> (CTA pair, 256x256 tile)", "achieved": gemm_tflops,
                          "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / int8_peak, "traffic": None,
                          "peak_note": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s); "
                                       "nominal dense int8 is 4500",

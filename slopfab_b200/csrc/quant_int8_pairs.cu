@@ -93,7 +93,9 @@ __device__ __forceinline__ float div127(float m) {
   return __fmaf_rn(__fmaf_rn(-q0, 127.0f, m), r, q0);
 }
 
-__global__ void __launch_bounds__(384, 2)
+// MAXT / MINB: 320 threads (K <= 5120) fit three CTAs per SM in 64 registers; up to 384 threads (K <= 6144) two.
+template <int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
 quantize_int8_pairs_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ row_scale,
                            int rows, int dim) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -209,29 +211,37 @@ quantize_int8_pairs_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restri
   }
 }
 
+template <int MAXT, int MINB>
+void launch_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, int threads, cudaStream_t stream) {
+  const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 2 * 32 * sizeof(uint32_t);
+  static size_t reserved = 0;  // per instantiation
+  if (smem > 48 * 1024 && smem > reserved) {
+    const cudaError_t e = cudaFuncSetAttribute(quantize_int8_pairs_kernel<MAXT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
+    reserved = smem;
+  }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_int8_pairs_kernel<MAXT, MINB>, threads, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = std::min((rows + 1) / 2, per_sm * sms);
+  quantize_int8_pairs_kernel<MAXT, MINB><<<grid, threads, smem, stream>>>(x, q, row_scale, rows, dim);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
+}
+
 }  // namespace
 
 bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, cudaStream_t stream) {
   if (dim % 256 != 0 || dim > 6144 || rows <= 0) return false;
   if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0) return false;
   const int threads = ((dim / 16 + 31) / 32) * 32;
-  const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 2 * 32 * sizeof(uint32_t);
-  static size_t reserved = 0;
-  if (smem > 48 * 1024 && smem > reserved) {
-    const cudaError_t e = cudaFuncSetAttribute(quantize_int8_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
-    reserved = smem;
-  }
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_int8_pairs_kernel, threads, smem) != cudaSuccess || per_sm < 1)
-    per_sm = 1;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = std::min((rows + 1) / 2, per_sm * sms);
-  quantize_int8_pairs_kernel<<<grid, threads, smem, stream>>>(x, q, row_scale, rows, dim);
-  const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
+  if (threads <= 320)
+    launch_pairs<320, 3>(x, q, row_scale, rows, dim, threads, stream);
+  else
+    launch_pairs<384, 2>(x, q, row_scale, rows, dim, threads, stream);
   return true;
 }
 
