@@ -153,6 +153,10 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one config-2 GEMM launch (ncu capture of `--case gemm_int8_c2`).
+C2_GEMM_DRAM_BYTES = 52883456 + 14948352
+
+
 def time_region(torch, fn, iters):
     """CUDA-event time of `iters` calls on the current stream, in milliseconds."""
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -321,7 +325,10 @@ def run_ours(args):
             "gpu_launches": 3 * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<int8> (CTA pair, 256x256 tile)", "achieved": gemm_tflops,
-                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / int8_peak, "traffic": None,
+                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / int8_peak, "traffic": C2_GEMM_DRAM_BYTES,
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this GEMM on cold "
+                                         "operands (ncu, profiles/bench_config2_w4a8_launch_list.md); algorithmic bytes "
+                                         f"{M * K + N * K + 2 * M * N}; part of the 42 MB output is still in L2 when the kernel ends",
                          "peak_note": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s); "
                                       "nominal dense int8 is 4500",
                          "ms_per_launch": kern["gemm_int8"]},
@@ -395,6 +402,7 @@ def run_case(name):
     torch.cuda.set_device(0)
     sfq.lib.sfq_gemm_tuning(int(os.environ.get("SFQ_TILE_N", "0")), 0, 0)  # experiments: 128 or 256
     m, n, k = 16384, 5120, 5120
+    reps = 3
     y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     if name == "gemm_int8":
         a8 = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
@@ -403,6 +411,19 @@ def run_case(name):
         ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
         fn = lambda i: sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(a8), sfq.ptr(w8), C.byref(ep), sfq.ptr(y), m, n, k,  # noqa: E731
                                                        sfq.stream_ptr()))
+        work = 2.0 * m * n * k
+    elif name == "gemm_int8_c2":
+        # the benchmark's own GEMM (config 2) on four rotating operand sets, so that a captured launch reads cold data
+        m, reps = 4096, 7
+        sets = []
+        for _ in range(4):
+            sets.append((torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda"),
+                         torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda"),
+                         torch.empty((m, n), dtype=torch.bfloat16, device="cuda")))
+        rs, cs = torch.rand(m, device="cuda") * 0.01, torch.rand(n, device="cuda") * 0.01
+        ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
+        fn = lambda i: sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(sets[i % 4][0]), sfq.ptr(sets[i % 4][1]), C.byref(ep),  # noqa: E731
+                                                       sfq.ptr(sets[i % 4][2]), m, n, k, sfq.stream_ptr()))
         work = 2.0 * m * n * k
     elif name == "gemm_nvfp4":
         aq = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda")
@@ -431,7 +452,7 @@ def run_case(name):
         raise SystemExit("unknown case " + name)
     fn(0)
     torch.cuda.synchronize()
-    ms = time_region(torch, fn, 3) / 3
+    ms = time_region(torch, fn, reps) / reps
     print(json.dumps({"case": name, "ms_per_launch": ms, "work_per_second": work / (ms * 1e-3),
                       "device_status": sfq.device_status()}))
 

@@ -76,7 +76,7 @@ def test_gemm_int8_multi_tile_persistence():
     assert torch.equal(y, want.to(torch.bfloat16))
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 512, 520), (77, 128, 5120)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 512, 520), (77, 128, 5120), (2500, 768, 1032)])
 def test_gemm_bf16_within_reference_tolerance(M, N, K):
     x = bf16_tensor(gaussian_bf16((M, K), seed=M))
     w = bf16_tensor(gaussian_bf16((N, K), seed=N + 1, sigma=0.02))
@@ -129,6 +129,17 @@ def test_gemm_nvfp4_matches_fp4_activation_oracle(M, N, K, tile_n):
     # the reference's own bar for this comparison
     got, ref_ = oracle.from_bf16(bits(y)), oracle.from_bf16(want)
     assert np.all(np.abs(got - ref_) <= 1e-3 + 1e-2 * np.abs(ref_))
+
+
+def test_gemm_nvfp4_multi_tile_persistence():
+    # more 256x256 tiles than CTA pairs, ragged M, ragged last K stage: every pair walks several tiles through the one
+    # accumulator and wraps the stage ring (and its scale slots) many times
+    M, N, K = 256 * 41 - 24, 2048, 448
+    x, data, scale, g = _nvfp4_case(M, N, K, seed=11)
+    y = _run_nvfp4(x, data, scale, g, M, N, K)
+    want = oracle.nvfp4_linear(x, data, scale, g, N, K)
+    max_abs, rel_l2, corr = oracle.compare_bf16(want, bits(y))
+    assert max_abs <= 2e-2 and rel_l2 <= 1e-3 and corr > 0.999, (max_abs, rel_l2, corr)
 
 
 def test_gemm_nvfp4_wrong_layouts_are_far_away():
