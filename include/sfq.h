@@ -103,6 +103,12 @@ typedef struct sfq_epilogue {
   const void* d_bias;          /* optional [N] */
   int32_t bias_format;         /* SFQ_F32 or SFQ_BF16 */
   int32_t activation;          /* sfq_activation */
+  /* Optional gated residual (launch_add_gated, include/slopfab/cuda/nn_kernels.cuh:64-69) fused behind bias and
+   * activation: when d_gate is non-null the output buffer is read-modify-written,
+   * y[r, c] = bf16(fma(d_gate[d_gate_index[r] * N + c], branch[r, c], y[r, c])), branch = the bf16 value the
+   * epilogue would have stored. Both null: plain store. */
+  const float* d_gate;         /* fp32 [*, N] */
+  const int32_t* d_gate_index; /* int32 [M] */
 } sfq_epilogue;
 
 /* Optional RMSNorm / adaLN-modulate stage fused in front of a quantizer.

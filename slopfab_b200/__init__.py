@@ -36,7 +36,7 @@ class QuantWeight(C.Structure):
 
 class Epilogue(C.Structure):
     _fields_ = [("d_row_scale", V), ("d_col_scale", V), ("global_scale", F), ("d_bias", V),
-                ("bias_format", C.c_int32), ("activation", C.c_int32)]
+                ("bias_format", C.c_int32), ("activation", C.c_int32), ("d_gate", V), ("d_gate_index", V)]
 
 
 class Norm(C.Structure):

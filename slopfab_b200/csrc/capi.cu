@@ -105,6 +105,12 @@ sfq::GemmArgs to_gemm(const sfq_epilogue* ep, void* y, int M, int N, int K) {
     if (ep->activation != SFQ_ACT_NONE && ep->activation != SFQ_ACT_GELU_TANH)
       throw std::invalid_argument("sfq gemm: unknown activation");
     g.act = ep->activation;
+    if ((ep->d_gate != nullptr) != (ep->d_gate_index != nullptr))
+      throw std::invalid_argument("sfq gemm: the gated residual needs both the gate table and the row index");
+    if (reinterpret_cast<uintptr_t>(ep->d_gate) % 16 != 0)
+      throw std::invalid_argument("sfq gemm: the gate table must be 16-byte aligned");
+    g.gate = ep->d_gate;
+    g.gate_index = ep->d_gate_index;
   }
   g.status = sfq::device_status_word();
   sfq::apply_tuning(g);

@@ -120,17 +120,48 @@ __device__ __forceinline__ void pack_chunk(const uint32_t (&r)[32], float rs, co
 // XOR-swizzled with the row, both phases bank-conflict free) and each instruction then writes 64 contiguous
 // bytes of 8 rows. `dst` = global address of (first row of the warp, first column of the chunk).
 __device__ __forceinline__ void flush_chunk(const uint4 (&packed)[4], uint4* stage, __nv_bfloat16* dst, size_t ldy,
-                                            int rows_ok, int lane) {
+                                            int rows_ok, int lane, const float* gate = nullptr, size_t gate_ld = 0,
+                                            const int (&gate_idx)[4] = {0, 0, 0, 0}) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = packed[v];
   __syncwarp();
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int row = 8 * i + (lane >> 2), unit = lane & 3;
-    const uint4 val = stage[row * 4 + (unit ^ ((row >> 1) & 3))];
-    if (row < rows_ok) *reinterpret_cast<uint4*>(dst + size_t(row) * ldy + unit * 8) = val;
+    uint4 val = stage[row * 4 + (unit ^ ((row >> 1) & 3))];
+    if (row < rows_ok) {
+      uint4* out = reinterpret_cast<uint4*>(dst + size_t(row) * ldy + unit * 8);
+      if (gate != nullptr) {  // `gate` already points at this chunk's first column
+        // gated residual, y = bf16(fma(gate, branch, y)) with the branch rounded to bf16 first: the arithmetic of
+        // add_gated_kernel (src/cuda/nn_pointwise.cu:16-37) on the value this GEMM would have stored
+        const uint4 cur = *out;
+        const float4* gp = reinterpret_cast<const float4*>(gate + size_t(gate_idx[i]) * gate_ld + unit * 8);
+        const float4 g0 = __ldg(gp), g1 = __ldg(gp + 1);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&val);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&cur);
+        uint4 res;
+        __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const float2 b = __bfloat1622float2(bp[h]), x = __bfloat1622float2(xp[h]);
+          rp[h] = __floats2bfloat162_rn(__fmaf_rn(gg[2 * h], b.x, x.x), __fmaf_rn(gg[2 * h + 1], b.y, x.y));
+        }
+        val = res;
+      }
+      *out = val;
+    }
   }
   __syncwarp();  // the block is reused by the next chunk
+}
+
+// The gate-table rows of the four output rows a lane meets in flush_chunk (rows 8 i + lane / 4 of its warp's 32).
+__device__ __forceinline__ void gate_rows_for(const GemmArgs& g, int warp_row0, int lane, int (&idx)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = warp_row0 + 8 * i + (lane >> 2);
+    idx[i] = (g.gate != nullptr && r < g.M) ? __ldg(g.gate_index + r) : 0;
+  }
 }
 
 // ------------------------------------------------------------------ host side

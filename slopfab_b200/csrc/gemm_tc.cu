@@ -283,6 +283,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         cs_s[et] = cs;
         bs_s[et] = bs;
       }
+      if (g.gate != nullptr) {
+        // Gated residual: the epilogue will read-modify-write this tile of y. Ask L2 for it now, a whole main loop
+        // ahead, so those reads do not pay HBM latency on the store path (128 rows x BN bf16 = BN/64 lines per row).
+        constexpr int kLinesPerRow = BN / 64;
+        for (int l = et; l < kBM * kLinesPerRow; l += 256) {
+          const int pr = tm * kBM + l / kLinesPerRow, pc = tn * BN + (l % kLinesPerRow) * 64;
+          if (pr < g.M && pc < g.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(g.y + size_t(pr) * g.ldy + pc));
+        }
+      }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (!(ok = wait_barrier(smem_u32(&sh->acc_full[a]), aph, sh, g.status, 4))) break;
       tc_fence_after_sync();
@@ -300,6 +309,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       constexpr int kTileChunks = BN / 32;
       constexpr int kMaxJ = (kTileChunks + 1) / 2;
       const uint32_t tbase = tmem + a * BN + (uint32_t(quad * 32) << 16);
+      int gate_idx[4];
+      gate_rows_for(g, warp_row0, lane, gate_idx);
+      const float* gate_row = (g.gate != nullptr && row_ok) ? g.gate + size_t(__ldg(g.gate_index + row)) * g.N : nullptr;
       uint32_t r[kMaxJ][32];
 #pragma unroll
       for (int j = 0; j < kMaxJ; ++j)
@@ -322,7 +334,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         else
           pack_chunk<KIND, true, true>(r[j], rs, cs_s + lc0, bs_s + lc0, packed);
         if (vec_ok && col0 + 32 <= g.N) {
-          flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane);
+          flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, g.gate ? g.gate + col0 : nullptr, size_t(g.N),
+                      gate_idx);
         } else if (row_ok) {  // ragged N or unaligned output: element stores from this thread's own row
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -330,7 +343,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const int col = col0 + v * 8 + q;
-              if (col < g.N) yrow[col] = __ushort_as_bfloat16((unsigned short)((w4[q >> 1] >> (16 * (q & 1))) & 0xFFFFu));
+              if (col < g.N) {
+                __nv_bfloat16 o = __ushort_as_bfloat16((unsigned short)((w4[q >> 1] >> (16 * (q & 1))) & 0xFFFFu));
+                if (gate_row != nullptr)
+                  o = __float2bfloat16(__fmaf_rn(__ldg(gate_row + col), __bfloat162float(o), __bfloat162float(yrow[col])));
+                yrow[col] = o;
+              }
             }
           }
         }

@@ -22,6 +22,10 @@ struct GemmArgs {
   const void* bias = nullptr;        // [N] fp32 or bf16, optional
   int bias_is_bf16 = 0;
   int act = SFQ_ACT_NONE;
+  // optional gated residual: y[r, c] = bf16(fma(gate[gate_index[r], c], branch[r, c], y[r, c])), branch = what the
+  // epilogue would otherwise have stored (launch_add_gated, include/slopfab/cuda/nn_kernels.cuh:64-69)
+  const float* gate = nullptr;          // fp32 [*, N]
+  const int32_t* gate_index = nullptr;  // int32 [M]
   // nvfp4 block scales, both in the 128x4-tiled layout (512-byte tiles, row tile major)
   const uint8_t* a_scale_tiled = nullptr;
   const uint8_t* w_scale_tiled = nullptr;

@@ -29,7 +29,8 @@ def _cpu_attention(qkv_bits, rows, heads, hidden):
     return oracle.to_bf16(out.astype(np.float32))
 
 
-def test_block_matches_cpu_composition():
+@pytest.mark.parametrize("fuse_residual", [False, True])
+def test_block_matches_cpu_composition(fuse_residual):
     rows, hidden, heads, ffn = 160, 256, 2, 512
     rng = np.random.default_rng(7)
     (cq, wq), (co, wo), (c1, w1), (c2, w2) = (_linear(3 * hidden, hidden, rng), _linear(hidden, hidden, rng),
@@ -43,6 +44,7 @@ def test_block_matches_cpu_composition():
     weights = BlockWeights(wq, wo, w1, w2, bf16_tensor(norm1), bf16_tensor(norm2))
     mod_d = {n: dev(v) for n, v in mod_h.items()}
     block = Nvfp4Block(rows, hidden, heads, ffn)
+    block.fuse_residual = fuse_residual  # gated residuals as their own kernel, or inside the GEMM epilogues
     dx = bf16_tensor(x)
     block.forward(dx, weights, mod_d, dev(a))
     torch.cuda.synchronize()

@@ -131,6 +131,41 @@ def test_gemm_nvfp4_matches_fp4_activation_oracle(M, N, K, tile_n):
     assert np.all(np.abs(got - ref_) <= 1e-3 + 1e-2 * np.abs(ref_))
 
 
+@pytest.mark.parametrize("tile_n", [0, 256])
+@pytest.mark.parametrize("M,N,K", [(300, 512, 256), (129, 34, 256), (1000, 1280, 512)])
+def test_gemm_gated_residual_epilogue(M, N, K, tile_n):
+    # x += gate[a[r]] * (q w^T scaled + bias) in the epilogue == the plain GEMM followed by add_gated
+    # (src/cuda/nn_pointwise.cu:16-37), bit for bit, on the vectorised and the ragged store paths
+    rng = np.random.default_rng(M + N)
+    a = rng.integers(-128, 128, size=(M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
+    rs = (rng.random(M, dtype=np.float32) * 0.05 + 1e-3).astype(np.float32)
+    cs = (rng.random(N, dtype=np.float32) * 0.01 + 1e-4).astype(np.float32)
+    bias = (0.01 * rng.standard_normal(N)).astype(np.float32)
+    gate = (0.5 * rng.standard_normal((5, N))).astype(np.float32)
+    idx = rng.integers(0, 5, size=M).astype(np.int32)
+    x = gaussian_bf16((M, N), seed=M)
+    da, dw, drs, dcs, db, dg, di = dev(a), dev(w), dev(rs), dev(cs), dev(bias), dev(gate), dev(idx)
+    sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
+    try:
+        branch = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        ep = sfq.Epilogue(sfq.ptr(drs), sfq.ptr(dcs), 1.0, sfq.ptr(db), sfq.F32, sfq.ACT_NONE)
+        sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(da), sfq.ptr(dw), C.byref(ep), sfq.ptr(branch), M, N, K, S))
+        y = bf16_tensor(x)
+        ep2 = sfq.Epilogue(sfq.ptr(drs), sfq.ptr(dcs), 1.0, sfq.ptr(db), sfq.F32, sfq.ACT_NONE, sfq.ptr(dg), sfq.ptr(di))
+        sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(da), sfq.ptr(dw), C.byref(ep2), sfq.ptr(y), M, N, K, S))
+        _status_clean()
+    finally:
+        sfq.lib.sfq_gemm_tuning(0, 0, 0)
+    want = x.copy()
+    bb = bits(branch)
+    oracle.lib.orc_add_gated_bf16(P(want), P(bb), P(gate), P(idx), M, N)
+    assert np.array_equal(bits(y), want)
+    # a gate without its index (or the other way round) is refused
+    bad = sfq.Epilogue(sfq.ptr(drs), sfq.ptr(dcs), 1.0, None, sfq.F32, sfq.ACT_NONE, sfq.ptr(dg), None)
+    assert sfq.lib.sfq_gemm_int8(sfq.ptr(da), sfq.ptr(dw), C.byref(bad), sfq.ptr(y), M, N, K, S) == sfq.ERR_INVALID_ARGUMENT
+
+
 def test_gemm_nvfp4_multi_tile_persistence():
     # more 256x256 tiles than CTA pairs, ragged M, ragged last K stage: every pair walks several tiles through the one
     # accumulator and wraps the stage ring (and its scale slots) many times
