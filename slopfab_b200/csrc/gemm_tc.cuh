@@ -34,6 +34,7 @@ struct GemmArgs {
   int band_m = 0;         // row tiles per raster band (0 = default)
   int max_ctas = 0;       // 0 = one CTA per SM
   int tile_n = 0;         // 128 or 256 select the one-CTA kernel with that tile width; 0 = default (CTA pairs, 256 x 256)
+  int tail_split = -1;    // CTA-pair kernel: trailing tiles cut into two 128-column halves (-1 = let the launcher choose)
   int debug = 0;          // experiment switches (environment SFQ_GEMM_DEBUG); 0 in normal use
 };
 

@@ -12,6 +12,9 @@
 //   leader only  warp 1 issues the MMAs for the pair; its commits arrive on `empty` / `acc_full` in both CTAs.
 //                Warps 12-15 (nvfp4) copy block scales into TMEM in both CTAs (each from its own shared memory).
 //   the peer's epilogue hands the accumulator back by arriving on the LEADER's acc_empty barrier.
+// Tail of the persistent schedule: when the last wave would leave more than half of the pairs idle, its tiles are
+// cut into two 256 x 128 halves (N = 128 MMAs, 64 weight rows per CTA), so that wave takes about two thirds of a
+// full one instead of a whole one (config 2: 320 tiles over 74 pairs = 4 waves + 24 tiles -> 48 half tiles).
 // Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before TMEM is freed, so
 // neither exits while its partner can still read its shared memory or signal its barriers.
 #include "gemm_common.cuh"
@@ -37,6 +40,7 @@ template <int KIND, int ACC> struct PairCfg {
   static constexpr int kTmemCols = 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;
   static constexpr uint32_t kTxBytes = 2u * kStageBytes;  // what both CTAs land per stage (TMA counts whole boxes)
+  static constexpr uint32_t kTxBytesNarrow = 2u * (kStageA + kStageB / 2 + kStageSfa + kStageSfb / 2);  // 256 x 128 tile
   static_assert(kAccCols + kStages * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kStageBytes % 1024 == 0, "stage bases must keep the 1024-byte swizzle alignment");
   static_assert(sizeof(Shared) <= kBarrierBytes, "barrier block");
@@ -45,7 +49,9 @@ template <int KIND, int ACC> struct PairCfg {
 template <int KIND, int ACC>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, GemmArgs g) {
+                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                 const __grid_constant__ CUtensorMap map_b_narrow, const __grid_constant__ CUtensorMap map_sfb_narrow,
+                 GemmArgs g) {
   using C = PairCfg<KIND, ACC>;
   constexpr int BN = kPairBN;
   extern __shared__ uint8_t smem_raw[];
@@ -64,7 +70,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int k_stages = (row_bytes + kSlabBytes - 1) / kSlabBytes;
   const int band = g.band_m > 0 ? (g.band_m + 1) / 2 : 8;  // pair tiles (256 rows) per raster band
 
-  auto tile_coords = [&](int t, int& tm, int& tn) {
+  // Work items: the tiles in raster order, except that the last `tail_split` of them appear as two 128-column
+  // halves each. Every role decodes an item the same way.
+  const int first_split = num_tiles - g.tail_split;
+  const int num_work = num_tiles + g.tail_split;
+  auto work_item = [&](int w, int& tm, int& tn, int& n_off, int& n_cols) {
+    int t = w;
+    n_off = 0;
+    n_cols = BN;
+    if (w >= first_split) {
+      const int j = w - first_split;
+      t = first_split + (j >> 1);
+      n_off = (j & 1) * (BN / 2);
+      n_cols = BN / 2;
+    }
     const int per_band = band * tiles_n;
     const int b = t / per_band;
     const int r = t - b * per_band;
@@ -103,9 +122,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // ------------------------------------------------------------ producer (both CTAs)
       uint32_t it = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        int tm, tn;
-        tile_coords(t, tm, tn);
+      for (int t = pair; t < num_work && ok; t += num_pairs) {
+        int tm, tn, n_off, n_cols;
+        work_item(t, tm, tn, n_off, n_cols);
+        const bool narrow = n_cols != BN;
         for (int ks = 0; ks < k_stages; ++ks, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
@@ -113,13 +133,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (elect_one()) {
             uint8_t* stage = smem + s * C::kStageBytes;
             const uint32_t bar = smem_u32(&sh->full[s]);  // the loads redirect it to the leader's copy
-            if (rank == 0) mbar_arrive_expect_tx(bar, C::kTxBytes);
+            if (rank == 0) mbar_arrive_expect_tx(bar, narrow ? C::kTxBytesNarrow : C::kTxBytes);
             tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
-            tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * BN + int(rank) * (BN / 2), bar);
+            if (!narrow)
+              tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * BN + int(rank) * (BN / 2), bar);
+            else
+              tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b_narrow, ks * kSlabBytes, tn * BN + n_off + int(rank) * (BN / 4),
+                               bar);
             if constexpr (KIND == kNvfp4) {
               // scale arrays as [128-row tile][K/64 atoms of 512 bytes], 8-byte elements: 256 elements = 4 atoms
               tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB), &map_sfa, ks * 256, tm * 2 + int(rank), bar);
-              tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
+              if (!narrow)
+                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
+              else
+                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256,
+                                 tn * 2 + n_off / 128, bar);
             }
           }
           __syncwarp();
@@ -134,7 +162,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     } else if (warp == 1 && rank == 0) {
       // ------------------------------------------------------------ MMA issuer (leader)
-      constexpr uint32_t idesc = KIND == kI8 ? idesc_i8(kPairBM, BN) : (KIND == kNvfp4 ? idesc_nvfp4(kPairBM, BN) : idesc_bf16(kPairBM, BN));
+      constexpr uint32_t idesc_wide = KIND == kI8 ? idesc_i8(kPairBM, BN) : (KIND == kNvfp4 ? idesc_nvfp4(kPairBM, BN) : idesc_bf16(kPairBM, BN));
+      constexpr uint32_t idesc_narrow =
+          KIND == kI8 ? idesc_i8(kPairBM, BN / 2) : (KIND == kNvfp4 ? idesc_nvfp4(kPairBM, BN / 2) : idesc_bf16(kPairBM, BN / 2));
       bool ok = true;
       const uint32_t a_base = (smem_u32(smem) & 0x3FFFFu) >> 4;  // descriptor address fields: offset in the CTA's window
       const uint32_t b_base = (smem_u32(smem + C::kStageA) & 0x3FFFFu) >> 4;
@@ -143,11 +173,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
       int s = 0;
       uint32_t ph = 0, tile_it = 0;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_it) {
+      for (int t = pair; t < num_work && ok; t += num_pairs, ++tile_it) {
         const int a = tile_it % ACC;
         if (!(ok = wait_barrier_warp(smem_u32(&sh->acc_empty[a]), ((tile_it / ACC) & 1) ^ 1, sh, g.status, 2))) break;
         tc_fence_after_sync();
         const uint32_t d = tmem + a * BN;
+        const bool narrow = t >= first_split;
+        const uint32_t idesc = narrow ? idesc_narrow : idesc_wide;
+        const uint32_t sfb_step = narrow ? BN / 64 : BN / 32;  // TMEM columns of the weight scales per k-block
         for (int ks = 0; ks < k_stages; ++ks) {
           if constexpr (KIND == kNvfp4) {
             if (!(ok = wait_barrier_warp(smem_u32(&sh->sf_full[s]), ph, sh, g.status, 5))) break;
@@ -170,7 +203,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 else if constexpr (KIND == kBf16)
                   mma_f16_pair(d, da + adv, db + adv, idesc, acc);
                 else
-                  mma_nvfp4_pair(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * (BN / 32));
+                  mma_nvfp4_pair(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * sfb_step);
               }
             }
             tc_commit_pair(smem_u32(&sh->empty[s]), 3);  // frees the stage (and its scale slot) in both CTAs
@@ -194,7 +227,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        for (int t = pair; t < num_work && ok; t += num_pairs) {
+          const int row_tiles = t >= first_split ? 1 : 2;  // 128-row weight scale tiles of this work item
           for (int ks = 0; ks < k_stages; ++ks) {
             if (!(ok = wait_barrier_warp(smem_u32(&sh->empty[s]), ph ^ 1, sh, g.status, 7))) break;
             if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
@@ -208,7 +242,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_copy_32x128b_x4_pair(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
 #pragma unroll
                 for (int rt = 0; rt < 2; ++rt)
-                  tc_copy_32x128b_x4_pair(sf_cols + 16 + kb * (BN / 32) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
+                  if (rt < row_tiles)
+                    tc_copy_32x128b_x4_pair(sf_cols + 16 + kb * (row_tiles * 4) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
               }
               tc_commit_pair_local(smem_u32(&sh->sf_full[s]));
             }
@@ -229,15 +264,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool vec_ok = (g.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(g.y) & 15) == 0) && (g.ldy % 8 == 0);
     const bool has_bias = g.bias != nullptr;
     const uint32_t acc_empty_leader[2] = {map_to_rank(smem_u32(&sh->acc_empty[0]), 0), map_to_rank(smem_u32(&sh->acc_empty[1]), 0)};
-    for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_it) {
-      int tm, tn;
-      tile_coords(t, tm, tn);
+    for (int t = pair; t < num_work && ok; t += num_pairs, ++tile_it) {
+      int tm, tn, n_off, n_cols;
+      work_item(t, tm, tn, n_off, n_cols);
+      const int col_base = tn * BN + n_off;  // first output column of this work item
       const int a = tile_it % ACC;
       const uint32_t aph = (tile_it / ACC) & 1;
       float* cs_s = sh->col_scale[tile_it & 1];
       float* bs_s = sh->bias[tile_it & 1];
-      if (et < BN) {
-        const int col = tn * BN + et;
+      if (et < n_cols) {
+        const int col = col_base + et;
         float cs = g.global_scale, bs = 0.0f;
         if (col < g.N) {
           if constexpr (KIND == kI8) cs = __ldg(g.col_scale + col);
@@ -251,9 +287,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (g.gate != nullptr) {
         // Gated residual: the epilogue will read-modify-write this tile of y. Ask L2 for it now, a whole main loop
         // ahead, so those reads do not pay HBM latency on the store path (128 rows x BN bf16 = BN/64 lines per row).
-        constexpr int kLinesPerRow = BN / 64;
+        const int kLinesPerRow = n_cols / 64;
         for (int l = et; l < kBM * kLinesPerRow; l += 256) {
-          const int pr = tm * kPairBM + int(rank) * kBM + l / kLinesPerRow, pc = tn * BN + (l % kLinesPerRow) * 64;
+          const int pr = tm * kPairBM + int(rank) * kBM + l / kLinesPerRow, pc = col_base + (l % kLinesPerRow) * 64;
           if (pr < g.M && pc < g.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(g.y + size_t(pr) * g.ldy + pc));
         }
       }
@@ -269,8 +305,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int rows_ok = max(0, min(32, g.M - warp_row0));
       __nv_bfloat16* ywarp = g.y + size_t(min(warp_row0, g.M - 1)) * g.ldy;
       uint4* stage_w = reinterpret_cast<uint4*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes) + (warp - 4) * 128;
-      constexpr int kTileChunks = BN / 32;
-      constexpr int kMaxJ = (kTileChunks + 1) / 2;
+      const int kTileChunks = n_cols / 32;
+      constexpr int kMaxJ = (BN / 32 + 1) / 2;
       const uint32_t tbase = tmem + a * BN + (uint32_t(quad * 32) << 16);
       int gate_idx[4];
       gate_rows_for(g, warp_row0, lane, gate_idx);
@@ -286,7 +322,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
       for (int j = 0; j < kMaxJ; ++j) {
         const int c = half + 2 * j;
-        const int col0 = tn * BN + c * 32;
+        const int col0 = col_base + c * 32;
         if (c >= kTileChunks || col0 >= g.N) continue;  // warp-uniform
         const int lc0 = c * 32;
         uint4 packed[4];
@@ -382,14 +418,23 @@ bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs&
   if (pairs_fit <= 0) return false;  // no room for clusters of two: the caller uses the one-CTA kernel
   const CUtensorMap ma = make_map(a, size_t(g.M), row_bytes, kBM);
   const CUtensorMap mb = make_map(w, size_t(g.N), row_bytes, kPairBN / 2);
-  CUtensorMap msa = ma, msb = mb;  // placeholders for the kinds without scales
+  const CUtensorMap mbn = make_map(w, size_t(g.N), row_bytes, kPairBN / 4);
+  CUtensorMap msa = ma, msb = mb, msbn = mb;  // placeholders for the kinds without scales
   if constexpr (KIND == kNvfp4) {
     msa = make_scale_map(g.a_scale_tiled, size_t((g.M + 127) / 128), size_t(g.K / 64), 1);
     msb = make_scale_map(g.w_scale_tiled, size_t(g.N / 128), size_t(g.K / 64), 2);
+    msbn = make_scale_map(g.w_scale_tiled, size_t(g.N / 128), size_t(g.K / 64), 1);
   }
   const int tiles = ((g.M + kPairBM - 1) / kPairBM) * ((g.N + kPairBN - 1) / kPairBN);
-  int pairs = std::min(tiles, pairs_fit);
-  if (g.max_ctas > 0) pairs = std::max(1, std::min(pairs, g.max_ctas / 2));
+  int pairs_cap = pairs_fit;
+  if (g.max_ctas > 0) pairs_cap = std::max(1, std::min(pairs_cap, g.max_ctas / 2));
+  // Tail of the schedule: r tiles are left for the last wave. If they would occupy at most half of the pairs they
+  // are cut in two, so that wave keeps twice as many pairs busy on narrower tiles and ends sooner.
+  GemmArgs ga = g;
+  const int r = tiles % pairs_cap;
+  ga.tail_split = g.tail_split >= 0 ? std::min(g.tail_split, tiles) : ((r > 0 && 2 * r <= pairs_cap) ? r : 0);
+  if (g.debug & 1) ga.tail_split = 0;  // experiment switch: whole tiles only
+  const int pairs = std::min(tiles + ga.tail_split, pairs_cap);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kThreads);
@@ -402,7 +447,7 @@ bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs&
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, ACC>, ma, mb, msa, msb, g);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, ACC>, ma, mb, msa, msb, mbn, msbn, ga);
   if (e != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: pair launch failed: ") + cudaGetErrorString(e));
   return true;
 }
