@@ -434,8 +434,10 @@ def run_case(name):
         fn = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
                                                         C.byref(ep), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
         work = 2.0 * m * n * k
-    elif name in ("quantize_int8", "quantize_nvfp4"):
+    elif name in ("quantize_int8", "quantize_nvfp4", "quantize_int8_k13824"):
         m = 32768
+        if name == "quantize_int8_k13824":  # the FFN-down input of config 3
+            m, k, name = 16384, 13824, "quantize_int8"
         x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
         q = torch.empty((m, k), dtype=torch.int8, device="cuda")
         rs = torch.empty(m, device="cuda")

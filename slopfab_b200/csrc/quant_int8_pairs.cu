@@ -2,7 +2,8 @@
 //
 // Same bits as the fused kernel of act_quant.cu (and so as the reference's convrot_kernel followed by
 // quantize_bf16, src/cuda/linear_weights.cu:422-471 and src/cuda/w4a8.cu:193-216), for the case the W4A8 / W6A8
-// Linear runs in its chunk loop: no norm in front, rotation on, K up to 6144. That kernel is bound by instruction
+// Linear runs in its chunk loop: no norm in front, rotation on (K up to 6144 with one 16-element chunk per thread,
+// wider rows with two to four). That kernel is bound by instruction
 // issue, not by HBM, so this one halves the instruction count per row:
 //   * a thread holds its 16 elements of TWO rows as 16 fp32x2 pairs (row r in the low half, row r+1 in the high
 //     half); every butterfly add, the 1/16 scale and the quotient refinement are one add/mul/fma.rn.f32x2 for both;
@@ -211,6 +212,138 @@ quantize_int8_pairs_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restri
   }
 }
 
+// Wide rows (6144 < K <= 16384): the same arithmetic with NC chunks of 16 elements per thread. A thread rotates its
+// chunks one after the other, keeps the rotated bf16 pairs of all of them (16 words per chunk), and quantizes them
+// after the single block-wide maximum. Chunk k of thread t is chunk k * blockDim.x + t of the row, so a rotation
+// group is still 16 neighbouring threads.
+constexpr int wide_max_threads(int nc) { return nc == 2 ? 384 : (nc == 3 ? 320 : 256); }  // two CTAs per SM each
+
+template <int NC>
+__global__ void __launch_bounds__(wide_max_threads(NC), 2)
+quantize_int8_pairs_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ row_scale,
+                                int rows, int dim) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  f2* tile = reinterpret_cast<f2*>(smem) + (tid >> 4) * kGroupTile;
+  uint8_t* bytes = smem + size_t(blockDim.x >> 4) * kGroupTile * 8 + (tid >> 4) * kGroupBytesOut;
+  uint32_t* partial = reinterpret_cast<uint32_t*>(smem + size_t(blockDim.x >> 4) * (kGroupTile * 8 + kGroupBytesOut));
+  const int T = tid & 15;
+  const int pairs = (rows + 1) >> 1;
+  const f2 sixteenth = pk(0.0625f, 0.0625f);
+
+  for (int pair = blockIdx.x, iter = 0; pair < pairs; pair += gridDim.x, ++iter) {
+    const int r0 = 2 * pair;
+    const bool two = r0 + 1 < rows;
+    const uint4* s0 = reinterpret_cast<const uint4*>(x + size_t(r0) * dim);
+    const uint4* s1 = reinterpret_cast<const uint4*>(x + size_t(two ? r0 + 1 : r0) * dim);
+    auto load = [&](int k, uint4 (&r)[4]) {
+      const int c = k * blockDim.x + tid;
+      r[0] = __ldg(s0 + 2 * c);
+      r[1] = __ldg(s0 + 2 * c + 1);
+      r[2] = two ? __ldg(s1 + 2 * c) : make_uint4(0, 0, 0, 0);
+      r[3] = two ? __ldg(s1 + 2 * c + 1) : make_uint4(0, 0, 0, 0);
+    };
+    uint4 raw[2][4];  // this chunk's 64 bytes and the next chunk's, already in flight
+    load(0, raw[0]);
+    uint32_t w[NC][16];
+    uint32_t amax = 0;
+#pragma unroll
+    for (int k = 0; k < NC; ++k) {
+      if (k + 1 < NC) load(k + 1, raw[(k + 1) & 1]);
+      f2 v[16];
+      const uint4(&rk)[4] = raw[k & 1];
+      const uint32_t a[8] = {rk[0].x, rk[0].y, rk[0].z, rk[0].w, rk[1].x, rk[1].y, rk[1].z, rk[1].w};
+      const uint32_t b[8] = {rk[2].x, rk[2].y, rk[2].z, rk[2].w, rk[3].x, rk[3].y, rk[3].z, rk[3].w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[2 * i] = pku(a[i] << 16, b[i] << 16);
+        v[2 * i + 1] = pku(a[i] & 0xFFFF0000u, b[i] & 0xFFFF0000u);
+      }
+      two_stages(v);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) tile[17 * T + e] = v[e];
+      __syncwarp();
+#pragma unroll
+      for (int t = 0; t < 16; ++t) v[t] = tile[17 * t + T];
+      __syncwarp();  // the tile is rewritten by the next chunk
+      two_stages(v);
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        float lo, hi;
+        upk(mul2(v[t], sixteenth), lo, hi);
+        w[k][t] = to_bf16x2(lo, hi);
+        amax = max_bf16x2(amax, w[k][t] & 0x7FFF7FFFu);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = max_bf16x2(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    uint32_t* part = partial + (iter & 1) * 32;
+    if (lane == 0) part[warp] = amax;
+    __syncthreads();
+    uint32_t m = 0;
+    for (int i = 0; i < nwarps; ++i) m = max_bf16x2(m, part[i]);
+    const float scale0 = fmaxf(div127(__uint_as_float(m << 16)), 1e-30f);
+    const float scale1 = fmaxf(div127(__uint_as_float(m & 0xFFFF0000u)), 1e-30f);
+    if (tid == 0) {
+      row_scale[r0] = scale0;
+      if (two) row_scale[r0 + 1] = scale1;
+    }
+    const float d0 = __bfloat162float(__float2bfloat16(scale0)), d1 = __bfloat162float(__float2bfloat16(scale1));
+    const f2 rcp = pk(__frcp_rn(d0), __frcp_rn(d1));
+    const f2 negd = pk(-d0, -d1);
+#pragma unroll
+    for (int k = 0; k < NC; ++k) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const f2 xv = pku(w[k][t] << 16, w[k][t] & 0xFFFF0000u);
+        const f2 a = mul2(xv, rcp);
+        const f2 qv = fma2(fma2(a, negd, xv), rcp, a);
+        float lo, hi;
+        upk(qv, lo, hi);
+        const uint32_t qb = to_bf16x2(lo, hi);
+        const int i0 = __float2int_rn(__uint_as_float(qb << 16));
+        const int i1 = __float2int_rn(__uint_as_float(qb & 0xFFFF0000u));
+        uint32_t both;
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(both) : "r"(i1), "r"(i0), "r"(0));
+        reinterpret_cast<uint16_t*>(bytes)[16 * t + T] = uint16_t(both);
+      }
+      __syncwarp();
+      const uint4 p0 = reinterpret_cast<const uint4*>(bytes)[2 * T], p1 = reinterpret_cast<const uint4*>(bytes)[2 * T + 1];
+      __syncwarp();  // the byte block is rewritten by the next chunk
+      uint4 o0, o1;
+      o0.x = __byte_perm(p0.x, p0.y, 0x6420), o1.x = __byte_perm(p0.x, p0.y, 0x7531);
+      o0.y = __byte_perm(p0.z, p0.w, 0x6420), o1.y = __byte_perm(p0.z, p0.w, 0x7531);
+      o0.z = __byte_perm(p1.x, p1.y, 0x6420), o1.z = __byte_perm(p1.x, p1.y, 0x7531);
+      o0.w = __byte_perm(p1.z, p1.w, 0x6420), o1.w = __byte_perm(p1.z, p1.w, 0x7531);
+      const int c = k * blockDim.x + tid;
+      reinterpret_cast<uint4*>(q + size_t(r0) * dim)[c] = o0;
+      if (two) reinterpret_cast<uint4*>(q + size_t(r0 + 1) * dim)[c] = o1;
+    }
+  }
+}
+
+template <int NC>
+void launch_pairs_wide(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, int threads, cudaStream_t stream) {
+  const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 2 * 32 * sizeof(uint32_t);
+  static size_t reserved = 0;  // per instantiation
+  if (smem > 48 * 1024 && smem > reserved) {
+    const cudaError_t e = cudaFuncSetAttribute(quantize_int8_pairs_wide_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
+    reserved = smem;
+  }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_int8_pairs_wide_kernel<NC>, threads, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = std::min((rows + 1) / 2, per_sm * sms);
+  quantize_int8_pairs_wide_kernel<NC><<<grid, threads, smem, stream>>>(x, q, row_scale, rows, dim);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
+}
+
 template <int MAXT, int MINB>
 void launch_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, int threads, cudaStream_t stream) {
   const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 2 * 32 * sizeof(uint32_t);
@@ -235,8 +368,20 @@ void launch_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows,
 }  // namespace
 
 bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, cudaStream_t stream) {
-  if (dim % 256 != 0 || dim > 6144 || rows <= 0) return false;
+  if (dim % 256 != 0 || rows <= 0) return false;
   if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0) return false;
+  if (dim > 6144) {
+    // NC chunks per thread; every thread must own whole chunks and a warp whole rotation groups
+    const int chunks = dim / 16;
+    for (int nc = 2; nc <= 4; ++nc) {
+      if (chunks % nc != 0 || (chunks / nc) % 32 != 0 || chunks / nc > wide_max_threads(nc)) continue;
+      if (nc == 2) launch_pairs_wide<2>(x, q, row_scale, rows, dim, chunks / nc, stream);
+      if (nc == 3) launch_pairs_wide<3>(x, q, row_scale, rows, dim, chunks / nc, stream);
+      if (nc == 4) launch_pairs_wide<4>(x, q, row_scale, rows, dim, chunks / nc, stream);
+      return true;
+    }
+    return false;  // the one-row kernel takes it
+  }
   const int threads = ((dim / 16 + 31) / 32) * 32;
   if (threads <= 320)
     launch_pairs<320, 3>(x, q, row_scale, rows, dim, threads, stream);

@@ -141,7 +141,8 @@ def test_convrot_bit_exact(rows, dim, group):
 
 
 @pytest.mark.parametrize("rows,dim,outliers", [(3, 256, False), (33, 5120, True), (5, 13824, False), (4, 1024, True),
-                                               (1, 512, False), (2, 6144, True), (1201, 5120, True), (6, 6400, False)])
+                                               (1, 512, False), (2, 6144, True), (1201, 5120, True), (6, 6400, False),
+                                               (7, 8192, True), (3, 16384, False), (301, 13824, True)])
 def test_fused_convrot_int8_quantizer_bit_exact(rows, dim, outliers):
     x = gaussian_bf16((rows, dim), seed=rows + dim, outliers=outliers)
     x[0] = 0  # a zero row: scale floors at 1e-30, codes all zero
