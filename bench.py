@@ -496,8 +496,163 @@ def run_block_stack(blocks=40, rows=75600, hidden=5120, heads=40, ffn=13824):
                       "finite": bool(torch.isfinite(x.float()).all().item()), "device_status": sfq.device_status()}))
 
 
+def run_config3(rows=32760, hidden=5120, ffn=13824, group=64, reps=5):
+    """BASELINE config 3: W6A8 FFN pair at 32760 tokens through the runner: prepare() once per layer (the int8
+    expansion), then up-projection with GELU-tanh in the epilogue and down-projection, as a DiT chunk loop does."""
+    import torch
+
+    import slopfab_b200 as sfq
+
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(2)
+
+    def w6(n, k):
+        packed = torch.randint(0, 256, (n, k * 3 // 4), dtype=torch.uint8, device="cuda", generator=g).view(torch.int8)
+        s_rel = torch.randint(0x28, 0x39, (n * k // group,), dtype=torch.uint8, device="cuda", generator=g)
+        s_ch = (torch.rand(n, device="cuda", generator=g) + 1.0) * 2.0 ** -8
+        return (packed, s_rel, s_ch), sfq.new_weight(format=sfq.W6A8, data=sfq.ptr(packed), out_features=n, in_features=k,
+                                                     block_scale=sfq.ptr(s_rel), weight_scale=sfq.ptr(s_ch),
+                                                     packed_group_size=group, convrot=1, convrot_group=256)
+
+    keep_up, w_up = w6(ffn, hidden)
+    keep_dn, w_dn = w6(hidden, ffn)
+    x = torch.randn((rows, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    h = torch.empty((rows, ffn), dtype=torch.bfloat16, device="cuda")
+    y = torch.empty((rows, hidden), dtype=torch.bfloat16, device="cuda")
+    up, dn = sfq.LinearRunner(), sfq.LinearRunner()
+    up.set_activation(sfq.ACT_GELU_TANH)
+    up.reserve(up.workspace_bytes(w_up, rows))
+    dn.reserve(dn.workspace_bytes(w_dn, rows))
+    p_up, used_up = up.prepare(w_up, rows)
+    p_dn, used_dn = dn.prepare(w_dn, rows)
+
+    def pair(i):
+        up.forward_prepared(w_up, p_up, used_up, x, h)
+        dn.forward_prepared(w_dn, p_dn, used_dn, h, y)
+
+    pair(0)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_up = t_dn = 0.0
+    for _ in range(reps):
+        ev[0].record()
+        up.forward_prepared(w_up, p_up, used_up, x, h)
+        ev[1].record()
+        dn.forward_prepared(w_dn, p_dn, used_dn, h, y)
+        ev[2].record()
+        ev[2].synchronize()
+        t_up += ev[0].elapsed_time(ev[1]) / reps
+        t_dn += ev[1].elapsed_time(ev[2]) / reps
+    flops = 2.0 * rows * hidden * ffn
+    print(json.dumps({"case": "config3_w6a8_ffn_pair", "tokens": rows, "up_ms": t_up, "down_ms": t_dn,
+                      "up_tflops": flops / (t_up * 1e-3) / 1e12, "down_tflops": flops / (t_dn * 1e-3) / 1e12,
+                      "pair_tflops": 2 * flops / ((t_up + t_dn) * 1e-3) / 1e12,
+                      "note": "each projection = fused ConvRot + int8 quantizer + int8 GEMM with fused epilogue; "
+                              "the W6 -> int8 expansion is done once by prepare() and not in these times",
+                      "finite": bool(torch.isfinite(y.float()).all().item()), "device_status": sfq.device_status()}))
+
+
+def run_config5(steps=5):
+    """BASELINE config 5: NVFP4 and W4A8 DiT Linears at M = 31x45x80 = 111600 tokens, token-sharded over the ranks
+    of this launch (weights replicated, no collective), plus the FFN-up column split with one all-gather. Launch
+    under torch.distributed.run for more than one GPU. One JSON line per (kind, shape, scheme), aggregate TFLOP/s."""
+    import torch
+    import torch.distributed as dist
+
+    import slopfab_b200 as sfq
+    from slopfab_b200.parallel import ColumnSplitPlan, column_shard, token_shard
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = load_peaks()
+    M = 31 * 45 * 80
+    _, m = token_shard(M, world, rank)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    import ctypes as C
+
+    def timed(fn):
+        for i in range(2):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            fn()
+        b.record()
+        b.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    for kname, k, n in (("attn_proj", 5120, 5120), ("ffn_up", 5120, 13824), ("ffn_down", 13824, 5120)):
+        x = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        # ---- W4A8: int8 expansion held (what prepare() keeps for a chunk loop), fused quantizer + GEMM per call
+        w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+        cs = torch.rand(n, device="cuda", generator=g) * 0.01
+        q = torch.empty((m, k), dtype=torch.int8, device="cuda")
+        rs = torch.empty(m, device="cuda")
+        ep8 = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
+
+        def w4a8():
+            sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(x), None, sfq.ptr(q), sfq.ptr(rs), None, m, k, 1, sfq.stream_ptr()))
+            sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(q), sfq.ptr(w8), C.byref(ep8), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
+
+        # ---- NVFP4 native
+        wq = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        wsf = torch.randint(0x30, 0x40, (n * k // 16,), dtype=torch.uint8, device="cuda", generator=g)
+        xq = torch.empty((m, k // 2), dtype=torch.uint8, device="cuda")
+        xsf = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(m, k), dtype=torch.uint8, device="cuda")
+        ep4 = sfq.Epilogue(None, None, 1e-3, None, sfq.F32, sfq.ACT_NONE)
+
+        def nvfp4():
+            sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(x), None, sfq.ptr(xq), sfq.ptr(xsf), None, m, k,
+                                                       sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
+            sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(xq), sfq.ptr(xsf), sfq.ptr(wq), sfq.ptr(wsf), C.byref(ep4), sfq.ptr(y), m, n, k,
+                                             sfq.stream_ptr()))
+
+        flops = 2.0 * M * n * k
+        for kind, fn, mult in (("w4a8", w4a8, 2), ("nvfp4", nvfp4, 4)):
+            ms = timed(fn)
+            if rank == 0:
+                tf = flops / (ms * 1e-3) / 1e12
+                print(json.dumps({"case": "config5", "kind": kind, "linear": kname, "scheme": "token-sharded", "n_gpus": world,
+                                  "tokens": M, "ms": ms, "tflops": tf,
+                                  "frac_of_peak": tf / (world * mult * peaks["bf16_tflops"]),
+                                  "peak_note": f"{mult} x measured dense bf16 burst per GPU"}), flush=True)
+        if kname == "ffn_up" and M % world == 0:
+            c0, nl = column_shard(n, world, rank)
+            plans = {"w4a8": ColumnSplitPlan("w4a8", m, k, nl, (w8[c0:c0 + nl].contiguous(), cs[c0:c0 + nl].contiguous()), world),
+                     "nvfp4": ColumnSplitPlan("nvfp4", m, k, nl, (wq[c0:c0 + nl].contiguous(),
+                                                                  wsf.view(n // 128, -1)[c0 // 128:(c0 + nl) // 128].contiguous().view(-1), 1e-3), world)}
+            for kind, mult in (("w4a8", 2), ("nvfp4", 4)):
+                ms = timed(lambda: plans[kind].forward(x))
+                if rank == 0:
+                    tf = flops / (ms * 1e-3) / 1e12
+                    print(json.dumps({"case": "config5", "kind": kind, "linear": kname, "scheme": "column-split, one all-gather",
+                                      "n_gpus": world, "tokens": M, "ms": ms, "tflops": tf,
+                                      "frac_of_peak": tf / (world * mult * peaks["bf16_tflops"]),
+                                      "gathered_bytes_per_gpu": plans[kind].block * (world - 1)}), flush=True)
+            del plans
+        del x, y, w8, q, wq, wsf, xq, xsf
+        torch.cuda.empty_cache()
+    st = sfq.device_status()
+    if rank == 0:
+        print(json.dumps({"case": "config5", "device_status": st}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--config5", action="store_true",
+                    help="run BASELINE config 5 (M=111600 scaling sweep) on the ranks of this launch and exit")
+    ap.add_argument("--config3", action="store_true", help="run BASELINE config 3 (W6A8 FFN pair, M=32760) and exit")
     ap.add_argument("--block-stack", type=int, default=0, metavar="BLOCKS",
                     help="run BASELINE config 4 (NVFP4 DiT block stack at 75600 tokens) with this many blocks and exit")
     ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu) and exit: gemm_int8, "
@@ -508,6 +663,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extra", action="store_true", help="also time the GEMMs at the other DiT shapes (1 GPU)")
     args = ap.parse_args()
+    if args.config3:
+        run_config3()
+        return
+    if args.config5:
+        run_config5()
+        return
     if args.case:
         run_case(args.case)
         return

@@ -103,3 +103,61 @@ def column_split_w4a8_forward(x_local: torch.Tensor, w8_cols: torch.Tensor, col_
         return y
 
     return column_split_int8_forward(quantize, gemm, x_local.contiguous(), group)
+
+
+class ColumnSplitPlan:
+    """FFN-up column split with preallocated buffers and equal token counts per rank (the benchmark's case).
+
+    Every rank quantizes its own `m` token rows straight into one send block [quantized rows | their scales],
+    ONE all-gather brings every rank's block into local memory, and the local weight columns are multiplied
+    block by block (one GEMM launch per source rank, so a block's GEMM never waits for a repack). Kinds: "w4a8"
+    (int8 rows + fp32 row scales; `weight` = (int8 [n_local, K], col_scale fp32 [n_local])) and "nvfp4" (fp4 rows +
+    128x4-tiled e4m3 scales; `weight` = (u8 [n_local, K/2], tiled scales, global_scale)).
+    """
+
+    def __init__(self, kind: str, m: int, k: int, n_local: int, weight, world: int, device="cuda", activation: int = 0):
+        from . import lib
+
+        if kind not in ("w4a8", "nvfp4"):
+            raise ValueError("ColumnSplitPlan: kind must be 'w4a8' or 'nvfp4'")
+        self.kind, self.m, self.k, self.n, self.world, self.weight, self.activation = kind, m, k, n_local, world, weight, activation
+        if kind == "w4a8":
+            self.q_bytes, self.s_bytes = m * k, 4 * m
+        else:
+            self.q_bytes, self.s_bytes = m * k // 2, lib.sfq_nvfp4_act_scale_bytes(m, k)
+        self.q_bytes_padded = (self.q_bytes + 255) // 256 * 256
+        self.block = self.q_bytes_padded + (self.s_bytes + 255) // 256 * 256
+        self.send = torch.zeros(self.block, dtype=torch.uint8, device=device)
+        self.recv = torch.empty(world * self.block, dtype=torch.uint8, device=device)
+        self.y = torch.empty((world * m, n_local), dtype=torch.bfloat16, device=device)
+
+    def forward(self, x_local: torch.Tensor, group=None) -> torch.Tensor:
+        """x_local bf16 [m, K] -> bf16 [world * m, n_local]: this rank's columns for all tokens."""
+        import ctypes as C
+
+        from . import F32, NVFP4_ACT_GEMM_FEED, Epilogue, check, lib, ptr, stream_ptr
+
+        m, k, n = self.m, self.k, self.n
+        q_ptr, s_ptr = ptr(self.send), ptr(self.send) + self.q_bytes_padded
+        if self.kind == "w4a8":
+            check(lib.sfq_quantize_int8_token(ptr(x_local), None, q_ptr, s_ptr, None, m, k, 1, stream_ptr()))
+        else:
+            check(lib.sfq_quantize_nvfp4_block(ptr(x_local), None, q_ptr, s_ptr, None, m, k, NVFP4_ACT_GEMM_FEED, stream_ptr()))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.recv, self.send, group=group)  # the one collective
+            base = ptr(self.recv)
+        else:
+            base = ptr(self.send)
+        for r in range(self.world):
+            qb = base + r * self.block
+            sb = qb + self.q_bytes_padded
+            yb = ptr(self.y) + r * m * n * 2
+            if self.kind == "w4a8":
+                w8, col_scale = self.weight
+                ep = Epilogue(sb, ptr(col_scale), 1.0, None, F32, self.activation)
+                check(lib.sfq_gemm_int8(qb, ptr(w8), C.byref(ep), yb, m, n, k, stream_ptr()))
+            else:
+                data, scale, g = self.weight
+                ep = Epilogue(None, None, g, None, F32, self.activation)
+                check(lib.sfq_gemm_nvfp4(qb, sb, ptr(data), ptr(scale), C.byref(ep), yb, m, n, k, stream_ptr()))
+        return self.y

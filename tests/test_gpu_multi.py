@@ -24,7 +24,8 @@ def _worker(rank, world, port, out):
     import oracle
     import slopfab_b200 as sfq
     from helpers import bf16_tensor, dev, gaussian_bf16, synthetic_packed_int8
-    from slopfab_b200.parallel import column_shard, column_split_w4a8_forward, token_shard
+    from slopfab_b200.parallel import ColumnSplitPlan, column_shard, column_split_w4a8_forward, token_shard
+    from helpers import pack_nvfp4
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -51,6 +52,39 @@ def _worker(rank, world, port, out):
         # token sharding: this rank's rows through the ordinary runner equal the same rows of the full result
         mine = sfq.LinearRunner().forward(w, bf16_tensor(np.ascontiguousarray(x[r0:r0 + rc])))
         ok = ok and torch.equal(mine.view(torch.int16), full[r0:r0 + rc].view(torch.int16))
+        # the preallocated plan (equal token counts per rank): int8 and fp4 activations, one all-gather each
+        import ctypes as C
+        Me = 1024
+        xe = gaussian_bf16((Me, K), seed=9)
+        me = Me // world
+        xl = bf16_tensor(np.ascontiguousarray(xe[rank * me:(rank + 1) * me]))
+        plan = ColumnSplitPlan("w4a8", me, K, cc, (w8[c0:c0 + cc].contiguous(), keep[2][c0:c0 + cc].contiguous()), world)
+        got = plan.forward(xl)
+        q = torch.empty((Me, K), dtype=torch.int8, device="cuda")
+        rs = torch.empty(Me, device="cuda")
+        xa = bf16_tensor(xe)
+        sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(xa), None, sfq.ptr(q), sfq.ptr(rs), None, Me, K, 1, sfq.stream_ptr()))
+        want = torch.empty((Me, N), dtype=torch.bfloat16, device="cuda")
+        ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(keep[2]), 1.0, None, sfq.F32, sfq.ACT_NONE)
+        sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(q), sfq.ptr(w8), C.byref(ep), sfq.ptr(want), Me, N, K, sfq.stream_ptr()))
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(got.view(torch.int16), want[:, c0:c0 + cc].contiguous().view(torch.int16))
+        wf = (0.02 * np.random.default_rng(10).standard_normal((N, K))).astype(np.float32)
+        data, scale, gs = pack_nvfp4(wf)
+        dd, ds = dev(data), dev(scale)
+        plan4 = ColumnSplitPlan("nvfp4", me, K, cc, (dd[c0:c0 + cc].contiguous(),
+                                                     ds.view(N // 128, -1)[c0 // 128:(c0 + cc) // 128].contiguous().view(-1), gs), world)
+        got4 = plan4.forward(xl)
+        xq = torch.empty((Me, K // 2), dtype=torch.uint8, device="cuda")
+        xs = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(Me, K), dtype=torch.uint8, device="cuda")
+        sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(xa), None, sfq.ptr(xq), sfq.ptr(xs), None, Me, K,
+                                                   sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
+        want4 = torch.empty((Me, N), dtype=torch.bfloat16, device="cuda")
+        ep4 = sfq.Epilogue(None, None, gs, None, sfq.F32, sfq.ACT_NONE)
+        sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(xq), sfq.ptr(xs), sfq.ptr(dd), sfq.ptr(ds), C.byref(ep4), sfq.ptr(want4), Me, N, K,
+                                         sfq.stream_ptr()))
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(got4.view(torch.int16), want4[:, c0:c0 + cc].contiguous().view(torch.int16))
         ok = ok and sfq.device_status() == 0
         flag = torch.tensor([1 if ok else 0], device="cuda")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
