@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--extra]
 
-Workload (config.workload): BASELINE config 2 -- the W4A8 attention projection, M=4096 tokens,
+Workload (config.workload): benchmark configuration 2 -- the W4A8 attention projection, M=4096 tokens,
 K=N=5120, weights ~N(0,0.02) packed by the library's W4A8 packer, activations bf16 ~N(0,1) with
 0.1 % outliers x20, fp32 bias, seed 1. A step is one LinearRunner.forward: expand the packed weight,
 fused ConvRot + per-token int8, tcgen05 int8 GEMM with the scale/bias epilogue (3 launches).
@@ -460,7 +460,7 @@ def run_case(name):
 
 
 def run_block_stack(blocks=40, rows=75600, hidden=5120, heads=40, ffn=13824):
-    """BASELINE config 4: NVFP4 DiT block stack, random init, 21x45x80 = 75600 tokens. Reports the Linear-path
+    """benchmark configuration 4: NVFP4 DiT block stack, random init, 21x45x80 = 75600 tokens. Reports the Linear-path
     milliseconds (norm+quant, GEMMs, gated residuals) and the whole-block milliseconds; attention is torch SDPA."""
     import torch
 
@@ -497,7 +497,7 @@ def run_block_stack(blocks=40, rows=75600, hidden=5120, heads=40, ffn=13824):
 
 
 def run_config3(rows=32760, hidden=5120, ffn=13824, group=64, reps=5):
-    """BASELINE config 3: W6A8 FFN pair at 32760 tokens through the runner: prepare() once per layer (the int8
+    """benchmark configuration 3: W6A8 FFN pair at 32760 tokens through the runner: prepare() once per layer (the int8
     expansion), then up-projection with GELU-tanh in the epilogue and down-projection, as a DiT chunk loop does."""
     import torch
 
@@ -553,7 +553,7 @@ def run_config3(rows=32760, hidden=5120, ffn=13824, group=64, reps=5):
 
 
 def run_config5(steps=5):
-    """BASELINE config 5: NVFP4 and W4A8 DiT Linears at M = 31x45x80 = 111600 tokens, token-sharded over the ranks
+    """benchmark configuration 5: NVFP4 and W4A8 DiT Linears at M = 31x45x80 = 111600 tokens, token-sharded over the ranks
     of this launch (weights replicated, no collective), plus the FFN-up column split with one all-gather. Launch
     under torch.distributed.run for more than one GPU. One JSON line per (kind, shape, scheme), aggregate TFLOP/s."""
     import torch
@@ -651,10 +651,10 @@ def run_config5(steps=5):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config5", action="store_true",
-                    help="run BASELINE config 5 (M=111600 scaling sweep) on the ranks of this launch and exit")
-    ap.add_argument("--config3", action="store_true", help="run BASELINE config 3 (W6A8 FFN pair, M=32760) and exit")
+                    help="run benchmark configuration 5 (M=111600 scaling sweep) on the ranks of this launch and exit")
+    ap.add_argument("--config3", action="store_true", help="run benchmark configuration 3 (W6A8 FFN pair, M=32760) and exit")
     ap.add_argument("--block-stack", type=int, default=0, metavar="BLOCKS",
-                    help="run BASELINE config 4 (NVFP4 DiT block stack at 75600 tokens) with this many blocks and exit")
+                    help="run benchmark configuration 4 (NVFP4 DiT block stack at 75600 tokens) with this many blocks and exit")
     ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu) and exit: gemm_int8, "
                     "gemm_nvfp4, quantize_int8, quantize_nvfp4")
     ap.add_argument("--gpus", type=int, default=1)
