@@ -3,6 +3,7 @@
 // each thread handles one 16-element scale group with 128-bit stores.
 #include "kernels.cuh"
 
+#include <algorithm>
 #include <stdexcept>
 #include <string>
 
@@ -49,32 +50,66 @@ unpack_nvfp4_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict_
 
 // q = clamp(rint(codebook[code] * e4m3(scale[row, col/16])), -127, 127), byte = even | odd << 4
 // (dequant_weight_kernel, src/cuda/w4a8.cu:44-68).
+//
+// A group's 16 outputs depend only on its scale byte and its codes, and there are 256 scale bytes: every CTA first
+// builds the table q[scale byte][code] (4 KB of shared memory, the reference's expression evaluated once per
+// entry), then walks groups. For a group, one 16-byte shared load fetches the table row of its scale; four codes
+// at a time are looked up with byte permutes (two 8-entry halves of the row, selected by bit 3 of each code), so a
+// group costs ~30 instructions instead of ~170 and the kernel runs at memory speed.
 __global__ void __launch_bounds__(kThreads)
 unpack_w4a8_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ gscale,
                    const float* __restrict__ codebook, int8_t* __restrict__ out, size_t groups) {
-  __shared__ float book[16];
-  if (threadIdx.x < 16) book[threadIdx.x] = codebook[threadIdx.x];
-  __syncthreads();
-  const size_t g = size_t(blockIdx.x) * kThreads + threadIdx.x;  // one group of 16 codes = 8 bytes
-  if (g >= groups) return;
-  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(packed) + g);
-  const float s = e4m3_decode(__ldg(gscale + g));
-  const uint32_t words[2] = {raw.x, raw.y};
-  uint32_t o[4];
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    uint32_t acc = 0;
+  __shared__ __align__(16) uint8_t table[256 * 16];
+  {
+    // thread t builds the row of scale byte t (kThreads == 256): decode the scale once, sixteen products
+    const float s = e4m3_decode(uint8_t(threadIdx.x));
+    uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int e = w * 4 + j;  // element in the group
-      const uint32_t byte = (words[e >> 3] >> (8 * ((e >> 1) & 3))) & 0xFFu;
-      const uint32_t code = (e & 1) ? (byte >> 4) : (byte & 15u);
-      const int q = max(-127, min(127, __float2int_rn(book[code] * s)));
-      acc |= uint32_t(uint8_t(q)) << (8 * j);
+      const float4 c = __ldg(reinterpret_cast<const float4*>(codebook) + j);
+      const float cc[4] = {c.x, c.y, c.z, c.w};
+      uint32_t acc = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        // NaN scale bytes (0x7F, 0xFF) never occur in valid files; the integer conversion turns NaN into 0
+        const int q = max(-127, min(127, __float2int_rn(cc[i] * s)));
+        acc |= uint32_t(uint8_t(q)) << (8 * i);
+      }
+      w[j] = acc;
     }
-    o[w] = acc;
+    reinterpret_cast<uint4*>(table)[threadIdx.x] = make_uint4(w[0], w[1], w[2], w[3]);
   }
-  reinterpret_cast<uint4*>(out)[g] = make_uint4(o[0], o[1], o[2], o[3]);
+  __syncthreads();
+  const uint4* rows = reinterpret_cast<const uint4*>(table);
+  auto expand = [&](const uint2 raw, const uint4 row, size_t g) {
+    const uint32_t words[2] = {raw.x, raw.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint32_t codes = (words[w >> 1] >> (16 * (w & 1))) & 0xFFFFu;      // four nibbles = elements 4w .. 4w+3
+      const uint32_t sel = codes & 0x7777u;                                   // index inside an 8-entry half
+      const uint32_t lo = __byte_perm(row.x, row.y, sel), hi = __byte_perm(row.z, row.w, sel);
+      // bit 3 of each code, spread to a full-byte mask in that element's output byte
+      const uint32_t b3 = ((codes >> 3) & 1u) | ((codes >> 7) & 1u) << 8 | ((codes >> 11) & 1u) << 16 | ((codes >> 15) & 1u) << 24;
+      const uint32_t mask = b3 * 0xFFu;
+      o[w] = (lo & ~mask) | (hi & mask);
+    }
+    reinterpret_cast<uint4*>(out)[g] = make_uint4(o[0], o[1], o[2], o[3]);
+  };
+  const size_t stride = size_t(gridDim.x) * kThreads;
+  size_t g = size_t(blockIdx.x) * kThreads + threadIdx.x;
+  for (; g + 3 * stride < groups; g += 4 * stride) {  // four groups per trip: eight independent loads in flight
+    uint2 raw[4];
+    uint8_t sc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      raw[u] = __ldg(reinterpret_cast<const uint2*>(packed) + g + u * stride);  // 16 codes, element e in nibble e
+      sc[u] = __ldg(gscale + g + u * stride);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) expand(raw[u], rows[sc[u]], g + u * stride);  // rows[s]: q for codes 0..15 at scale s
+  }
+  for (; g < groups; g += stride) expand(__ldg(reinterpret_cast<const uint2*>(packed) + g), rows[__ldg(gscale + g)], g);
 }
 
 // Row = K/2 low-nibble bytes then K/4 bytes of 2-bit highs (shifts 0,2,4,6);
@@ -286,8 +321,11 @@ void unpack_w4a8_int8(const int8_t* packed, const uint8_t* gscale, const float* 
   if (out_features <= 0 || in_features <= 0 || group != 16 || in_features % 16 != 0)
     throw std::invalid_argument("W4A8 weight decode: needs positive dims, group 16 and in_features % 16 == 0");
   const size_t groups = size_t(out_features) * (in_features / 16);
-  unpack_w4a8_kernel<<<blocks_for(groups, kThreads), kThreads, 0, stream>>>(reinterpret_cast<const uint8_t*>(packed),
-                                                                           gscale, codebook, out, groups);
+  // every CTA first spends one table row per thread, so give each one many groups
+  static_assert(kThreads == 256, "one table row per thread");
+  if (reinterpret_cast<uintptr_t>(codebook) % 16 != 0) throw std::invalid_argument("W4A8 weight decode: codebook must be 16-byte aligned");
+  const unsigned grid = unsigned(std::min<size_t>(blocks_for(groups, kThreads), size_t(148) * 4));
+  unpack_w4a8_kernel<<<grid, kThreads, 0, stream>>>(reinterpret_cast<const uint8_t*>(packed), gscale, codebook, out, groups);
   check_launch("unpack_w4a8");
 }
 
