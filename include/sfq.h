@@ -56,7 +56,11 @@ typedef enum { SFQ_COMPUTE_BF16 = 0, SFQ_COMPUTE_F32 = 1 } sfq_compute;
 
 /* Fused activation of the GEMM epilogue. GELU-tanh is the arithmetic of
  * launch_gelu_tanh (src/cuda/nn_pointwise.cu:74-81) applied to the bf16 result. */
-typedef enum { SFQ_ACT_NONE = 0, SFQ_ACT_GELU_TANH = 1 } sfq_activation;
+/* SFQ_ACT_SWIGLU: the weight's N rows are [gate (N/2) | up (N/2)] as in the reference's fused mlp.fc1, and the output has
+ * N/2 columns: y[r, i] = bf16(silu(g) * u) with g, u the bf16 values a plain epilogue would have stored at columns i and
+ * N/2 + i (launch_swiglu, include/slopfab/cuda/nn_kernels.cuh; swiglu_kernel, src/cuda/nn_pointwise.cu:44-64). Needs
+ * N % 256 == 0; not combined with the gated residual. */
+typedef enum { SFQ_ACT_NONE = 0, SFQ_ACT_GELU_TANH = 1, SFQ_ACT_SWIGLU = 2 } sfq_activation;
 
 /* Layout of quantized NVFP4 activations.
  * REFERENCE: low nibble = even element, scales row-major [rows, dim/16]

@@ -125,7 +125,8 @@ public:
   void init(cublasHandle_t handle, cudaStream_t stream);
   void set_native(bool enable) { native_ = enable; }
   bool native() const { return native_; }
-  // Extension: activation fused into the GEMM epilogue (sfq_activation). Default none.
+  // Extension: activation fused into the GEMM epilogue (sfq_activation). Default none. With SFQ_ACT_SWIGLU the weight's
+  // rows are [gate | up] and y is [rows, out_features / 2].
   void set_activation(int activation) { activation_ = activation; }
 
   void forward(const QuantWeight& w, const __nv_bfloat16* x, int rows, __nv_bfloat16* y, Workspace& ws);

@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libsfq.so")
 OK, ERR_INVALID_ARGUMENT, ERR_RUNTIME, ERR_OUT_OF_MEMORY, ERR_DEVICE_TIMEOUT = 0, -1, -2, -3, -4
 F32, F16, BF16, F8E4M3, I8, NVFP4, NF4, W4A8, W6A8 = range(9)
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
-ACT_NONE, ACT_GELU_TANH = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_SWIGLU = 0, 1, 2
 NVFP4_ACT_REFERENCE, NVFP4_ACT_GEMM_FEED = 0, 1
 
 V, I, U32, F, SZ = C.c_void_p, C.c_int, C.c_uint32, C.c_float, C.c_size_t

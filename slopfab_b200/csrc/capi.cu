@@ -102,9 +102,10 @@ sfq::GemmArgs to_gemm(const sfq_epilogue* ep, void* y, int M, int N, int K) {
     if (ep->d_bias != nullptr && ep->bias_format != SFQ_F32 && ep->bias_format != SFQ_BF16)
       throw std::invalid_argument("sfq gemm: bias must be fp32 or bf16");
     g.bias_is_bf16 = ep->bias_format == SFQ_BF16;
-    if (ep->activation != SFQ_ACT_NONE && ep->activation != SFQ_ACT_GELU_TANH)
+    if (ep->activation != SFQ_ACT_NONE && ep->activation != SFQ_ACT_GELU_TANH && ep->activation != SFQ_ACT_SWIGLU)
       throw std::invalid_argument("sfq gemm: unknown activation");
     g.act = ep->activation;
+    if (g.act == SFQ_ACT_SWIGLU) g.ldy = N / 2;  // the output has one column per (gate, up) pair
     if ((ep->d_gate != nullptr) != (ep->d_gate_index != nullptr))
       throw std::invalid_argument("sfq gemm: the gated residual needs both the gate table and the row index");
     if (reinterpret_cast<uintptr_t>(ep->d_gate) % 16 != 0)

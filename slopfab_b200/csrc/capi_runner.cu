@@ -60,7 +60,7 @@ int sfq_runner_native(const sfq_runner* r) { return r != nullptr && r->runner.na
 int sfq_runner_set_activation(sfq_runner* r, int activation) {
   return guarded([&] {
     if (r == nullptr) throw std::invalid_argument("sfq: null runner");
-    if (activation != SFQ_ACT_NONE && activation != SFQ_ACT_GELU_TANH)
+    if (activation != SFQ_ACT_NONE && activation != SFQ_ACT_GELU_TANH && activation != SFQ_ACT_SWIGLU)
       throw std::invalid_argument("sfq: unknown activation");
     r->runner.set_activation(activation);
   });

@@ -67,6 +67,22 @@ __device__ __forceinline__ float gelu_tanh_ref(float v) {
   return 0.5f * v * (1.0f + tanhf(k * (v + 0.044715f * v * v * v)));
 }
 
+// out = silu(gate) * up on bf16 inputs, fast exponential and IEEE division as in swiglu_kernel
+// (src/cuda/nn_pointwise.cu:44-64): 32 columns of one row, gate and up already rounded like a stored GEMM output.
+__device__ __forceinline__ void swiglu_chunk(const uint4 (&gate)[4], const uint4 (&up)[4], uint4 (&out)[4]) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gate[v]);
+    const __nv_bfloat162* up2 = reinterpret_cast<const __nv_bfloat162*>(&up[v]);
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&out[v]);
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const float2 g = __bfloat1622float2(gp[h]), u = __bfloat1622float2(up2[h]);
+      op[h] = __floats2bfloat162_rn((g.x / (1.0f + __expf(-g.x))) * u.x, (g.y / (1.0f + __expf(-g.y))) * u.y);
+    }
+  }
+}
+
 // Rounding points of the epilogue, as in the reference: the GEMM result is rounded to bf16 (output_bf16 /
 // the GEMM's own store), the bias is added to that bf16 value and re-rounded (add_bias_kernel,
 // src/cuda/linear_weights.cu:483-491), and GELU runs in place on the bf16 result.

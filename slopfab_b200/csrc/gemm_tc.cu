@@ -391,6 +391,10 @@ void gemm_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t
     throw std::invalid_argument("sfq gemm int8: null operand");
   // Default: CTA pairs on 256 x 256 tiles once there are at least two 128-row tiles to pair up. tile_n = 256 or
   // 128 selects the one-CTA kernel with that tile width (256 is the faster of the two at every DiT shape).
+  if (g.act == SFQ_ACT_SWIGLU) {  // only the CTA-pair kernel pairs gate and up columns in one tile
+    if (!gemm_pair_int8(a, w, g, stream)) throw std::runtime_error("sfq gemm int8: the SwiGLU epilogue needs the CTA-pair kernel, which this device cannot schedule");
+    return;
+  }
   if (g.tile_n == 0 && g.M > kBM && gemm_pair_int8(a, w, g, stream)) return;
   if (g.tile_n == 128)
     launch<kI8, 128, 2>(a, w, size_t(g.K), g, stream);
@@ -406,6 +410,10 @@ void gemm_nvfp4(const uint8_t* a, const uint8_t* w, const GemmArgs& g, cudaStrea
     throw std::invalid_argument("sfq gemm nvfp4: null operand");
   // One-CTA form: a 256-wide tile has one accumulator (256 columns + the scale slots); 128-wide tiles have two
   // but feed the tensor pipe less efficiently.
+  if (g.act == SFQ_ACT_SWIGLU) {  // only the CTA-pair kernel pairs gate and up columns in one tile
+    if (!gemm_pair_nvfp4(a, w, g, stream)) throw std::runtime_error("sfq gemm nvfp4: the SwiGLU epilogue needs the CTA-pair kernel, which this device cannot schedule");
+    return;
+  }
   if (g.tile_n == 0 && g.M > kBM && gemm_pair_nvfp4(a, w, g, stream)) return;
   if (g.tile_n == 128)
     launch<kNvfp4, 128, 2>(a, w, size_t(g.K) / 2, g, stream);
@@ -417,6 +425,10 @@ void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g
   if (g.M <= 0 || g.N <= 0) return;
   if (g.K <= 0 || g.K % 8 != 0) throw std::invalid_argument("sfq gemm bf16: K must be a positive multiple of 8");
   if (!a || !w || !g.y || !g.status) throw std::invalid_argument("sfq gemm bf16: null operand");
+  if (g.act == SFQ_ACT_SWIGLU) {  // only the CTA-pair kernel pairs gate and up columns in one tile
+    if (!gemm_pair_bf16(a, w, g, stream)) throw std::runtime_error("sfq gemm bf16: the SwiGLU epilogue needs the CTA-pair kernel, which this device cannot schedule");
+    return;
+  }
   if (g.tile_n == 0 && g.M > kBM && gemm_pair_bf16(a, w, g, stream)) return;
   if (g.tile_n == 128)
     launch<kBf16, 128, 2>(a, w, size_t(g.K) * 2, g, stream);

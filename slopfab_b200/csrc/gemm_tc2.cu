@@ -64,7 +64,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int tiles_m = (g.M + kPairBM - 1) / kPairBM;
-  const int tiles_n = (g.N + BN - 1) / BN;
+  // SwiGLU epilogue: the weight rows are [gate | up], `inner` each, and a tile pairs 128 gate columns (the leader's
+  // weight rows) with the 128 up columns of the same outputs (the peer's), so both meet in one accumulator row.
+  const bool swiglu = g.act == SFQ_ACT_SWIGLU;
+  const int inner = g.N / 2;
+  const int tiles_n = swiglu ? inner / (BN / 2) : (g.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int row_bytes = KIND == kNvfp4 ? g.K / 2 : (KIND == kBf16 ? g.K * 2 : g.K);
   const int k_stages = (row_bytes + kSlabBytes - 1) / kSlabBytes;
@@ -135,7 +139,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t bar = smem_u32(&sh->full[s]);  // the loads redirect it to the leader's copy
             if (rank == 0) mbar_arrive_expect_tx(bar, narrow ? C::kTxBytesNarrow : C::kTxBytes);
             tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
-            if (!narrow)
+            if (swiglu)
+              tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * (BN / 2) + int(rank) * inner, bar);
+            else if (!narrow)
               tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * BN + int(rank) * (BN / 2), bar);
             else
               tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b_narrow, ks * kSlabBytes, tn * BN + n_off + int(rank) * (BN / 4),
@@ -143,7 +149,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if constexpr (KIND == kNvfp4) {
               // scale arrays as [128-row tile][K/64 atoms of 512 bytes], 8-byte elements: 256 elements = 4 atoms
               tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB), &map_sfa, ks * 256, tm * 2 + int(rank), bar);
-              if (!narrow)
+              if (swiglu) {  // scales of the gate rows' tile and of the up rows' tile, one 128-row tile each
+                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256, tn, bar);
+                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa + C::kStageSfb / 2), &map_sfb_narrow,
+                                 ks * 256, inner / 128 + tn, bar);
+              } else if (!narrow)
                 tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
               else
                 tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256,
@@ -273,7 +283,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       float* cs_s = sh->col_scale[tile_it & 1];
       float* bs_s = sh->bias[tile_it & 1];
       if (et < n_cols) {
-        const int col = col_base + et;
+        const int col = swiglu ? (et < BN / 2 ? tn * (BN / 2) + et : inner + tn * (BN / 2) + et - BN / 2) : col_base + et;
         float cs = g.global_scale, bs = 0.0f;
         if (col < g.N) {
           if constexpr (KIND == kI8) cs = __ldg(g.col_scale + col);
@@ -319,6 +329,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader[a]);
+      if (swiglu) {
+        // this warp holds gate chunks half, half + 2 (r[0], r[1]) and their up chunks half + 4, half + 6 (r[2], r[3])
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int c = half + 2 * j;
+          uint4 pg[4], pu[4], po[4];
+          if (has_bias) {
+            pack_chunk<KIND, true, false>(r[j], rs, cs_s + c * 32, bs_s + c * 32, pg);
+            pack_chunk<KIND, true, false>(r[j + 2], rs, cs_s + (c + 4) * 32, bs_s + (c + 4) * 32, pu);
+          } else {
+            pack_chunk<KIND, false, false>(r[j], rs, cs_s + c * 32, bs_s + c * 32, pg);
+            pack_chunk<KIND, false, false>(r[j + 2], rs, cs_s + (c + 4) * 32, bs_s + (c + 4) * 32, pu);
+          }
+          swiglu_chunk(pg, pu, po);
+          flush_chunk(po, stage_w, ywarp + tn * (BN / 2) + c * 32, size_t(g.ldy), rows_ok, lane);
+        }
+        continue;
+      }
 #pragma unroll
       for (int j = 0; j < kMaxJ; ++j) {
         const int c = half + 2 * j;
@@ -425,7 +453,13 @@ bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs&
     msb = make_scale_map(g.w_scale_tiled, size_t(g.N / 128), size_t(g.K / 64), 2);
     msbn = make_scale_map(g.w_scale_tiled, size_t(g.N / 128), size_t(g.K / 64), 1);
   }
-  const int tiles = ((g.M + kPairBM - 1) / kPairBM) * ((g.N + kPairBN - 1) / kPairBN);
+  if (g.act == SFQ_ACT_SWIGLU) {
+    if (g.N % kPairBN != 0) throw std::invalid_argument("sfq gemm: the SwiGLU epilogue needs N % 256 == 0 (gate and up halves in 128-column blocks)");
+    if (g.gate != nullptr) throw std::invalid_argument("sfq gemm: the SwiGLU epilogue cannot be combined with the gated residual");
+    if (g.ldy != g.N / 2 || reinterpret_cast<uintptr_t>(g.y) % 16 != 0)
+      throw std::invalid_argument("sfq gemm: the SwiGLU epilogue writes [M, N/2], 16-byte aligned");
+  }
+  const int tiles = ((g.M + kPairBM - 1) / kPairBM) * ((g.N + kPairBN - 1) / kPairBN);  // same count with or without SwiGLU
   int pairs_cap = pairs_fit;
   if (g.max_ctas > 0) pairs_cap = std::max(1, std::min(pairs_cap, g.max_ctas / 2));
   // Tail of the schedule: r tiles are left for the last wave. If they would occupy at most half of the pairs they
@@ -433,6 +467,7 @@ bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs&
   GemmArgs ga = g;
   const int r = tiles % pairs_cap;
   ga.tail_split = g.tail_split >= 0 ? std::min(g.tail_split, tiles) : ((r > 0 && 2 * r <= pairs_cap) ? r : 0);
+  if (g.act == SFQ_ACT_SWIGLU) ga.tail_split = 0;  // a tile must keep its gate and up halves together
   if (g.debug & 1) ga.tail_split = 0;  // experiment switch: whole tiles only
   const int pairs = std::min(tiles + ga.tail_split, pairs_cap);
   cudaLaunchConfig_t cfg = {};

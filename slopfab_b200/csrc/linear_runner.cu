@@ -68,6 +68,7 @@ sfq::GemmArgs epilogue_for(const QuantWeight& w, int rows, __nv_bfloat16* y, int
     g.bias_is_bf16 = w.bias_format == QuantFormat::kBF16;
   }
   g.act = activation;
+  if (activation == SFQ_ACT_SWIGLU) g.ldy = w.out_features / 2;  // y is [rows, out_features / 2]
   g.status = sfq::device_status_word();
   sfq::apply_tuning(g);
   return g;

@@ -28,6 +28,7 @@ class LinearRunner:
             check(lib.sfq_runner_create(stream_ptr(stream), C.byref(handle)))
         self._h = handle
         self._ws = torch.empty(0, dtype=torch.uint8, device=self.device)
+        self._activation = 0
 
     def close(self) -> None:
         if self._h:
@@ -44,7 +45,9 @@ class LinearRunner:
         return bool(lib.sfq_runner_native(self._h))
 
     def set_activation(self, activation: int) -> None:
+        """ACT_NONE, ACT_GELU_TANH, or ACT_SWIGLU (weight rows [gate | up]; the output then has out_features / 2 columns)."""
         check(lib.sfq_runner_set_activation(self._h, activation))
+        self._activation = activation
 
     @staticmethod
     def workspace_bytes(w: QuantWeight, rows: int) -> int:
@@ -59,7 +62,8 @@ class LinearRunner:
     def forward(self, w: QuantWeight, x: torch.Tensor, y: torch.Tensor | None = None) -> torch.Tensor:
         rows = x.shape[0]
         if y is None:
-            y = torch.empty((rows, w.out_features), dtype=torch.bfloat16, device=x.device)
+            cols = w.out_features // 2 if self._activation == 2 else w.out_features
+            y = torch.empty((rows, cols), dtype=torch.bfloat16, device=x.device)
         self.reserve(self.workspace_bytes(w, rows))
         check(lib.sfq_linear_forward(self._h, C.byref(w), ptr(x), rows, ptr(y), ptr(self._ws), self._ws.numel()))
         return y

@@ -166,6 +166,56 @@ def test_gemm_gated_residual_epilogue(M, N, K, tile_n):
     assert sfq.lib.sfq_gemm_int8(sfq.ptr(da), sfq.ptr(dw), C.byref(bad), sfq.ptr(y), M, N, K, S) == sfq.ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("kind", ["int8", "nvfp4"])
+@pytest.mark.parametrize("M,N,K,bias", [(200, 512, 256, True), (1, 256, 128, False), (700, 1536, 512, True)])
+def test_gemm_swiglu_epilogue(kind, M, N, K, bias):
+    # weight rows [gate | up]: the fused epilogue equals the plain GEMM followed by swiglu_kernel
+    # (src/cuda/nn_pointwise.cu:44-64), bit for bit
+    rng = np.random.default_rng(M + N + K)
+    b = (0.05 * rng.standard_normal(N)).astype(np.float32)
+    db = dev(b)
+    if kind == "int8":
+        a = rng.integers(-128, 128, size=(M, K), dtype=np.int8)
+        w = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
+        rs = (rng.random(M, dtype=np.float32) * 0.02 + 1e-3).astype(np.float32)
+        cs = (rng.random(N, dtype=np.float32) * 0.01 + 1e-4).astype(np.float32)
+        keep = [dev(a), dev(w), dev(rs), dev(cs)]
+
+        def run(act, y):
+            ep = sfq.Epilogue(sfq.ptr(keep[2]), sfq.ptr(keep[3]), 1.0, sfq.ptr(db) if bias else None, sfq.F32, act)
+            return sfq.lib.sfq_gemm_int8(sfq.ptr(keep[0]), sfq.ptr(keep[1]), C.byref(ep), sfq.ptr(y), M, N, K, S)
+    else:
+        x, data, scale, g = _nvfp4_case(M, N, K, seed=M + 3)
+        dx = bf16_tensor(x)
+        xq = torch.empty((M, K // 2), dtype=torch.uint8, device="cuda")
+        xs = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(M, K), dtype=torch.uint8, device="cuda")
+        sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(xq), sfq.ptr(xs), None, M, K,
+                                                   sfq.NVFP4_ACT_GEMM_FEED, S))
+        keep = [dev(data), dev(scale)]
+
+        def run(act, y):
+            ep = sfq.Epilogue(None, None, g, sfq.ptr(db) if bias else None, sfq.F32, act)
+            return sfq.lib.sfq_gemm_nvfp4(sfq.ptr(xq), sfq.ptr(xs), sfq.ptr(keep[0]), sfq.ptr(keep[1]), C.byref(ep), sfq.ptr(y),
+                                          M, N, K, S)
+    fused_in = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sfq.check(run(sfq.ACT_NONE, fused_in))
+    want = torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_swiglu(sfq.ptr(fused_in), sfq.ptr(want), M, N // 2, S))
+    got = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+    sfq.check(run(sfq.ACT_SWIGLU, got))
+    _status_clean()
+    assert np.array_equal(bits(got), bits(want))
+
+
+def test_gemm_swiglu_contract():
+    y = torch.empty((4, 64), dtype=torch.bfloat16, device="cuda")
+    a = torch.zeros((4, 64), dtype=torch.int8, device="cuda")
+    w = torch.zeros((128, 64), dtype=torch.int8, device="cuda")  # N = 128 is not a multiple of 256
+    s = torch.ones(128, device="cuda")
+    ep = sfq.Epilogue(sfq.ptr(s), sfq.ptr(s), 1.0, None, sfq.F32, sfq.ACT_SWIGLU)
+    assert sfq.lib.sfq_gemm_int8(sfq.ptr(a), sfq.ptr(w), C.byref(ep), sfq.ptr(y), 4, 128, 64, S) == sfq.ERR_INVALID_ARGUMENT
+
+
 def test_gemm_nvfp4_multi_tile_persistence():
     # more 256x256 tiles than CTA pairs, ragged M, ragged last K stage: every pair walks several tiles through the one
     # accumulator and wraps the stage ring (and its scale slots) many times

@@ -217,3 +217,21 @@ def test_bf16_weight_arm():
     want = oracle.from_bf16(x).astype(np.float64) @ oracle.from_bf16(wb).astype(np.float64).T
     got = oracle.from_bf16(bits(y))
     assert np.all(np.abs(got - want) <= 1e-3 + 1e-2 * np.abs(want))
+
+
+def test_runner_swiglu_activation_matches_gemm_then_swiglu():
+    # the H3 block's mlp.fc1 is [gate | up] followed by launch_swiglu (src/dit/transformer_execution.cpp); with
+    # set_activation(ACT_SWIGLU) the runner writes silu(gate) * up directly, same bits
+    M, N, K = 300, 1024, 512
+    packed, s_rel, s_ch, book = synthetic_packed_int8(4, 16, N, K, seed=11)
+    w, keep = _packed_weight(4, 16, N, K, packed, s_rel, s_ch, book)
+    x = bf16_tensor(gaussian_bf16((M, K), seed=12, outliers=True))
+    plain = sfq.LinearRunner().forward(w, x)
+    want = torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_swiglu(sfq.ptr(plain), sfq.ptr(want), M, N // 2, None))
+    runner = sfq.LinearRunner()
+    runner.set_activation(sfq.ACT_SWIGLU)
+    got = runner.forward(w, x)
+    assert got.shape == (M, N // 2)
+    assert sfq.device_status() == 0
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
