@@ -283,6 +283,15 @@ SFQ_API int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w
                                         const void* d_x_bf16, int rows, void* d_y_bf16, void* d_workspace,
                                         size_t workspace_bytes);
 
+/* ---- caller side: views over a row-fused weight ----------------------------------- */
+
+/* The index-th of `parts` equal row blocks of a fused weight, e.g. Wq / Wk / Wv of the canonical [Wq; Wk; Wv] upload:
+ * build_block's view slicing (src/dit/transformer_load.cpp:660-737). Every row-indexed array moves with the view (packed
+ * data, group / block scales, per-channel scales, bias). Refused with SFQ_ERR_INVALID_ARGUMENT where a block is not a
+ * whole number of storage units: NVFP4 needs rows-per-block % 128 == 0 (128-row scale tiles), NF4 whole absmax and
+ * nested blocks. Pointers are not dereferenced (host or device). Host only. */
+SFQ_API int sfq_weight_row_block(const sfq_quant_weight* fused, int parts, int index, sfq_quant_weight* out);
+
 /* ---- caller side: row -> adaLN table index ------------------------------------- */
 
 /* build_indices + build_row_timesteps (include/slopfab/dit/packing.h:81-176, src/dit/packing.cpp:213-248,407-489)

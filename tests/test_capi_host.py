@@ -169,3 +169,55 @@ def test_adaln_index_known_answers():
             want_tag[a0 + Sa:] = 0
             assert np.array_equal(uniq, want_u) and np.array_equal(idx, want_i) and np.array_equal(tags, want_tag)
             assert np.array_equal(ada, want_i * 3 + want_tag)
+
+
+def test_weight_row_block_views_follow_build_block():
+    # build_block (src/dit/transformer_load.cpp:660-737): q/k/v are views over one [3 * inner, hidden] upload, and every
+    # row-indexed array moves with the view. Pointers are opaque here: use small integers as "addresses".
+    inner, hidden = 256, 512
+    third = inner * hidden
+
+    def block(w, i):
+        out = sfq.QuantWeight()
+        rc = sfq.lib.sfq_weight_row_block(C.byref(w), 3, i, C.byref(out))
+        return rc, out
+
+    base = dict(data=1 << 20, out_features=3 * inner, in_features=hidden)
+    # NVFP4: data by K/2 bytes per row, block scales by K/16 bytes per row (both arrays sliced)
+    w = sfq.new_weight(format=sfq.NVFP4, block_scale=2 << 20, global_scale=0.5, **base)
+    for i in range(3):
+        rc, v = block(w, i)
+        assert rc == 0 and v.out_features == inner and v.in_features == hidden and v.global_scale == 0.5
+        assert v.data == (1 << 20) + i * third // 2 and v.block_scale == (2 << 20) + i * third // 16
+    # ... and refused when a third does not fall on a 128-row scale tile boundary
+    bad = sfq.new_weight(format=sfq.NVFP4, block_scale=2 << 20, data=1 << 20, out_features=3 * 192, in_features=hidden)
+    assert block(bad, 1)[0] == sfq.ERR_INVALID_ARGUMENT
+    # W4A8 / W6A8: packed bytes, group scales [N, K/g], channel scales [N]
+    for fmt, bits, group in ((sfq.W4A8, 4, 16), (sfq.W6A8, 6, 64)):
+        w = sfq.new_weight(format=fmt, block_scale=2 << 20, weight_scale=3 << 20, w4_codebook=4 << 20 if bits == 4 else None,
+                           packed_group_size=group, convrot=1, convrot_group=256, **base)
+        rc, v = block(w, 2)
+        assert rc == 0
+        assert v.data == (1 << 20) + 2 * third * bits // 8
+        assert v.block_scale == (2 << 20) + 2 * third // group
+        assert v.weight_scale == (3 << 20) + 2 * inner * 4
+        assert v.w4_codebook == w.w4_codebook and v.packed_group_size == group
+    # NF4: data, absmax and nested absmax; refused when a third is not a whole number of nested blocks
+    w = sfq.new_weight(format=sfq.NF4, nf4_absmax=2 << 20, nf4_nested_absmax=3 << 20, nf4_block_size=64,
+                       nf4_nested_block_size=256, **base)
+    rc, v = block(w, 1)
+    assert rc == 0 and v.data == (1 << 20) + third // 2 and v.nf4_absmax == (2 << 20) + third // 64
+    assert v.nf4_nested_absmax == (3 << 20) + (third // 64 // 256) * 4
+    w.nf4_nested_block_size = 1024 * 1024
+    assert block(w, 1)[0] == sfq.ERR_INVALID_ARGUMENT
+    # dense formats: element width; the scale moves only when it is per channel
+    for fmt, width in ((sfq.BF16, 2), (sfq.F32, 4), (sfq.F8E4M3, 1), (sfq.I8, 1)):
+        w = sfq.new_weight(format=fmt, weight_scale=3 << 20, per_channel_scale=1 if fmt == sfq.I8 else 0, bias=5 << 20,
+                           bias_format=sfq.F32, **base)
+        rc, v = block(w, 1)
+        assert rc == 0 and v.data == (1 << 20) + third * width
+        assert v.weight_scale == (3 << 20) + (inner * 4 if fmt == sfq.I8 else 0)
+        assert v.bias == (5 << 20) + inner * 4
+    # argument checks
+    assert block(sfq.new_weight(format=sfq.BF16, data=1, out_features=10, in_features=4), 0)[0] == sfq.ERR_INVALID_ARGUMENT  # 10 % 3
+    assert sfq.lib.sfq_weight_row_block(C.byref(w), 3, 3, C.byref(sfq.QuantWeight())) == sfq.ERR_INVALID_ARGUMENT

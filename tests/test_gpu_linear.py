@@ -235,3 +235,28 @@ def test_runner_swiglu_activation_matches_gemm_then_swiglu():
     assert got.shape == (M, N // 2)
     assert sfq.device_status() == 0
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "w4a8"])
+def test_qkv_views_over_a_fused_weight(fmt):
+    # three views from sfq_weight_row_block give exactly the column blocks of the fused projection
+    inner, K, M = 256, 512, 100
+    x = bf16_tensor(gaussian_bf16((M, K), seed=21, outliers=True))
+    if fmt == "nvfp4":
+        wf = (0.03 * np.random.default_rng(22).standard_normal((3 * inner, K))).astype(np.float32)
+        data, scale, g = pack_nvfp4(wf)
+        keep = [dev(data), dev(scale)]
+        fused = sfq.new_weight(format=sfq.NVFP4, data=sfq.ptr(keep[0]), out_features=3 * inner, in_features=K,
+                               block_scale=sfq.ptr(keep[1]), global_scale=g)
+    else:
+        packed, s_rel, s_ch, book = synthetic_packed_int8(4, 16, 3 * inner, K, seed=23)
+        fused, keep = _packed_weight(4, 16, 3 * inner, K, packed, s_rel, s_ch, book)
+    runner = sfq.LinearRunner()
+    runner.set_native(True)
+    whole = runner.forward(fused, x)
+    for i in range(3):
+        view = sfq.QuantWeight()
+        sfq.check(sfq.lib.sfq_weight_row_block(C.byref(fused), 3, i, C.byref(view)))
+        part = runner.forward(view, x)
+        assert torch.equal(part.view(torch.int16), whole[:, i * inner:(i + 1) * inner].contiguous().view(torch.int16)), i
+    assert sfq.device_status() == 0
