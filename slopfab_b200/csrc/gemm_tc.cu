@@ -48,7 +48,7 @@ template <int KIND, int BN, int ACC> struct Cfg {
   static_assert(kStages >= 2, "pipeline needs at least two stages");
 };
 
-template <int KIND, int BN, int ACC>
+template <int KIND, int BN, int ACC, bool GATED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
   using C = Cfg<KIND, BN, ACC>;
@@ -229,7 +229,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         for (int ks = 0; ks < k_stages; ++ks) {
-          if (!(ok = wait_barrier_warp(smem_u32(&sh->empty[s]), ph ^ 1, sh, g.status, 7))) break;
+          // full[s] of this round completes only after the producer has seen empty[s] of the previous round, so the
+          // loads having landed also says that the MMAs which read this stage's scale slot are done: one wait, not two
           if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
           tc_fence_after_sync();
           const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
@@ -283,7 +284,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         cs_s[et] = cs;
         bs_s[et] = bs;
       }
-      if (g.gate != nullptr) {
+      if constexpr (GATED) {
         // Gated residual: the epilogue will read-modify-write this tile of y. Ask L2 for it now, a whole main loop
         // ahead, so those reads do not pay HBM latency on the store path (128 rows x BN bf16 = BN/64 lines per row).
         constexpr int kLinesPerRow = BN / 64;
@@ -309,9 +310,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       constexpr int kTileChunks = BN / 32;
       constexpr int kMaxJ = (kTileChunks + 1) / 2;
       const uint32_t tbase = tmem + a * BN + (uint32_t(quad * 32) << 16);
-      int gate_idx[4];
-      gate_rows_for(g, warp_row0, lane, gate_idx);
-      const float* gate_row = (g.gate != nullptr && row_ok) ? g.gate + size_t(__ldg(g.gate_index + row)) * g.N : nullptr;
+      int gate_idx[4] = {0, 0, 0, 0};
+      const float* gate_row = nullptr;
+      if constexpr (GATED) {
+        gate_rows_for(g, warp_row0, lane, gate_idx);
+        if (row_ok) gate_row = g.gate + size_t(__ldg(g.gate_index + row)) * g.N;
+      }
       uint32_t r[kMaxJ][32];
 #pragma unroll
       for (int j = 0; j < kMaxJ; ++j)
@@ -334,8 +338,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         else
           pack_chunk<KIND, true, true>(r[j], rs, cs_s + lc0, bs_s + lc0, packed);
         if (vec_ok && col0 + 32 <= g.N) {
-          flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, g.gate ? g.gate + col0 : nullptr, size_t(g.N),
-                      gate_idx);
+          if constexpr (GATED)
+            flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, g.gate + col0, size_t(g.N), gate_idx);
+          else
+            flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane);
         } else if (row_ok) {  // ragged N or unaligned output: element stores from this thread's own row
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -364,22 +370,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 }
 
-template <int KIND, int BN, int ACC>
-void launch(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
+template <int KIND, int BN, int ACC, bool GATED>
+void launch_epi(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
   using C = Cfg<KIND, BN, ACC>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_kernel<KIND, BN, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_kernel<KIND, BN, ACC, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   });
   if (attr_err != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
   const CUtensorMap ma = make_map(a, size_t(g.M), row_bytes, kBM);
   const CUtensorMap mb = make_map(w, size_t(g.N), row_bytes, BN);
   const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + BN - 1) / BN);
   const int grid = g.max_ctas > 0 ? std::min(tiles, g.max_ctas) : std::min(tiles, sm_count());
-  gemm_kernel<KIND, BN, ACC><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, g);
+  gemm_kernel<KIND, BN, ACC, GATED><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, g);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: launch failed: ") + cudaGetErrorString(e));
+}
+
+// The gated residual is a compile-time variant of the epilogue, so the plain store path carries none of its registers.
+template <int KIND, int BN, int ACC>
+void launch(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
+  if (g.gate != nullptr)
+    launch_epi<KIND, BN, ACC, true>(a, w, row_bytes, g, stream);
+  else
+    launch_epi<KIND, BN, ACC, false>(a, w, row_bytes, g, stream);
 }
 
 }  // namespace

@@ -46,7 +46,13 @@ template <int KIND, int ACC> struct PairCfg {
   static_assert(sizeof(Shared) <= kBarrierBytes, "barrier block");
 };
 
-template <int KIND, int ACC>
+// EPI selects the epilogue variant at compile time, so the plain store path carries none of the others' registers or
+// branches: 0 = scales / bias / GELU, 1 = + gated residual (read-modify-write of y), 2 = SwiGLU over [gate | up].
+enum { kEpiPlain = 0, kEpiGated = 1, kEpiSwiglu = 2 };
+
+// TAIL: the schedule ends with tiles cut into 128-column halves (see above); without it every tile is 256 wide at
+// compile time.
+template <int KIND, int ACC, int EPI, bool TAIL>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -66,7 +72,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int tiles_m = (g.M + kPairBM - 1) / kPairBM;
   // SwiGLU epilogue: the weight rows are [gate | up], `inner` each, and a tile pairs 128 gate columns (the leader's
   // weight rows) with the 128 up columns of the same outputs (the peer's), so both meet in one accumulator row.
-  const bool swiglu = g.act == SFQ_ACT_SWIGLU;
+  constexpr bool swiglu = EPI == kEpiSwiglu;
   const int inner = g.N / 2;
   const int tiles_n = swiglu ? inner / (BN / 2) : (g.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
@@ -76,13 +82,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   // Work items: the tiles in raster order, except that the last `tail_split` of them appear as two 128-column
   // halves each. Every role decodes an item the same way.
-  const int first_split = num_tiles - g.tail_split;
-  const int num_work = num_tiles + g.tail_split;
+  const int first_split = TAIL ? num_tiles - g.tail_split : num_tiles;
+  const int num_work = TAIL ? num_tiles + g.tail_split : num_tiles;
   auto work_item = [&](int w, int& tm, int& tn, int& n_off, int& n_cols) {
     int t = w;
     n_off = 0;
     n_cols = BN;
-    if (w >= first_split) {
+    if (TAIL && w >= first_split) {
       const int j = w - first_split;
       t = first_split + (j >> 1);
       n_off = (j & 1) * (BN / 2);
@@ -129,7 +135,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       for (int t = pair; t < num_work && ok; t += num_pairs) {
         int tm, tn, n_off, n_cols;
         work_item(t, tm, tn, n_off, n_cols);
-        const bool narrow = n_cols != BN;
+        const bool narrow = TAIL && n_cols != BN;
         for (int ks = 0; ks < k_stages; ++ks, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
@@ -153,11 +159,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256, tn, bar);
                 tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa + C::kStageSfb / 2), &map_sfb_narrow,
                                  ks * 256, inner / 128 + tn, bar);
-              } else if (!narrow)
+              } else if (!narrow) {
                 tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
-              else
+              } else {
                 tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256,
                                  tn * 2 + n_off / 128, bar);
+              }
             }
           }
           __syncwarp();
@@ -188,10 +195,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!(ok = wait_barrier_warp(smem_u32(&sh->acc_empty[a]), ((tile_it / ACC) & 1) ^ 1, sh, g.status, 2))) break;
         tc_fence_after_sync();
         const uint32_t d = tmem + a * BN;
-        const bool narrow = t >= first_split;
+        const bool narrow = TAIL && t >= first_split;
         const uint32_t idesc = narrow ? idesc_narrow : idesc_wide;
         const uint32_t sfb_step = narrow ? BN / 64 : BN / 32;  // TMEM columns of the weight scales per k-block
         for (int ks = 0; ks < k_stages; ++ks) {
+          // nvfp4: the scale-copy warps arrive on sf_full[s] after they have seen full[s] themselves and their
+          // copies into TMEM slot s have landed, so that one barrier stands for operands and scales alike.
           if constexpr (KIND == kNvfp4) {
             if (!(ok = wait_barrier_warp(smem_u32(&sh->sf_full[s]), ph, sh, g.status, 5))) break;
             tc_fence_after_sync();
@@ -238,9 +247,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t ph = 0;
         bool ok = true;
         for (int t = pair; t < num_work && ok; t += num_pairs) {
-          const int row_tiles = t >= first_split ? 1 : 2;  // 128-row weight scale tiles of this work item
+          const int row_tiles = (TAIL && t >= first_split) ? 1 : 2;  // 128-row weight scale tiles of this work item
           for (int ks = 0; ks < k_stages; ++ks) {
-            if (!(ok = wait_barrier_warp(smem_u32(&sh->empty[s]), ph ^ 1, sh, g.status, 7))) break;
+            // full[s] of this round completes only after the producer has seen empty[s] of the previous round, so the
+            // loads having landed also says that the MMAs which read this stage's scale slot are done: one wait, not two
             if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
             tc_fence_after_sync();
             const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
@@ -275,9 +285,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool has_bias = g.bias != nullptr;
     const uint32_t acc_empty_leader[2] = {map_to_rank(smem_u32(&sh->acc_empty[0]), 0), map_to_rank(smem_u32(&sh->acc_empty[1]), 0)};
     for (int t = pair; t < num_work && ok; t += num_pairs, ++tile_it) {
-      int tm, tn, n_off, n_cols;
-      work_item(t, tm, tn, n_off, n_cols);
-      const int col_base = tn * BN + n_off;  // first output column of this work item
+      int tm, tn, n_off, n_cols_rt;
+      work_item(t, tm, tn, n_off, n_cols_rt);
+      const int n_cols = TAIL ? n_cols_rt : BN;  // a compile-time constant without the tail split
+      const int col_base = tn * BN + n_off;      // first output column of this work item
       const int a = tile_it % ACC;
       const uint32_t aph = (tile_it / ACC) & 1;
       float* cs_s = sh->col_scale[tile_it & 1];
@@ -294,7 +305,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         cs_s[et] = cs;
         bs_s[et] = bs;
       }
-      if (g.gate != nullptr) {
+      if constexpr (EPI == kEpiGated) {
         // Gated residual: the epilogue will read-modify-write this tile of y. Ask L2 for it now, a whole main loop
         // ahead, so those reads do not pay HBM latency on the store path (128 rows x BN bf16 = BN/64 lines per row).
         const int kLinesPerRow = n_cols / 64;
@@ -318,9 +329,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int kTileChunks = n_cols / 32;
       constexpr int kMaxJ = (BN / 32 + 1) / 2;
       const uint32_t tbase = tmem + a * BN + (uint32_t(quad * 32) << 16);
-      int gate_idx[4];
-      gate_rows_for(g, warp_row0, lane, gate_idx);
-      const float* gate_row = (g.gate != nullptr && row_ok) ? g.gate + size_t(__ldg(g.gate_index + row)) * g.N : nullptr;
+      int gate_idx[4] = {0, 0, 0, 0};
+      const float* gate_row = nullptr;
+      if constexpr (EPI == kEpiGated) {
+        gate_rows_for(g, warp_row0, lane, gate_idx);
+        if (row_ok) gate_row = g.gate + size_t(__ldg(g.gate_index + row)) * g.N;
+      }
       uint32_t r[kMaxJ][32];
 #pragma unroll
       for (int j = 0; j < kMaxJ; ++j)
@@ -329,7 +343,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader[a]);
-      if (swiglu) {
+      if constexpr (swiglu) {
         // this warp holds gate chunks half, half + 2 (r[0], r[1]) and their up chunks half + 4, half + 6 (r[2], r[3])
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -361,8 +375,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         else
           pack_chunk<KIND, true, true>(r[j], rs, cs_s + lc0, bs_s + lc0, packed);
         if (vec_ok && col0 + 32 <= g.N) {
-          flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, g.gate ? g.gate + col0 : nullptr, size_t(g.N),
-                      gate_idx);
+          if constexpr (EPI == kEpiGated)
+            flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane, g.gate + col0, size_t(g.N), gate_idx);
+          else
+            flush_chunk(packed, stage_w, ywarp + col0, size_t(g.ldy), rows_ok, lane);
         } else if (row_ok) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -407,7 +423,7 @@ CUtensorMap make_scale_map(const void* base, size_t row_tiles, size_t k_atoms, i
   return m;
 }
 
-template <int KIND, int ACC> int max_pairs() {
+template <int KIND, int ACC, int EPI> int max_pairs() {  // the same for both TAIL variants
   // Clusters of two need both CTAs in one GPC; ask the runtime how many pairs fit at once.
   static int n = [] {
     using C = PairCfg<KIND, ACC>;
@@ -423,7 +439,7 @@ template <int KIND, int ACC> int max_pairs() {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<KIND, ACC>, &cfg);
+    const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<KIND, ACC, EPI, false>, &cfg);
     if (e != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       return 0;
@@ -433,16 +449,18 @@ template <int KIND, int ACC> int max_pairs() {
   return n;
 }
 
-template <int KIND, int ACC>
-bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
+template <int KIND, int ACC, int EPI>
+bool launch_pair_epi(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
   using C = PairCfg<KIND, ACC>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_pair_kernel<KIND, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_pair_kernel<KIND, ACC, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_pair_kernel<KIND, ACC, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   });
   if (attr_err != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
-  const int pairs_fit = max_pairs<KIND, ACC>();
+  const int pairs_fit = max_pairs<KIND, ACC, EPI>();
   if (pairs_fit <= 0) return false;  // no room for clusters of two: the caller uses the one-CTA kernel
   const CUtensorMap ma = make_map(a, size_t(g.M), row_bytes, kBM);
   const CUtensorMap mb = make_map(w, size_t(g.N), row_bytes, kPairBN / 2);
@@ -463,10 +481,14 @@ bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs&
   int pairs_cap = pairs_fit;
   if (g.max_ctas > 0) pairs_cap = std::max(1, std::min(pairs_cap, g.max_ctas / 2));
   // Tail of the schedule: r tiles are left for the last wave. If they would occupy at most half of the pairs they
-  // are cut in two, so that wave keeps twice as many pairs busy on narrower tiles and ends sooner.
+  // can be cut in two, so that wave keeps twice as many pairs busy on narrower tiles and ends sooner. That pays
+  // while the launch has few waves (the saved third of a wave outweighs the narrow tiles' lower efficiency and the
+  // TAIL kernel variant's extra bookkeeping: +3.5 % at 4.3 waves, -1 % at 17.3) and, for nvfp4, only for launches
+  // of less than half a wave: a narrow nvfp4 stage is bound by its scale hand-off, not by its MMAs.
   GemmArgs ga = g;
   const int r = tiles % pairs_cap;
-  ga.tail_split = g.tail_split >= 0 ? std::min(g.tail_split, tiles) : ((r > 0 && 2 * r <= pairs_cap) ? r : 0);
+  const bool few_waves = KIND == kNvfp4 ? 2 * tiles <= pairs_cap : tiles < 8 * pairs_cap;
+  ga.tail_split = g.tail_split >= 0 ? std::min(g.tail_split, tiles) : ((r > 0 && 2 * r <= pairs_cap && few_waves) ? r : 0);
   if (g.act == SFQ_ACT_SWIGLU) ga.tail_split = 0;  // a tile must keep its gate and up halves together
   if (g.debug & 1) ga.tail_split = 0;  // experiment switch: whole tiles only
   const int pairs = std::min(tiles + ga.tail_split, pairs_cap);
@@ -482,9 +504,18 @@ bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs&
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, ACC>, ma, mb, msa, msb, mbn, msbn, ga);
+  const cudaError_t e = ga.tail_split > 0
+                            ? cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, ACC, EPI, true>, ma, mb, msa, msb, mbn, msbn, ga)
+                            : cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, ACC, EPI, false>, ma, mb, msa, msb, mbn, msbn, ga);
   if (e != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: pair launch failed: ") + cudaGetErrorString(e));
   return true;
+}
+
+template <int KIND, int ACC>
+bool launch_pair(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
+  if (g.act == SFQ_ACT_SWIGLU) return launch_pair_epi<KIND, ACC, kEpiSwiglu>(a, w, row_bytes, g, stream);
+  if (g.gate != nullptr) return launch_pair_epi<KIND, ACC, kEpiGated>(a, w, row_bytes, g, stream);
+  return launch_pair_epi<KIND, ACC, kEpiPlain>(a, w, row_bytes, g, stream);
 }
 
 }  // namespace
