@@ -283,6 +283,41 @@ SFQ_API int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w
                                         const void* d_x_bf16, int rows, void* d_y_bf16, void* d_workspace,
                                         size_t workspace_bytes);
 
+/* ---- caller side: the checkpoint boundary ------------------------------------------ */
+
+/* Element types of safetensors entries (the reference's DType, include/slopfab/dtype.h:16-30). */
+typedef enum {
+  SFQ_DT_UNKNOWN = 0, SFQ_DT_BOOL, SFQ_DT_U8, SFQ_DT_I8, SFQ_DT_I16, SFQ_DT_I32, SFQ_DT_I64, SFQ_DT_F8E4M3, SFQ_DT_F8E5M2,
+  SFQ_DT_F16, SFQ_DT_BF16, SFQ_DT_F32, SFQ_DT_F64
+} sfq_dtype;
+
+typedef struct sfq_checkpoint sfq_checkpoint;
+
+/* Maps a .safetensors file and parses its header (SafeTensors, include/slopfab/safetensors.h). The handle owns the
+ * mapping and every device buffer sfq_checkpoint_linear uploads; close it after the last use of those weights. */
+SFQ_API int sfq_checkpoint_open(const char* path, sfq_checkpoint** out);
+SFQ_API void sfq_checkpoint_close(sfq_checkpoint* c);
+SFQ_API int sfq_checkpoint_count(const sfq_checkpoint* c);
+/* One entry by name: dtype (sfq_dtype), rank and up to 8 dimensions, host pointer into the mapping, byte count.
+ * Any output may be null. SFQ_ERR_RUNTIME when the tensor does not exist. */
+SFQ_API int sfq_checkpoint_tensor(const sfq_checkpoint* c, const char* name, int32_t* dtype, int32_t* rank, int64_t* shape8,
+                                  const void** h_data, size_t* nbytes);
+/* One string of the header's __metadata__ table, NUL-terminated into `buffer` (truncated to capacity); *length is
+ * the full length. */
+SFQ_API int sfq_checkpoint_metadata(const sfq_checkpoint* c, const char* key, char* buffer, size_t capacity, size_t* length);
+/* quant() of the reference's loader (src/dit/transformer_load.cpp:585-659): decides the layer's format from the file
+ * (<name>.comfy_quant or the header's _quantization_metadata for W4A8 / W6A8 / ConvRot tags, the bitsandbytes NF4
+ * state tensor, the U8 weight + e4m3 [*, in/16] scale pair for NVFP4, else the weight's dtype), checks the tensor
+ * sizes the layer needs, uploads them (each tensor once per handle; channel scales, codebooks and NF4 tables as fp32)
+ * and fills `out` with DEVICE pointers. Same refusals as the reference: nvfp4 without weight_scale_2, fp8 / int8
+ * without weight_scale, unknown quant formats, incompatible ConvRot metadata, W4 group != 16, ConvRot != 256. */
+SFQ_API int sfq_checkpoint_linear(sfq_checkpoint* c, const char* name, int out_features, int in_features,
+                                  sfq_quant_weight* out);
+/* The same rule without a device: every pointer of `out` is a HOST pointer (into the mapping, or into fp32 copies the
+ * handle keeps). For inspection and for hosts that stage uploads themselves. */
+SFQ_API int sfq_checkpoint_linear_host(sfq_checkpoint* c, const char* name, int out_features, int in_features,
+                                       sfq_quant_weight* out);
+
 /* ---- caller side: views over a row-fused weight ----------------------------------- */
 
 /* The index-th of `parts` equal row blocks of a fused weight, e.g. Wq / Wk / Wv of the canonical [Wq; Wk; Wv] upload:

@@ -376,3 +376,56 @@ REF_API int ref_dev_packed_int8_accumulate(const RefWeight* rw, const void* x, i
     sync();
   });
 }
+
+// ---- the reference's safetensors reader and format detectors (src/core/safetensors.cpp, w4a8.cpp, nf4.cpp) ----
+#include "slopfab/nf4.h"
+#include "slopfab/safetensors.h"
+#include "slopfab/w4a8.h"
+
+REF_API int ref_st_open(const char* path, void** handle) {
+  return guarded([&] {
+    auto* st = new slopfab::SafeTensors();
+    try {
+      st->open(path);
+    } catch (...) {
+      delete st;
+      throw;
+    }
+    *handle = st;
+  });
+}
+REF_API void ref_st_close(void* handle) { delete static_cast<slopfab::SafeTensors*>(handle); }
+// dtype as the reference's DType enumerator value; data pointer into the reference's own mapping.
+REF_API int ref_st_find(void* handle, const char* name, int* dtype, int* rank, int64_t* shape8, const void** data,
+                        size_t* nbytes) {
+  return guarded([&] {
+    const slopfab::TensorView& v = static_cast<slopfab::SafeTensors*>(handle)->at(name);
+    *dtype = int(v.dtype);
+    *rank = int(v.shape.size());
+    for (size_t i = 0; i < v.shape.size() && i < 8; ++i) shape8[i] = v.shape[i];
+    *data = v.data;
+    *nbytes = v.nbytes;
+  });
+}
+REF_API int ref_st_is_packed_int8(void* handle, const char* weight_name, int* yes) {
+  return guarded([&] { *yes = slopfab::is_packed_int8_weight(*static_cast<slopfab::SafeTensors*>(handle), weight_name) ? 1 : 0; });
+}
+REF_API int ref_st_packed_state(void* handle, const char* weight_name, int* bits, int* group, int* rotation) {
+  return guarded([&] {
+    const auto s = slopfab::read_packed_int8_state(*static_cast<slopfab::SafeTensors*>(handle), weight_name, "test");
+    *bits = s.bits;
+    *group = s.group_size;
+    *rotation = s.convrot_group_size;
+  });
+}
+REF_API int ref_st_is_nf4(void* handle, const char* weight_name, int* yes) {
+  return guarded([&] { *yes = slopfab::is_nf4_weight(*static_cast<slopfab::SafeTensors*>(handle), weight_name) ? 1 : 0; });
+}
+REF_API int ref_st_nf4_state(void* handle, const char* weight_name, int* block, int* nested, float* offset) {
+  return guarded([&] {
+    const auto s = slopfab::read_nf4_state(*static_cast<slopfab::SafeTensors*>(handle), weight_name, "test", true);
+    *block = s.block_size;
+    *nested = s.nested_block_size;
+    *offset = s.nested_offset;
+  });
+}

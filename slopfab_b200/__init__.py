@@ -98,6 +98,13 @@ def _load() -> C.CDLL:
         "sfq_linear_nvfp4_forward_static": (I, [V, I, V, V, F, V, I, I, V, I, I, V]),
         "sfq_build_adaln_index": (I, [I, I, I, I, I, I, F, F, V, V, V, V, P(I)]),
         "sfq_weight_row_block": (I, [P(QuantWeight), I, I, P(QuantWeight)]),
+        "sfq_checkpoint_open": (I, [C.c_char_p, P(V)]),
+        "sfq_checkpoint_close": (None, [V]),
+        "sfq_checkpoint_count": (I, [V]),
+        "sfq_checkpoint_tensor": (I, [V, C.c_char_p, P(C.c_int32), P(C.c_int32), P(C.c_int64), P(V), P(SZ)]),
+        "sfq_checkpoint_metadata": (I, [V, C.c_char_p, C.c_char_p, SZ, P(SZ)]),
+        "sfq_checkpoint_linear": (I, [V, C.c_char_p, I, I, P(QuantWeight)]),
+        "sfq_checkpoint_linear_host": (I, [V, C.c_char_p, I, I, P(QuantWeight)]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)  # AttributeError here means header and library disagree
@@ -114,7 +121,8 @@ EXPORTS = ("sfq_last_error sfq_version sfq_quant_weight_init sfq_device_status s
            "sfq_gemm_nvfp4 sfq_gemm_bf16 sfq_gemm_tuning sfq_runner_create sfq_runner_destroy sfq_runner_set_native "
            "sfq_runner_native sfq_runner_set_activation sfq_linear_workspace_bytes sfq_linear_dense_weight_bytes "
            "sfq_linear_activation_workspace_bytes sfq_linear_forward sfq_linear_prepare "
-           "sfq_linear_forward_prepared sfq_linear_nvfp4_forward_static sfq_build_adaln_index sfq_weight_row_block").split()
+           "sfq_linear_forward_prepared sfq_linear_nvfp4_forward_static sfq_build_adaln_index sfq_weight_row_block sfq_checkpoint_open "
+           "sfq_checkpoint_close sfq_checkpoint_count sfq_checkpoint_tensor sfq_checkpoint_metadata sfq_checkpoint_linear sfq_checkpoint_linear_host").split()
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 
 
