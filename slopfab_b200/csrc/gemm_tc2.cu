@@ -190,6 +190,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
       int s = 0;
       uint32_t ph = 0, tile_it = 0;
+      // What the MMAs of stage s wait for: nvfp4 - the scale-copy warps arrive on sf_full[s] after they have seen
+      // full[s] themselves and their copies into TMEM slot s have landed, so that one barrier stands for operands and
+      // scales alike; the other kinds - the loads.
+      auto stage_bar = [&](int st) { return smem_u32(KIND == kNvfp4 ? &sh->sf_full[st] : &sh->full[st]); };
+      // The barrier of the NEXT stage is probed (without blocking) in the same breath as a stage's MMAs are issued, so
+      // in steady state the blocking wait and its round trip never sit between two stages' MMAs.
+      uint32_t ready = 0;
       for (int t = pair; t < num_work && ok; t += num_pairs, ++tile_it) {
         const int a = tile_it % ACC;
         if (!(ok = wait_barrier_warp(smem_u32(&sh->acc_empty[a]), ((tile_it / ACC) & 1) ^ 1, sh, g.status, 2))) break;
@@ -199,37 +206,44 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t idesc = narrow ? idesc_narrow : idesc_wide;
         const uint32_t sfb_step = narrow ? BN / 64 : BN / 32;  // TMEM columns of the weight scales per k-block
         for (int ks = 0; ks < k_stages; ++ks) {
-          // nvfp4: the scale-copy warps arrive on sf_full[s] after they have seen full[s] themselves and their
-          // copies into TMEM slot s have landed, so that one barrier stands for operands and scales alike.
-          if constexpr (KIND == kNvfp4) {
-            if (!(ok = wait_barrier_warp(smem_u32(&sh->sf_full[s]), ph, sh, g.status, 5))) break;
-            tc_fence_after_sync();
-          } else {
-            if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 3))) break;
+          if (!__all_sync(0xffffffffu, ready != 0)) {
+            if (!(ok = wait_barrier_warp(stage_bar(s), ph, sh, g.status, KIND == kNvfp4 ? 5 : 3))) break;
           }
+          tc_fence_after_sync();
+          const int s_next = s + 1 == C::kStages ? 0 : s + 1;
+          const uint32_t ph_next = s_next == 0 ? ph ^ 1 : ph;
           const uint64_t da = kDescHi | uint64_t(a_base + s * kStageStep);
           const uint64_t db = kDescHi | uint64_t(b_base + s * kStageStep);
           const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
           const uint32_t sf_cols = tmem + C::kAccCols + s * C::kSfSlotCols;
+          ready = 1;  // the lanes that issue nothing do not vote against
           if (elect_one()) {
+            if (kb_valid == 4) {
+              // commit: frees the stage (and its scale slot) in both CTAs
+              ready = stage4_pair<int(KIND)>(d, da, db, idesc, ks ? 1u : 0u, sf_cols, sf_cols + 16, sfb_step, smem_u32(&sh->empty[s]),
+                                             stage_bar(s_next), ph_next);
+            } else {
+              ready = mbar_test_wait(stage_bar(s_next), ph_next);
 #pragma unroll
-            for (int kb = 0; kb < 4; ++kb) {
-              if (kb < kb_valid) {
-                const uint32_t acc = (ks | kb) ? 1u : 0u;
-                const uint64_t adv = uint64_t(kb * (kMmaKBytes >> 4));
-                if constexpr (KIND == kI8)
-                  mma_i8_pair(d, da + adv, db + adv, idesc, acc);
-                else if constexpr (KIND == kBf16)
-                  mma_f16_pair(d, da + adv, db + adv, idesc, acc);
-                else
-                  mma_nvfp4_pair(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * sfb_step);
+              for (int kb = 0; kb < 4; ++kb) {
+                if (kb < kb_valid) {
+                  const uint32_t acc = (ks | kb) ? 1u : 0u;
+                  const uint64_t adv = uint64_t(kb * (kMmaKBytes >> 4));
+                  if constexpr (KIND == kI8)
+                    mma_i8_pair(d, da + adv, db + adv, idesc, acc);
+                  else if constexpr (KIND == kBf16)
+                    mma_f16_pair(d, da + adv, db + adv, idesc, acc);
+                  else
+                    mma_nvfp4_pair(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * sfb_step);
+                }
               }
+              tc_commit_pair(smem_u32(&sh->empty[s]), 3);
             }
-            tc_commit_pair(smem_u32(&sh->empty[s]), 3);  // frees the stage (and its scale slot) in both CTAs
             if (ks == k_stages - 1) tc_commit_pair(smem_u32(&sh->acc_full[a]), 3);
           }
-          __syncwarp();
-          if (++s == C::kStages) s = 0, ph ^= 1;
+          // no __syncwarp here: the vote at the top of the next stage (or the accumulator wait) reconverges the warp
+          s = s_next;
+          ph = ph_next;
         }
       }
     }

@@ -61,6 +61,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (try_wait may suspend the thread; this one never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // ---------------------------------------------------------------- TMA
 // 2D tiled load, no multicast: box lands at `dst`, bytes are counted on `bar`.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
@@ -147,8 +160,10 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {  // barrier may live in the peer CTA
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+// Arrive on a barrier that may live in the peer CTA. CTA-scope release (the default): what the waiter must see is
+// ordered by the tcgen05 fences on either side, and a cluster-scope release measured ~1700 cycles per arrival here.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 2D tiled load (no multicast) into this CTA's shared memory; the bytes are counted on the barrier at `bar`'s
 // offset in the LEADER CTA of the pair (address bit 24 selects the CTA inside the pair's shared window).
@@ -203,6 +218,61 @@ __device__ __forceinline__ void mma_nvfp4_pair(uint32_t d, uint64_t a, uint64_t 
       "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d),
       "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
+}
+
+// One whole pipeline stage of the pair kernel from a single thread: probe the NEXT stage's barrier without blocking,
+// issue this stage's four MMAs (each advances the K offset of both descriptors by two 16-byte units; nvfp4 also
+// advances the scale columns: four per MMA for the activations, `sfb_step` for the weights), then commit to
+// `commit_bar` in both CTAs. The probe's verdict is read only after the MMAs and the commit are on their way, so the
+// barrier's round trip hides behind their issue. `kind`: 0 int8, 1 nvfp4, 2 bf16.
+template <int kind>
+__device__ __forceinline__ uint32_t stage4_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate_first,
+                                                uint32_t sfa, uint32_t sfb, uint32_t sfb_step, uint32_t commit_bar,
+                                                uint32_t next_bar, uint32_t next_parity) {
+  uint32_t ready;
+  if constexpr (kind == 1) {
+    asm volatile(
+        "{\n\t.reg .pred p, pt, pn;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t.reg .b32 fa1, fa2, fa3, fb1, fb2, fb3;\n\t.reg .b16 m;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%10], %11;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tmov.b16 m, 3;\n\t"
+        "add.s64 a1, %2, 2;\n\tadd.s64 a2, %2, 4;\n\tadd.s64 a3, %2, 6;\n\t"
+        "add.s64 b1, %3, 2;\n\tadd.s64 b2, %3, 4;\n\tadd.s64 b3, %3, 6;\n\t"
+        "add.u32 fa1, %6, 4;\n\tadd.u32 fa2, %6, 8;\n\tadd.u32 fa3, %6, 12;\n\t"
+        "add.u32 fb1, %7, %8;\n\tadd.u32 fb2, fb1, %8;\n\tadd.u32 fb3, fb2, %8;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], %2, %3, %4, [%6], [%7], p;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], a1, b1, %4, [fa1], [fb1], pt;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], a2, b2, %4, [fa2], [fb2], pt;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], a3, b3, %4, [fa3], [fb3], pt;\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%9], m;\n\t"
+        "selp.u32 %0, 1, 0, pn;\n\t}"
+        : "=r"(ready)
+        : "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate_first), "r"(sfa), "r"(sfb), "r"(sfb_step), "r"(commit_bar),
+          "r"(next_bar), "r"(next_parity)
+        : "memory");
+  } else {
+#define SFQ_STAGE4_PLAIN(KIND_STR)                                                                                      \
+  asm volatile(                                                                                                         \
+      "{\n\t.reg .pred p, pt, pn;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t.reg .b16 m;\n\t"                              \
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%7], %8;\n\t"                                                     \
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tmov.b16 m, 3;\n\t"                                             \
+      "add.s64 a1, %2, 2;\n\tadd.s64 a2, %2, 4;\n\tadd.s64 a3, %2, 6;\n\t"                                              \
+      "add.s64 b1, %3, 2;\n\tadd.s64 b2, %3, 4;\n\tadd.s64 b3, %3, 6;\n\t"                                              \
+      "tcgen05.mma.cta_group::2.kind::" KIND_STR " [%1], %2, %3, %4, p;\n\t"                                            \
+      "tcgen05.mma.cta_group::2.kind::" KIND_STR " [%1], a1, b1, %4, pt;\n\t"                                           \
+      "tcgen05.mma.cta_group::2.kind::" KIND_STR " [%1], a2, b2, %4, pt;\n\t"                                           \
+      "tcgen05.mma.cta_group::2.kind::" KIND_STR " [%1], a3, b3, %4, pt;\n\t"                                           \
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], m;\n\t"          \
+      "selp.u32 %0, 1, 0, pn;\n\t}"                                                                                     \
+      : "=r"(ready)                                                                                                     \
+      : "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate_first), "r"(commit_bar), "r"(next_bar), "r"(next_parity)      \
+      : "memory")
+    if constexpr (kind == 0)
+      SFQ_STAGE4_PLAIN("i8");
+    else
+      SFQ_STAGE4_PLAIN("f16");
+#undef SFQ_STAGE4_PLAIN
+  }
+  return ready;
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base lane + t).
