@@ -342,6 +342,27 @@ SFQ_API int sfq_build_adaln_index(int num_text, int num_condition_video, int num
 
 /* ---- for callers that cannot allocate ------------------------------------------ */
 
+/* ---- LoRA side branch: y[rows,out] += (x[rows,in] A^T) B^T -------------------------------------------
+ * LoraRunner of include/slopfab/cuda/lora.cuh:14-37 (src/cuda/lora.cu:16-93). Factors arrive as fp32 host
+ * arrays in model coordinates (LoraFactors, include/slopfab/lora.h:18-23: a[rank,in], b[out_total,rank], the
+ * adapter's scale already folded into b) and are rounded to bf16 on upload. `row_offset`/`out` select the rows
+ * of b that belong to one view of a fused projection (q, k or v). Several attach calls under one key add
+ * several factor pairs; apply runs all of them; an unknown key is a no-op. Both products run on the tcgen05
+ * bf16 GEMM (fp32 accumulation), hidden and product rounded to bf16 like the reference's, the addition fused
+ * into the second GEMM's epilogue. */
+typedef struct sfq_lora sfq_lora;
+SFQ_API int sfq_lora_create(sfq_lora** out);
+SFQ_API void sfq_lora_destroy(sfq_lora* l);
+SFQ_API int sfq_lora_attach(sfq_lora* l, const void* key, const float* a, const float* b, int rank, int in_features,
+                            int out_total, int row_offset, int out);
+/* The same with the bf16 factor bytes written to host staging memory at *staged_offset (advanced in 256-byte
+ * steps) instead of being uploaded; apply reads them at the same offset of `staged_device` (the caller copies). */
+SFQ_API int sfq_lora_attach_staged(sfq_lora* l, const void* key, const float* a, const float* b, int rank,
+                                   int in_features, int out_total, int row_offset, int out, uint8_t* staged_host,
+                                   uint8_t* staged_device, size_t* staged_offset);
+SFQ_API int sfq_lora_apply(sfq_lora* l, const void* key, const void* d_x_bf16, int rows, void* d_y_bf16, void* stream);
+SFQ_API int sfq_lora_bytes(const sfq_lora* l, size_t* weight_bytes, size_t* scratch_bytes);
+
 /* Bytes of scratch built into the library image for sfq_linear_nvfp4_forward_static (16 MiB, plus a
  * 256-byte status area). Every GPU that loads libsfq.so holds this much until the process exits. */
 #define SFQ_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)

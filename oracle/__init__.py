@@ -87,6 +87,7 @@ _sig(lib.orc_w4a8_output_bf16, None, V, V, V, C.c_int, C.c_int, V)
 _sig(lib.orc_add_bias_bf16, None, V, V, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_gelu_tanh_bf16, None, V, C.c_size_t)
 _sig(lib.orc_swiglu_bf16, None, V, C.c_int, C.c_int, V)
+_sig(lib.orc_lora_apply, None, V, C.c_int, V, V, C.c_int, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_add_gated_bf16, None, V, V, V, V, C.c_int, C.c_int)
 _sig(lib.orc_rmsnorm_bf16, None, V, V, V, V, V, C.c_int, C.c_int, C.c_float, V)
 _sig(lib.orc_rmsnorm_spec_f32, None, V, V, V, V, V, C.c_int, C.c_int, C.c_float, V)
@@ -231,6 +232,17 @@ def packed_int8_linear(x_bf16, packed, s_rel, s_channel, codebook, bits, group, 
                                n, k, _p(bias), int(bias_is_bf16), act, _p(y), g("w8"), g("rot"), g("q"),
                                g("row_scale"), g("acc"))
     return (y, inter) if want_intermediates else y
+
+
+def lora_apply(x_bf16, a, b, offset, out, y_bf16):
+    """y += (x A^T) B[offset:offset+out]^T with the reference test's rounding points; returns the new y."""
+    rows, k = x_bf16.shape
+    rank = a.shape[0]
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    y = np.array(y_bf16, np.uint16, copy=True)
+    lib.orc_lora_apply(_p(x_bf16), rows, _p(a), _p(b), rank, k, offset, out, _p(y))
+    return y
 
 
 # --------------------------------------------------------------------------- norm

@@ -701,6 +701,33 @@ ORC_API void orc_add_gated_bf16(uint16_t* x, const uint16_t* branch, const float
     }
 }
 
+// LoRA side branch, the CPU statement the reference's own test holds its kernels to
+// (tests/test_lora_backends.cu:84-101): sequential fma in index order, hidden rounded to bf16, the product
+// rounded to bf16, then added to y and rounded again. a: [rank, in] and b: [out_total, rank] as fp32 (rounded
+// to bf16 here, as LoraRunner::attach does, src/cuda/lora.cu:25-27); rows [offset, offset + out) of b are used.
+ORC_API void orc_lora_apply(const uint16_t* x, int rows, const float* a, const float* b, int rank, int in, int offset,
+                            int out, uint16_t* y) {
+  std::vector<float> ab(size_t(rank) * in), bb(size_t(out) * rank);
+  for (size_t i = 0; i < ab.size(); ++i) ab[i] = bf16_to_f32(f32_to_bf16(a[i]));
+  for (int o = 0; o < out; ++o)
+    for (int r = 0; r < rank; ++r) bb[size_t(o) * rank + r] = bf16_to_f32(f32_to_bf16(b[size_t(o + offset) * rank + r]));
+#pragma omp parallel for
+  for (int row = 0; row < rows; ++row) {
+    std::vector<float> mid(rank);
+    for (int r = 0; r < rank; ++r) {
+      float sum = 0.0f;
+      for (int i = 0; i < in; ++i) sum = std::fmaf(bf16_to_f32(x[size_t(row) * in + i]), ab[size_t(r) * in + i], sum);
+      mid[r] = bf16_to_f32(f32_to_bf16(sum));
+    }
+    for (int o = 0; o < out; ++o) {
+      float sum = 0.0f;
+      for (int r = 0; r < rank; ++r) sum = std::fmaf(mid[r], bb[size_t(o) * rank + r], sum);
+      const size_t i = size_t(row) * out + o;
+      y[i] = f32_to_bf16(bf16_to_f32(y[i]) + bf16_to_f32(f32_to_bf16(sum)));
+    }
+  }
+}
+
 // ===========================================================================
 // RMSNorm and adaLN modulation
 // ===========================================================================

@@ -429,3 +429,22 @@ REF_API int ref_st_nf4_state(void* handle, const char* weight_name, int* block, 
     *offset = s.nested_offset;
   });
 }
+
+// ---- LoRA side branch (src/cuda/lora.cu): the reference's runner, deterministic or cuBLAS arm
+#include "slopfab/cuda/lora.cuh"
+REF_API int ref_lora_apply(const float* a, const float* b, int rank, int in, int out_total, int offset, int out,
+                           const void* d_x, int rows, void* d_y, int exact) {
+  return guarded([&] {
+    slopfab::LoraFactors f;
+    f.rank = rank, f.in = in, f.out = out_total;
+    f.a.assign(a, a + size_t(rank) * in);
+    f.b.assign(b, b + size_t(out_total) * rank);
+    sc::LoraRunner runner;
+    runner.attach(&f, {f}, offset, out);
+    cublasHandle_t blas = nullptr;
+    SLOPFAB_CUBLAS_CHECK(sc::cublas_create(&blas));
+    runner.apply(&f, static_cast<const bf16*>(d_x), rows, static_cast<bf16*>(d_y), blas, nullptr, exact != 0);
+    sync();
+    SLOPFAB_CUBLAS_CHECK(sc::cublas_destroy(blas));
+  });
+}

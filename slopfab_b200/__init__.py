@@ -105,6 +105,12 @@ def _load() -> C.CDLL:
         "sfq_checkpoint_metadata": (I, [V, C.c_char_p, C.c_char_p, SZ, P(SZ)]),
         "sfq_checkpoint_linear": (I, [V, C.c_char_p, I, I, P(QuantWeight)]),
         "sfq_checkpoint_linear_host": (I, [V, C.c_char_p, I, I, P(QuantWeight)]),
+        "sfq_lora_create": (I, [P(V)]),
+        "sfq_lora_destroy": (None, [V]),
+        "sfq_lora_attach": (I, [V, V, V, V, I, I, I, I, I]),
+        "sfq_lora_attach_staged": (I, [V, V, V, V, I, I, I, I, I, V, V, P(SZ)]),
+        "sfq_lora_apply": (I, [V, V, V, I, V, V]),
+        "sfq_lora_bytes": (I, [V, P(SZ), P(SZ)]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)  # AttributeError here means header and library disagree
@@ -122,7 +128,8 @@ EXPORTS = ("sfq_last_error sfq_version sfq_quant_weight_init sfq_device_status s
            "sfq_runner_native sfq_runner_set_activation sfq_linear_workspace_bytes sfq_linear_dense_weight_bytes "
            "sfq_linear_activation_workspace_bytes sfq_linear_forward sfq_linear_prepare "
            "sfq_linear_forward_prepared sfq_linear_nvfp4_forward_static sfq_build_adaln_index sfq_weight_row_block sfq_checkpoint_open "
-           "sfq_checkpoint_close sfq_checkpoint_count sfq_checkpoint_tensor sfq_checkpoint_metadata sfq_checkpoint_linear sfq_checkpoint_linear_host").split()
+           "sfq_checkpoint_close sfq_checkpoint_count sfq_checkpoint_tensor sfq_checkpoint_metadata sfq_checkpoint_linear sfq_checkpoint_linear_host "
+           "sfq_lora_create sfq_lora_destroy sfq_lora_attach sfq_lora_attach_staged sfq_lora_apply sfq_lora_bytes").split()
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 
 

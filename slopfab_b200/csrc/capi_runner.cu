@@ -6,6 +6,7 @@
 #include <string>
 
 #include "../../include/slopfab_b200/linear.hpp"
+#include "../../include/slopfab_b200/lora.hpp"
 
 namespace sc = slopfab::cuda;
 using bf16 = __nv_bfloat16;
@@ -18,6 +19,9 @@ sc::QuantWeight weight_from_c(const sfq_quant_weight* w);
 
 struct sfq_runner {
   sc::LinearRunner runner;
+};
+struct sfq_lora {
+  sc::LoraRunner runner;
 };
 
 namespace {
@@ -128,6 +132,50 @@ int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w, const 
     }
     r->runner.forward_prepared(qw, static_cast<const bf16*>(d_prepared), static_cast<const bf16*>(d_x_bf16), rows,
                                static_cast<bf16*>(d_y_bf16), ws);
+  });
+}
+
+int sfq_lora_create(sfq_lora** out) {
+  return guarded([&] {
+    if (!out) throw std::invalid_argument("sfq_lora_create: null output");
+    *out = new sfq_lora();
+  });
+}
+void sfq_lora_destroy(sfq_lora* l) { delete l; }
+static slopfab::LoraFactors lora_factors(const float* a, const float* b, int rank, int in, int out_total) {
+  if (!a || !b || rank <= 0 || in <= 0 || out_total <= 0) throw std::invalid_argument("sfq_lora_attach: bad factor arguments");
+  slopfab::LoraFactors f;
+  f.rank = rank, f.in = in, f.out = out_total;
+  f.a.assign(a, a + size_t(rank) * in);
+  f.b.assign(b, b + size_t(out_total) * rank);
+  return f;
+}
+int sfq_lora_attach(sfq_lora* l, const void* key, const float* a, const float* b, int rank, int in_features, int out_total,
+                    int row_offset, int out) {
+  return guarded([&] {
+    if (!l) throw std::invalid_argument("sfq_lora_attach: null runner");
+    l->runner.attach(key, {lora_factors(a, b, rank, in_features, out_total)}, row_offset, out);
+  });
+}
+int sfq_lora_attach_staged(sfq_lora* l, const void* key, const float* a, const float* b, int rank, int in_features, int out_total,
+                           int row_offset, int out, uint8_t* staged_host, uint8_t* staged_device, size_t* staged_offset) {
+  return guarded([&] {
+    if (!l) throw std::invalid_argument("sfq_lora_attach_staged: null runner");
+    l->runner.attach(key, {lora_factors(a, b, rank, in_features, out_total)}, row_offset, out, staged_host, staged_device, staged_offset);
+  });
+}
+int sfq_lora_apply(sfq_lora* l, const void* key, const void* d_x_bf16, int rows, void* d_y_bf16, void* stream) {
+  return guarded([&] {
+    if (!l) throw std::invalid_argument("sfq_lora_apply: null runner");
+    l->runner.apply(key, static_cast<const __nv_bfloat16*>(d_x_bf16), rows, static_cast<__nv_bfloat16*>(d_y_bf16), nullptr,
+                    static_cast<cudaStream_t>(stream), false);
+  });
+}
+int sfq_lora_bytes(const sfq_lora* l, size_t* weight_bytes, size_t* scratch_bytes) {
+  return guarded([&] {
+    if (!l) throw std::invalid_argument("sfq_lora_bytes: null runner");
+    if (weight_bytes) *weight_bytes = l->runner.weight_bytes();
+    if (scratch_bytes) *scratch_bytes = l->runner.scratch_bytes();
   });
 }
 

@@ -340,3 +340,20 @@ def test_oracle_against_compiled_reference_host_code():
     c_orc = np.empty((64, 1024), np.float32)
     lib.orc_matmul_nt(P(dense), P(odn), 64, 1024, 1024, P(c_orc))
     assert np.array_equal(c_ref.view(np.uint32), c_orc.view(np.uint32))
+
+
+def test_lora_statement_known_answer():
+    """tests/test_lora_backends.cu:84-101 on numbers small enough to do by hand (all exact in bf16)."""
+    x = oracle.to_bf16(np.array([[1.0, 2.0, 0.0, -1.0], [0.5, 0.0, 0.0, 0.0]], np.float32))
+    a = np.array([[1.0, 0.5, 0.0, 1.0], [0.0, 0.0, 2.0, 0.0]], np.float32)           # rank 2, in 4
+    b = np.array([[9.0, 9.0], [1.0, 0.0], [2.0, 1.0], [0.0, 3.0]], np.float32)       # out_total 4, rank 2
+    y0 = oracle.to_bf16(np.array([[1.0, 1.0], [0.25, 0.0]], np.float32))
+    # hidden = x A^T = [[1, 0], [0.5, 0]]; rows 1..2 of b -> [[1, 0], [2, 1]]; delta = [[1, 2], [0.5, 1]]
+    got = oracle.from_bf16(oracle.lora_apply(x, a, b, 1, 2, y0))
+    assert np.array_equal(got, np.array([[2.0, 3.0], [0.75, 1.0]], np.float32))
+    # rounding points: hidden is rounded to bf16 before the second product
+    x = oracle.to_bf16(np.array([[1.0, 2.0 ** -9]], np.float32))
+    a = np.array([[1.0, 1.0]], np.float32)                                              # 1 + 2^-9 rounds to 1 in bf16
+    b = np.array([[256.0]], np.float32)
+    got = oracle.from_bf16(oracle.lora_apply(x, a, b, 0, 1, oracle.to_bf16(np.zeros((1, 1), np.float32))))
+    assert got[0, 0] == 256.0
