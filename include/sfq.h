@@ -342,6 +342,19 @@ SFQ_API int sfq_build_adaln_index(int num_text, int num_condition_video, int num
 
 /* ---- for callers that cannot allocate ------------------------------------------ */
 
+/* LinearRunner::forward_f32 (include/slopfab/cuda/linear.cuh:229-232, src/cuda/linear.cu:251-285): fp32 activations
+ * and fp32 output; the weight as stored when fp32, else its dense bf16 form; fp32 accumulation on CUDA cores; the
+ * bias added to the finished sum. The DiT uses this arm for the few timestep rows of the adaLN tables
+ * (src/dit/transformer_execution.cpp:55,63). W4A8/W6A8, AWQ pre-scale and ConvRot weights are refused. */
+SFQ_API int sfq_linear_forward_f32(sfq_runner* r, const sfq_quant_weight* w, const float* d_x_f32, int rows, float* d_y_f32,
+                                   void* d_workspace, size_t workspace_bytes);
+
+/* launch_adaln_expand (src/dit/transformer_support.h:58, src/cuda/dit_kernels.cu:61-134): the per-timestep
+ * modulation tables out[param][t][modality][channel] = bias[p] + sum_k w[p,k] code[t,k] as one fp32 fma chain
+ * started from the bias, p = (modality * num_param + param) * channels + channel. Bit-exact. */
+SFQ_API int sfq_adaln_expand(const float* d_w, const float* d_bias, const float* d_code, float* d_out, int num_t,
+                             int num_modality, int num_param, int channels, int rank, void* stream);
+
 /* ---- LoRA side branch: y[rows,out] += (x[rows,in] A^T) B^T -------------------------------------------
  * LoraRunner of include/slopfab/cuda/lora.cuh:14-37 (src/cuda/lora.cu:16-93). Factors arrive as fp32 host
  * arrays in model coordinates (LoraFactors, include/slopfab/lora.h:18-23: a[rank,in], b[out_total,rank], the

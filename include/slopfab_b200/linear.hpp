@@ -197,6 +197,10 @@ void launch_add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float
                       int dim, cudaStream_t stream);
 void launch_swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int inner, cudaStream_t stream);
 void launch_gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream);
+// adaLN table expansion (src/dit/transformer_support.h:58, src/cuda/dit_kernels.cu:108-134): fp32 fma chain from the
+// bias, out[param][timestep][modality][channel]. Same checks and messages as the reference.
+void launch_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality,
+                         int num_param, int channels, int rank, cudaStream_t stream);
 
 }  // namespace slopfab::cuda
 #pragma GCC visibility pop

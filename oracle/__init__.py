@@ -87,6 +87,7 @@ _sig(lib.orc_w4a8_output_bf16, None, V, V, V, C.c_int, C.c_int, V)
 _sig(lib.orc_add_bias_bf16, None, V, V, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_gelu_tanh_bf16, None, V, C.c_size_t)
 _sig(lib.orc_swiglu_bf16, None, V, C.c_int, C.c_int, V)
+_sig(lib.orc_adaln_expand, None, V, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_lora_apply, None, V, C.c_int, V, V, C.c_int, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_add_gated_bf16, None, V, V, V, V, C.c_int, C.c_int)
 _sig(lib.orc_rmsnorm_bf16, None, V, V, V, V, V, C.c_int, C.c_int, C.c_float, V)
@@ -232,6 +233,15 @@ def packed_int8_linear(x_bf16, packed, s_rel, s_channel, codebook, bits, group, 
                                n, k, _p(bias), int(bias_is_bf16), act, _p(y), g("w8"), g("rot"), g("q"),
                                g("row_scale"), g("acc"))
     return (y, inter) if want_intermediates else y
+
+
+def adaln_expand(w, bias, code, num_modality, num_param, channels):
+    """Modulation tables [param, t, modality, channel] (fp32) from w [features, rank], bias [features], code [t, rank]."""
+    num_t, rank = code.shape
+    out = np.empty((num_param, num_t, num_modality, channels), np.float32)
+    lib.orc_adaln_expand(_p(np.ascontiguousarray(w, np.float32)), _p(np.ascontiguousarray(bias, np.float32)),
+                         _p(np.ascontiguousarray(code, np.float32)), _p(out), num_t, num_modality, num_param, channels, rank)
+    return out
 
 
 def lora_apply(x_bf16, a, b, offset, out, y_bf16):

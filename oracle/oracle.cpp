@@ -701,6 +701,22 @@ ORC_API void orc_add_gated_bf16(uint16_t* x, const uint16_t* branch, const float
     }
 }
 
+// adaLN table expansion, src/cuda/dit_kernels.cu:61-90: acc = bias[p]; acc = fmaf(w[p,k], code[t,k], acc), k ascending;
+// destination [param][t][modality][channel] with p = (modality * num_param + param) * channels + channel.
+ORC_API void orc_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality,
+                              int num_param, int channels, int rank) {
+  const int features = num_modality * num_param * channels;
+  for (int ti = 0; ti < num_t; ++ti)
+#pragma omp parallel for
+    for (int p = 0; p < features; ++p) {
+      float acc = bias[p];
+      for (int k = 0; k < rank; ++k) acc = std::fmaf(w[size_t(p) * rank + k], code[size_t(ti) * rank + k], acc);
+      const int channel = p % channels, rest = p / channels;
+      const int param = rest % num_param, modality = rest / num_param;
+      out[(size_t(param) * num_t * num_modality + size_t(ti) * num_modality + modality) * channels + channel] = acc;
+    }
+}
+
 // LoRA side branch, the CPU statement the reference's own test holds its kernels to
 // (tests/test_lora_backends.cu:84-101): sequential fma in index order, hidden rounded to bf16, the product
 // rounded to bf16, then added to y and rounded again. a: [rank, in] and b: [out_total, rank] as fp32 (rounded

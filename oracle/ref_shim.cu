@@ -448,3 +448,25 @@ REF_API int ref_lora_apply(const float* a, const float* b, int rank, int in, int
     SLOPFAB_CUBLAS_CHECK(sc::cublas_destroy(blas));
   });
 }
+
+// ---- fp32-compute arm and the adaLN table expansion, the reference's own code
+namespace slopfab::cuda {
+void launch_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality,
+                         int num_param, int channels, int rank, cudaStream_t stream);  // src/dit/transformer_support.h:58
+}
+REF_API int ref_dev_linear_forward_f32(const RefWeight* rw, const float* x, int rows, float* y) {
+  return guarded([&] {
+    Runner& r = runner();
+    const sc::QuantWeight w = to_weight(*rw);
+    r.ws.reserve(sc::linear_workspace_bytes(w, rows, sc::ComputeType::kF32) + 4096);
+    r.runner.forward_f32(w, x, rows, y, r.ws);
+    sync();
+  });
+}
+REF_API int ref_dev_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality,
+                                 int num_param, int channels, int rank) {
+  return guarded([&] {
+    sc::launch_adaln_expand(w, bias, code, out, num_t, num_modality, num_param, channels, rank, nullptr);
+    sync();
+  });
+}

@@ -135,6 +135,22 @@ int sfq_linear_forward_prepared(sfq_runner* r, const sfq_quant_weight* w, const 
   });
 }
 
+int sfq_linear_forward_f32(sfq_runner* r, const sfq_quant_weight* w, const float* d_x_f32, int rows, float* d_y_f32, void* d_workspace,
+                           size_t workspace_bytes) {
+  return guarded([&] {
+    if (r == nullptr) throw std::invalid_argument("sfq: null runner");
+    const sc::QuantWeight qw = sfq_capi::weight_from_c(w);
+    sc::Workspace ws;
+    ws.adopt(d_workspace, workspace_bytes);
+    r->runner.forward_f32(qw, d_x_f32, rows, d_y_f32, ws);
+  });
+}
+int sfq_adaln_expand(const float* d_w, const float* d_bias, const float* d_code, float* d_out, int num_t, int num_modality,
+                     int num_param, int channels, int rank, void* stream) {
+  return guarded([&] {
+    sc::launch_adaln_expand(d_w, d_bias, d_code, d_out, num_t, num_modality, num_param, channels, rank, static_cast<cudaStream_t>(stream));
+  });
+}
 int sfq_lora_create(sfq_lora** out) {
   return guarded([&] {
     if (!out) throw std::invalid_argument("sfq_lora_create: null output");

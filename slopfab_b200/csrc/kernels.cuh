@@ -59,4 +59,11 @@ bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale
 void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate, const int32_t* index, int rows,
                int dim, cudaStream_t stream);
 
+// fp32 Linear on CUDA cores: y[rows,out] = x[rows,in] W^T (+ bias), W fp32 or bf16, bias fp32 or bf16 or null.
+void linear_f32(const float* x, const void* w, bool w_is_bf16, const void* bias, bool bias_is_bf16, float* y, int rows, int out_features,
+                int in_features, cudaStream_t stream);
+// adaLN table expansion, launch_adaln_expand (src/cuda/dit_kernels.cu:108-134): out[param][t][modality][channel].
+void adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality, int num_param,
+                  int channels, int rank, cudaStream_t stream);
+
 }  // namespace sfq

@@ -167,7 +167,11 @@ size_t linear_activation_workspace_bytes(const QuantWeight& w, int rows, Compute
     if (compute != ComputeType::kBF16) throw std::invalid_argument("W4A8/W6A8 requires BF16 activations");
     return align_up(r * w.in_features) + align_up(r * 4);
   }
-  if (compute != ComputeType::kBF16) throw std::runtime_error("linear: fp32 compute is not built in this library");
+  if (compute != ComputeType::kBF16) {
+    if (w.pre_quant_scale != nullptr || convrot_applies(w))
+      throw std::runtime_error("linear: AWQ pre-scale and ConvRot are not built for fp32 activations");
+    return 0;  // forward_f32 reads x and writes y directly
+  }
   size_t total = 0;
   if (w.pre_quant_scale != nullptr) total += align_up(r * w.in_features * sizeof(__nv_bfloat16));
   if (convrot_applies(w)) total += align_up(r * w.in_features * sizeof(__nv_bfloat16));
@@ -370,12 +374,43 @@ void LinearRunner::run_packed_int8(const QuantWeight& w, const int8_t* codes, co
   sfq::gemm_int8(q, codes, g, stream_);
 }
 
-void LinearRunner::forward_f32(const QuantWeight&, const float*, int, float*, Workspace&) {
-  throw std::runtime_error("LinearRunner::forward_f32: fp32 compute is not built in this library");
+// fp32 activations in, fp32 out (src/cuda/linear.cu:251-285): the weight is used as stored when it is fp32 and in
+// its dense bf16 form otherwise (the reference widens that copy to fp32 first; the values are the same), the product
+// runs on CUDA cores with fp32 accumulation, the bias is added to the finished sum. The reference's two optional
+// front stages in fp32 (AWQ pre-scale, ConvRot) are not built: such a weight is refused.
+void LinearRunner::forward_f32(const QuantWeight& w, const float* x, int rows, float* y, Workspace& ws) {
+  if (!initialised_) throw std::runtime_error("LinearRunner::forward_f32: init() not called");
+  if (rows <= 0) return;
+  if (is_packed_int8(w.format)) throw std::invalid_argument("W4A8/W6A8 requires BF16 activations");
+  if (w.pre_quant_scale != nullptr || convrot_applies(w))
+    throw std::runtime_error("LinearRunner::forward_f32: AWQ pre-scale and ConvRot are not built for fp32 activations");
+  Workspace::Scope scope(ws);
+  const bool bias_bf16 = w.bias != nullptr && w.bias_format == QuantFormat::kBF16;
+  if (w.bias != nullptr && w.bias_format != QuantFormat::kF32 && w.bias_format != QuantFormat::kBF16)
+    throw std::runtime_error("linear: bias must be F32 or BF16");
+  if (w.format == QuantFormat::kF32) {
+    sfq::linear_f32(x, w.data, false, w.bias, bias_bf16, y, rows, w.out_features, w.in_features, stream_);
+    return;
+  }
+  const bool was_native = native_;
+  native_ = false;  // the dense form, whatever the runner's NVFP4 switch says
+  const __nv_bfloat16* dense = nullptr;
+  try {
+    dense = prepare(w, ws);
+  } catch (...) {
+    native_ = was_native;
+    throw;
+  }
+  native_ = was_native;
+  sfq::linear_f32(x, dense, true, w.bias, bias_bf16, y, rows, w.out_features, w.in_features, stream_);
 }
 
 // ---- free launchers ------------------------------------------------------------------------
 
+void launch_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality, int num_param,
+                         int channels, int rank, cudaStream_t stream) {
+  sfq::adaln_expand(w, bias, code, out, num_t, num_modality, num_param, channels, rank, stream);
+}
 void launch_convrot(const __nv_bfloat16* in, __nv_bfloat16* out, int rows, int dim, int group, cudaStream_t stream) {
   sfq::convrot(in, out, rows, dim, group, stream);
 }

@@ -117,4 +117,102 @@ void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate,
   check_launch("add_gated");
 }
 
+// ---- fp32 Linear (the reference's fp32-compute arm, src/cuda/linear.cu:251-285: fp32 GEMM + add_bias) ----
+// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n], added to the finished sum as add_bias_kernel does). CUDA cores: the
+// DiT calls this arm only for the handful of timestep rows that make the adaLN tables. 64 x 64 outputs per block,
+// 4 x 4 per thread, K in slices of 16 through shared memory.
+namespace {
+template <typename WT> __device__ __forceinline__ float widen(WT v);
+template <> __device__ __forceinline__ float widen<float>(float v) { return v; }
+template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename WT>
+__global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ x, const WT* __restrict__ w, const void* __restrict__ bias,
+                                                         int bias_is_bf16, float* __restrict__ y, int rows, int out_features, int in_features) {
+  __shared__ float xs[16][65], ws[16][65];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < in_features; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i >> 4, k = i & 15;
+      const bool k_ok = k0 + k < in_features;
+      xs[k][r] = (k_ok && m0 + r < rows) ? x[size_t(m0 + r) * in_features + k0 + k] : 0.0f;
+      ws[k][r] = (k_ok && n0 + r < out_features) ? widen<WT>(w[size_t(n0 + r) * in_features + k0 + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i], b[i] = ws[k][tx * 4 + i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < rows && n < out_features) {
+        float v = acc[i][j];
+        if (bias != nullptr)
+          v += bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]) : static_cast<const float*>(bias)[n];
+        y[size_t(m) * out_features + n] = v;
+      }
+    }
+}
+
+// adaLN table expansion (adaln_expand_kernel, src/cuda/dit_kernels.cu:61-90): one fp32 fma chain per output feature
+// and timestep, started from the bias, k ascending; the result lands at [param][timestep][modality][channel].
+__global__ void adaln_expand_kernel(const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ code,
+                                    float* __restrict__ out, int num_t, int num_modality, int num_param, int channels, int rank,
+                                    int out_features) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= out_features) return;
+  const int ti = blockIdx.y;
+  const float* c = code + size_t(ti) * rank;
+  const float* row = w + size_t(p) * rank;
+  float acc = bias[p];
+  for (int k = 0; k < rank; ++k) acc = fmaf(row[k], c[k], acc);
+  const int channel = p % channels, rest = p / channels;
+  const int param = rest % num_param, modality = rest / num_param;
+  out[(size_t(param) * num_t * num_modality + size_t(ti) * num_modality + modality) * channels + channel] = acc;
+}
+}  // namespace
+
+void linear_f32(const float* x, const void* w, bool w_is_bf16, const void* bias, bool bias_is_bf16, float* y, int rows, int out_features,
+                int in_features, cudaStream_t stream) {
+  if (rows <= 0 || out_features <= 0) return;
+  if (in_features <= 0 || !x || !w || !y) throw std::invalid_argument("linear_f32: bad arguments");
+  const dim3 grid((out_features + 63) / 64, (rows + 63) / 64);
+  if (grid.y > 65535) throw std::invalid_argument("linear_f32: too many rows for one launch");
+  if (w_is_bf16)
+    linear_f32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(x, static_cast<const __nv_bfloat16*>(w), bias, bias_is_bf16 ? 1 : 0, y, rows,
+                                                                out_features, in_features);
+  else
+    linear_f32_kernel<float><<<grid, 256, 0, stream>>>(x, static_cast<const float*>(w), bias, bias_is_bf16 ? 1 : 0, y, rows, out_features,
+                                                       in_features);
+  check_launch("linear_f32");
+}
+
+void adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality, int num_param,
+                  int channels, int rank, cudaStream_t stream) {
+  // the checks of launch_adaln_expand (src/cuda/dit_kernels.cu:108-127), same messages
+  if (num_t <= 0 || num_modality <= 0 || num_param <= 0 || channels <= 0 || rank <= 0)
+    throw std::runtime_error("launch_adaln_expand: every extent must be positive");
+  const size_t features = size_t(num_modality) * num_param * channels;
+  if (features > 0x7FFFFFFFull)
+    throw std::runtime_error("launch_adaln_expand: " + std::to_string(features) + " output features overflows the kernel's index type");
+  if (num_t > 65535) throw std::runtime_error("launch_adaln_expand: " + std::to_string(num_t) + " timesteps exceeds the gridDim.y limit");
+  if (!w || !bias || !code || !out) throw std::invalid_argument("adaln_expand: null operand");
+  const dim3 grid(unsigned((features + 255) / 256), unsigned(num_t));
+  adaln_expand_kernel<<<grid, 256, 0, stream>>>(w, bias, code, out, num_t, num_modality, num_param, channels, rank, int(features));
+  check_launch("adaln_expand");
+}
+
 }  // namespace sfq

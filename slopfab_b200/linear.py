@@ -68,6 +68,16 @@ class LinearRunner:
         check(lib.sfq_linear_forward(self._h, C.byref(w), ptr(x), rows, ptr(y), ptr(self._ws), self._ws.numel()))
         return y
 
+    def forward_f32(self, w: QuantWeight, x: torch.Tensor) -> torch.Tensor:
+        """fp32 activations in, fp32 out (the arm the DiT uses for its adaLN tables)."""
+        rows = x.shape[0]
+        y = torch.empty((rows, w.out_features), dtype=torch.float32, device=x.device)
+        n = C.c_size_t(0)
+        check(lib.sfq_linear_workspace_bytes(C.byref(w), rows, 1, C.byref(n)))
+        self.reserve(n.value)
+        check(lib.sfq_linear_forward_f32(self._h, C.byref(w), ptr(x), rows, ptr(y), ptr(self._ws), self._ws.numel()))
+        return y
+
     def prepare(self, w: QuantWeight, rows_per_chunk: int):
         """Returns (prepared pointer or None, bytes consumed at the front of the arena)."""
         self.reserve(self.workspace_bytes(w, rows_per_chunk))
