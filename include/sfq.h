@@ -355,6 +355,20 @@ SFQ_API int sfq_linear_forward_f32(sfq_runner* r, const sfq_quant_weight* w, con
 SFQ_API int sfq_adaln_expand(const float* d_w, const float* d_bias, const float* d_code, float* d_out, int num_t,
                              int num_modality, int num_param, int channels, int rank, void* stream);
 
+/* ---- full self-attention, head_dim 128 ---------------------------------------------------------------
+ * attention_forward / attention_forward_query_chunk / attention_forward_gqa of
+ * include/slopfab/cuda/attention.cuh:176-203: out[seq_q, heads*128] = softmax(q k^T * scale) v per head, no mask,
+ * no causality. q and out may be a compact chunk of the sequence's rows (seq_q <= seq_kv is not required); k and v
+ * are the whole sequence, [seq_kv, kv_heads*128]; query head h reads key/value head h / (heads / kv_heads). The
+ * three leading dimensions are in elements, so the thirds of a fused QKV projection are passed as they lie
+ * (ld = 3 * heads * 128). scale <= 0 selects 1/sqrt(128). The workspace (sfq_attention_workspace_bytes) holds V
+ * transposed. out may not alias the inputs. Parity: the reference's own bound against a dense fp64 softmax,
+ * |err| <= 1e-3 + 1e-2 |want| (tests/test_nn_kernels_attention_synthetic.cu:40). */
+SFQ_API int sfq_attention_workspace_bytes(int seq_kv, int kv_heads, int head_dim, size_t* out);
+SFQ_API int sfq_attention_forward(const void* d_q_bf16, int ld_q, const void* d_k_bf16, const void* d_v_bf16, int ld_kv,
+                                  void* d_out_bf16, int ld_out, int seq_q, int seq_kv, int heads, int kv_heads,
+                                  int head_dim, float scale, void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* ---- LoRA side branch: y[rows,out] += (x[rows,in] A^T) B^T -------------------------------------------
  * LoraRunner of include/slopfab/cuda/lora.cuh:14-37 (src/cuda/lora.cu:16-93). Factors arrive as fp32 host
  * arrays in model coordinates (LoraFactors, include/slopfab/lora.h:18-23: a[rank,in], b[out_total,rank], the

@@ -87,6 +87,7 @@ _sig(lib.orc_w4a8_output_bf16, None, V, V, V, C.c_int, C.c_int, V)
 _sig(lib.orc_add_bias_bf16, None, V, V, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_gelu_tanh_bf16, None, V, C.c_size_t)
 _sig(lib.orc_swiglu_bf16, None, V, C.c_int, C.c_int, V)
+_sig(lib.orc_attention, None, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, V)
 _sig(lib.orc_adaln_expand, None, V, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_lora_apply, None, V, C.c_int, V, V, C.c_int, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_add_gated_bf16, None, V, V, V, V, C.c_int, C.c_int)
@@ -233,6 +234,14 @@ def packed_int8_linear(x_bf16, packed, s_rel, s_channel, codebook, bits, group, 
                                n, k, _p(bias), int(bias_is_bf16), act, _p(y), g("w8"), g("rot"), g("q"),
                                g("row_scale"), g("acc"))
     return (y, inter) if want_intermediates else y
+
+
+def attention(q, k, v, heads, kv_heads, head_dim, scale):
+    """Dense fp64 softmax attention on fp32 arrays q [seq_q, heads*dim], k / v [seq_kv, kv_heads*dim]."""
+    q, k, v = (np.ascontiguousarray(t, np.float32) for t in (q, k, v))
+    out = np.empty_like(q)
+    lib.orc_attention(_p(q), _p(k), _p(v), q.shape[0], k.shape[0], heads, kv_heads, head_dim, scale, _p(out))
+    return out
 
 
 def adaln_expand(w, bias, code, num_modality, num_param, channels):

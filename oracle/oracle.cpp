@@ -701,6 +701,36 @@ ORC_API void orc_add_gated_bf16(uint16_t* x, const uint16_t* branch, const float
     }
 }
 
+// Dense attention, no mask (cpu_attention, tests/detail/nn_kernels_fixture.h:193-231): fp64 scores, softmax and
+// weighted sum; q is [seq_q, heads*dim], k and v are [seq_kv, kv_heads*dim], all fp32 holding bf16 values.
+ORC_API void orc_attention(const float* q, const float* k, const float* v, int seq_q, int seq_kv, int heads, int kv_heads,
+                           int head_dim, float scale, float* out) {
+  const int qld = heads * head_dim, kvld = kv_heads * head_dim, group = heads / kv_heads;
+#pragma omp parallel for collapse(2)
+  for (int h = 0; h < heads; ++h)
+    for (int i = 0; i < seq_q; ++i) {
+      const int kv = h / group;
+      std::vector<double> p(seq_kv);
+      double m = -1e300;
+      for (int j = 0; j < seq_kv; ++j) {
+        double dot = 0.0;
+        for (int d = 0; d < head_dim; ++d) dot += double(q[size_t(i) * qld + h * head_dim + d]) * k[size_t(j) * kvld + kv * head_dim + d];
+        p[j] = dot * scale;
+        m = std::max(m, p[j]);
+      }
+      double sum = 0.0;
+      for (int j = 0; j < seq_kv; ++j) {
+        p[j] = std::exp(p[j] - m);
+        sum += p[j];
+      }
+      for (int d = 0; d < head_dim; ++d) {
+        double acc = 0.0;
+        for (int j = 0; j < seq_kv; ++j) acc += p[j] * v[size_t(j) * kvld + kv * head_dim + d];
+        out[size_t(i) * qld + h * head_dim + d] = float(acc / sum);
+      }
+    }
+}
+
 // adaLN table expansion, src/cuda/dit_kernels.cu:61-90: acc = bias[p]; acc = fmaf(w[p,k], code[t,k], acc), k ascending;
 // destination [param][t][modality][channel] with p = (modality * num_param + param) * channels + channel.
 ORC_API void orc_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality,

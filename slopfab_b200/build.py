@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libsfq.so")
-SOURCES = ["gemm_tc.cu", "gemm_tc2.cu", "unpack.cu", "act_quant.cu", "quant_int8_pairs.cu", "pointwise.cu", "runtime.cu", "linear_runner.cu", "capi.cu",
+SOURCES = ["gemm_tc.cu", "gemm_tc2.cu", "unpack.cu", "act_quant.cu", "quant_int8_pairs.cu", "pointwise.cu", "attention.cu", "runtime.cu", "linear_runner.cu", "capi.cu",
            "capi_runner.cu", "lora_runner.cu", "static_scratch.cu", "packers.cpp", "adaln_index.cpp", "weight_views.cpp", "checkpoint.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden,-fopenmp"]

@@ -1,0 +1,383 @@
+// Full (unmasked, non-causal) self-attention with head_dim 128 on tcgen05: out = softmax(q k^T * scale) v per head.
+//
+// The reference's interface is attention_forward / attention_forward_query_chunk
+// (include/slopfab/cuda/attention.cuh:176-196): q, k, v are [seq, heads * 128] row-major bf16, exactly the thirds of the
+// fused QKV projection; queries may be a compact chunk of the sequence; no mask exists anywhere in the model.
+//
+// One CTA owns 128 queries of one head and walks the keys in tiles of 128 with an online softmax:
+//   warp 0      TMA producer: Q once, then a two-stage ring of K tiles [128 keys x 128 d] and V^T tiles
+//               [128 d x 128 keys]; V is transposed once per call by transpose_v_kernel so that both products are
+//               K-major x K-major, the operand form the GEMM kernels already use
+//   warp 1      issues S = Q K^T (8 MMAs 128x128x16 into one of two S buffers in TMEM) one tile AHEAD of
+//               O += P V^T (8 MMAs into the O accumulator in TMEM)
+//   warps 2-5   softmax, one query row per thread: S from TMEM, running maximum and sum, P = exp2(s - m) as bf16 into
+//               shared memory in the swizzled operand layout, and - only when a row's maximum has grown by more than
+//               2^8 since the accumulator was last scaled - a rescale of O in TMEM. A stale maximum changes nothing
+//               in exact arithmetic (numerator and denominator carry the same factor) and bounds every p by 2^8.
+// Every wait is bounded; a wait that runs out stores a code in the status word and the CTA leaves.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+
+#include "gemm_common.cuh"
+#include "kernels.cuh"
+#include "ptx.cuh"
+#include "runtime.h"
+
+namespace sfq {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTile = 128;             // queries per CTA, keys per step, head_dim
+constexpr int kSlab = kTile * 128;     // 128 rows x 128 bytes: 64 bf16 columns of a tile
+constexpr int kTileBytes = 2 * kSlab;  // [128 x 128] bf16
+constexpr int kAttnThreads = 192;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct AttnShared {
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+constexpr int kAttnSmem = 1024 /* alignment slack */ + 6 * kTileBytes /* Q, K x2, V^T x2, P */ + 256;
+
+struct AttnArgs {
+  __nv_bfloat16* out;
+  int ld_out;
+  int seq_q, seq_kv;
+  int group;         // query heads per key/value head
+  float scale_log2;  // scale * log2(e)
+  int* status;
+};
+
+__device__ __forceinline__ bool attn_wait(uint32_t bar, uint32_t parity, AttnShared* sh, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock_now();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sh->abort) return false;
+    if (clock_now() - start > kWaitCycles) {
+      atomicCAS(status, 0, code);
+      sh->abort = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+    attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_vt, const AttnArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* k_s = smem + kTileBytes;       // two stages
+  uint8_t* v_s = smem + 3 * kTileBytes;   // two stages
+  uint8_t* p_s = smem + 5 * kTileBytes;
+  AttnShared* sh = reinterpret_cast<AttnShared*>(smem + 6 * kTileBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * kTile;
+  const int head = blockIdx.y;
+  const int kv_head = head / g.group;
+  const int tiles = (g.seq_kv + kTile - 1) / kTile;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&sh->q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh->k_full[i]), 1);
+      mbar_init(smem_u32(&sh->k_empty[i]), 1);
+      mbar_init(smem_u32(&sh->v_full[i]), 1);
+      mbar_init(smem_u32(&sh->v_empty[i]), 1);
+      mbar_init(smem_u32(&sh->s_full[i]), 1);
+      mbar_init(smem_u32(&sh->s_empty[i]), 4);
+    }
+    mbar_init(smem_u32(&sh->p_full), 4);
+    mbar_init(smem_u32(&sh->pv_done), 1);
+    sh->abort = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_vt);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&sh->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tmem_o = tmem + 256;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(smem_u32(&sh->q_full), kTileBytes);
+      tma_load_2d(smem_u32(q_s), &map_q, head * 256, q0, smem_u32(&sh->q_full));
+      tma_load_2d(smem_u32(q_s + kSlab), &map_q, head * 256 + 128, q0, smem_u32(&sh->q_full));
+      for (int j = 0; j < tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!attn_wait(smem_u32(&sh->k_empty[st]), ph, sh, g.status, 11)) break;
+        mbar_arrive_expect_tx(smem_u32(&sh->k_full[st]), kTileBytes);
+        tma_load_2d(smem_u32(k_s + st * kTileBytes), &map_k, kv_head * 256, j * kTile, smem_u32(&sh->k_full[st]));
+        tma_load_2d(smem_u32(k_s + st * kTileBytes + kSlab), &map_k, kv_head * 256 + 128, j * kTile, smem_u32(&sh->k_full[st]));
+        if (!attn_wait(smem_u32(&sh->v_empty[st]), ph, sh, g.status, 12)) break;
+        mbar_arrive_expect_tx(smem_u32(&sh->v_full[st]), kTileBytes);
+        // V^T: rows are (kv_head, d), columns are keys; 64 keys = 128 bytes per slab
+        tma_load_2d(smem_u32(v_s + st * kTileBytes), &map_vt, j * 256, kv_head * kTile, smem_u32(&sh->v_full[st]));
+        tma_load_2d(smem_u32(v_s + st * kTileBytes + kSlab), &map_vt, j * 256 + 128, kv_head * kTile, smem_u32(&sh->v_full[st]));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(kTile, kTile);
+      bool ok = attn_wait(smem_u32(&sh->q_full), 0, sh, g.status, 13);
+      auto issue_s = [&](int j) {  // S[j & 1] = Q K_j^T
+        const int st = j & 1;
+        if (!attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14)) return false;
+        if (!attn_wait(smem_u32(&sh->s_empty[st]), ((j >> 1) & 1) ^ 1, sh, g.status, 15)) return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kb = 0; kb < 8; ++kb) {
+          const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
+          mma_f16(tmem + st * kTile, smem_desc_sw128(smem_u32(q_s) + off), smem_desc_sw128(smem_u32(k_s + st * kTileBytes) + off), idesc,
+                  kb ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&sh->k_empty[st]));
+        tc_commit(smem_u32(&sh->s_full[st]));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < tiles && ok; ++j) {
+        if (j + 1 < tiles && !(ok = issue_s(j + 1))) break;
+        const int st = j & 1;
+        if (!(ok = attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16))) break;
+        if (!(ok = attn_wait(smem_u32(&sh->p_full), j & 1, sh, g.status, 17))) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kb = 0; kb < 8; ++kb) {  // O += P V_j: A = P [queries x keys], B = V^T [d x keys]
+          const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
+          mma_f16(tmem_o, smem_desc_sw128(smem_u32(p_s) + off), smem_desc_sw128(smem_u32(v_s + st * kTileBytes) + off), idesc,
+                  (j | kb) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&sh->v_empty[st]));
+        tc_commit(smem_u32(&sh->pv_done));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax, rescale, output (one query row per thread)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    float m_used = -INFINITY;  // the maximum the accumulator and the running sum are expressed against (log2 units)
+    float l = 0.0f;
+    bool ok = true;
+    uint32_t r[4][32];
+    for (int j = 0; j < tiles; ++j) {
+      const int b = j & 1;
+      if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->s_full[b]), (j >> 1) & 1, sh, g.status, 18)))) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem + lane_base + b * kTile + c * 32, r[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->s_empty[b]));
+      // scores in log2 units; keys past the end of the sequence never count
+      const int valid = g.seq_kv - j * kTile;  // >= 1
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[c][i]) * g.scale_log2;
+          if (c * 32 + i >= valid) s = -INFINITY;
+          r[c][i] = __float_as_uint(s);
+          m_tile = fmaxf(m_tile, s);
+        }
+      // P and (if rescaling) O belong to the previous step's product until it has completed
+      if (j > 0 && !(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (j - 1) & 1, sh, g.status, 19)))) break;
+      const bool grow = m_tile > m_used + kRescaleThreshold;  // also true at j == 0 (m_used = -inf)
+      if (__any_sync(0xffffffffu, grow && j > 0)) {
+        // the warp rescales its 32 rows of O together (the TMEM accesses are warp-wide); rows that did not grow use 1
+        const float m_new = grow ? m_tile : m_used;
+        const float f = grow ? fast_exp2(m_used - m_new) : 1.0f;
+        l *= f;
+        m_used = m_new;
+        tc_fence_after_sync();
+        uint32_t o[32];
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st_32x32(tmem_o + lane_base + c * 32, o);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+      } else if (grow) {
+        m_used = m_tile;  // first tile: nothing accumulated yet
+      }
+      // p = 2^(s - m_used) <= 2^8, rounded to bf16; the sum runs over the rounded values, the ones the product sees
+      uint8_t* prow = p_s + row * 128;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {  // 8 probabilities = 16 bytes = one swizzle unit
+          uint32_t w[4];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const float p0 = fast_exp2(__uint_as_float(r[c][q * 8 + 2 * h]) - m_used);
+            const float p1 = fast_exp2(__uint_as_float(r[c][q * 8 + 2 * h + 1]) - m_used);
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            const float2 back = __bfloat1622float2(pb);
+            sum += back.x + back.y;
+            w[h] = *reinterpret_cast<const uint32_t*>(&pb);
+          }
+          const int col = c * 32 + q * 8;               // first key of the unit
+          const int unit = (col & 63) >> 3;              // 16-byte unit inside the 128-byte row of its slab
+          uint8_t* dst = prow + (col >> 6) * kSlab + ((unit ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l += sum;
+      fence_proxy_async();  // the tensor core reads P through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->p_full));
+    }
+    if (ok && (ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (tiles - 1) & 1, sh, g.status, 20)))) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l;
+      const bool row_ok = q0 + row < g.seq_q;
+      __nv_bfloat16* dst = g.out + size_t(row_ok ? q0 + row : 0) * g.ld_out + head * kTile;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * h]) * inv, __uint_as_float(o[q * 8 + 2 * h + 1]) * inv);
+              w[h] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+  if (sh->abort) {
+    // Leaving early: loads may still be in flight into this CTA's shared memory; give them far more time than a
+    // load takes before the memory is released.
+    const long long start = clock_now();
+    while (clock_now() - start < 4000000ll) {
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// V [seq, width] (row pitch ld_v) -> V^T [width, ld_t] with the columns [seq, ld_t) zeroed.
+__global__ void __launch_bounds__(256) transpose_v_kernel(const __nv_bfloat16* __restrict__ v, int ld_v, __nv_bfloat16* __restrict__ vt, int ld_t,
+                                                          int seq, int width) {
+  __shared__ __nv_bfloat16 tile[64][66];
+  const int s0 = blockIdx.x * 64, w0 = blockIdx.y * 64;
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int rs = i >> 6, cw = i & 63;
+    tile[rs][cw] = (s0 + rs < seq && w0 + cw < width) ? v[size_t(s0 + rs) * ld_v + w0 + cw] : __float2bfloat16(0.0f);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int rw = i >> 6, cs = i & 63;
+    if (w0 + rw < width && s0 + cs < ld_t) vt[size_t(w0 + rw) * ld_t + s0 + cs] = tile[cs][rw];
+  }
+}
+
+// [rows, cols] bf16 with a row pitch, boxes of {64 columns, 128 rows}, 128-byte swizzle, zero fill outside.
+CUtensorMap make_attn_map(const void* base, size_t rows, size_t cols, size_t pitch_elems) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (pitch_elems * 2) % 16 != 0)
+    throw std::invalid_argument("sfq attention: operand base and row pitch must be 16-byte aligned for TMA");
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {cols * 2, rows};
+  const cuuint64_t strides[1] = {pitch_elems * 2};
+  const cuuint32_t box[2] = {128, cuuint32_t(kTile)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("sfq attention: cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return m;
+}
+
+size_t align256(size_t n) { return (n + 255) / 256 * 256; }
+int padded_keys(int seq_kv) { return (seq_kv + 63) / 64 * 64; }
+
+}  // namespace
+
+size_t attention_workspace_bytes(int seq_kv, int kv_heads, int head_dim) {
+  if (seq_kv <= 0 || kv_heads <= 0 || head_dim != kTile) throw std::invalid_argument("sfq attention: head_dim must be 128 and the extents positive");
+  return align256(size_t(kv_heads) * kTile * padded_keys(seq_kv) * sizeof(__nv_bfloat16));
+}
+
+void attention_forward(const __nv_bfloat16* q, int ld_q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ld_kv, __nv_bfloat16* out, int ld_out,
+                       int seq_q, int seq_kv, int heads, int kv_heads, int head_dim, float scale, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream) {
+  if (seq_q <= 0) return;
+  if (head_dim != kTile) throw std::invalid_argument("sfq attention: only head_dim 128 is built");
+  if (seq_kv <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) throw std::invalid_argument("sfq attention: bad extents");
+  if (!q || !k || !v || !out || !workspace) throw std::invalid_argument("sfq attention: null operand");
+  if (ld_q < heads * kTile || ld_kv < kv_heads * kTile || ld_out < heads * kTile || ld_out % 8 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0)
+    throw std::invalid_argument("sfq attention: row pitches must cover heads * 128 columns and keep 16-byte alignment");
+  if (workspace_bytes < attention_workspace_bytes(seq_kv, kv_heads, head_dim)) throw std::invalid_argument("sfq attention: workspace too small");
+  if (out == q || out == k || out == v) throw std::invalid_argument("sfq attention: out may not alias q, k or v");
+  if ((seq_q + kTile - 1) / kTile > 0x7FFFFFFF / 2 || heads > 65535) throw std::invalid_argument("sfq attention: too many query tiles or heads");
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] { attr_err = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem); });
+  if (attr_err != cudaSuccess) throw std::runtime_error(std::string("sfq attention: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
+
+  const int ld_t = padded_keys(seq_kv);
+  __nv_bfloat16* vt = static_cast<__nv_bfloat16*>(workspace);
+  const int width = kv_heads * kTile;
+  transpose_v_kernel<<<dim3((ld_t + 63) / 64, (width + 63) / 64), 256, 0, stream>>>(v, ld_kv, vt, ld_t, seq_kv, width);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("sfq attention: launch failed: ") + cudaGetErrorString(e));
+
+  const CUtensorMap mq = make_attn_map(q, size_t(seq_q), size_t(heads) * kTile, size_t(ld_q));
+  const CUtensorMap mk = make_attn_map(k, size_t(seq_kv), size_t(kv_heads) * kTile, size_t(ld_kv));
+  const CUtensorMap mv = make_attn_map(vt, size_t(width), size_t(ld_t), size_t(ld_t));
+  AttnArgs a;
+  a.out = out, a.ld_out = ld_out, a.seq_q = seq_q, a.seq_kv = seq_kv, a.group = heads / kv_heads;
+  a.scale_log2 = (scale > 0.0f ? scale : 1.0f / sqrtf(float(head_dim))) * 1.4426950408889634f;
+  a.status = device_status_word();
+  attention_kernel<<<dim3((seq_q + kTile - 1) / kTile, heads), kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("sfq attention: launch failed: ") + cudaGetErrorString(e));
+}
+
+}  // namespace sfq

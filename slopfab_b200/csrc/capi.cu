@@ -291,6 +291,21 @@ int sfq_gemm_bf16(const void* d_x_bf16, const void* d_w_bf16, const sfq_epilogue
                    to_gemm(ep, d_y_bf16, M, N, K), as_stream(stream));
   });
 }
+int sfq_attention_workspace_bytes(int seq_kv, int kv_heads, int head_dim, size_t* out) {
+  return guarded([&] {
+    if (!out) throw std::invalid_argument("sfq_attention_workspace_bytes: null output");
+    *out = sfq::attention_workspace_bytes(seq_kv, kv_heads, head_dim);
+  });
+}
+int sfq_attention_forward(const void* d_q_bf16, int ld_q, const void* d_k_bf16, const void* d_v_bf16, int ld_kv, void* d_out_bf16,
+                          int ld_out, int seq_q, int seq_kv, int heads, int kv_heads, int head_dim, float scale, void* d_workspace,
+                          size_t workspace_bytes, void* stream) {
+  return guarded([&] {
+    sfq::attention_forward(static_cast<const bf16*>(d_q_bf16), ld_q, static_cast<const bf16*>(d_k_bf16), static_cast<const bf16*>(d_v_bf16),
+                           ld_kv, static_cast<bf16*>(d_out_bf16), ld_out, seq_q, seq_kv, heads, kv_heads, head_dim, scale, d_workspace,
+                           workspace_bytes, as_stream(stream));
+  });
+}
 void sfq_gemm_tuning(int tile_n, int band_m, int max_ctas) { sfq::set_tuning(tile_n, band_m, max_ctas); }
 
 }  // extern "C"

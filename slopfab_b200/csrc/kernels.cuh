@@ -66,4 +66,12 @@ void linear_f32(const float* x, const void* w, bool w_is_bf16, const void* bias,
 void adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality, int num_param,
                   int channels, int rank, cudaStream_t stream);
 
+// Full self-attention, head_dim 128 (attention.cu). q: [seq_q, heads*128] with row pitch ld_q; k, v: [seq_kv, kv_heads*128]
+// with row pitch ld_kv; out: [seq_q, heads*128] with row pitch ld_out. scale <= 0 selects 1/sqrt(head_dim). The workspace
+// holds V^T (attention_workspace_bytes).
+size_t attention_workspace_bytes(int seq_kv, int kv_heads, int head_dim);
+void attention_forward(const __nv_bfloat16* q, int ld_q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ld_kv, __nv_bfloat16* out, int ld_out,
+                       int seq_q, int seq_kv, int heads, int kv_heads, int head_dim, float scale, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream);
+
 }  // namespace sfq
