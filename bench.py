@@ -450,6 +450,25 @@ def run_case(name):
             fn = lambda i: sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(x), None, sfq.ptr(q), sfq.ptr(sc), None, m,  # noqa: E731
                                                                       k, sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
             work = 2.0 * m * k + m * k / 2 + m * k / 16
+    elif name in ("attention", "attention_torch"):
+        # a quarter of configuration 4's sequence (75600 / 4 tokens), its 40 heads of 128; Gaussian q, k, v
+        seq, heads = int(os.environ.get("SFQ_ATTN_SEQ", "18900")), 40
+        g = torch.Generator(device="cuda").manual_seed(7)
+        qkv = torch.randn((seq, 3 * heads * 128), device="cuda", generator=g).to(torch.bfloat16)
+        w = heads * 128
+        q, kk, v = qkv[:, :w], qkv[:, w:2 * w], qkv[:, 2 * w:]
+        out = torch.empty((seq, w), dtype=torch.bfloat16, device="cuda")
+        work = 4.0 * seq * seq * 128 * heads
+        if name == "attention":
+            nbytes = C.c_size_t()
+            sfq.check(sfq.lib.sfq_attention_workspace_bytes(seq, heads, 128, C.byref(nbytes)))
+            ws = torch.empty(nbytes.value, dtype=torch.uint8, device="cuda")
+            fn = lambda i: sfq.check(sfq.lib.sfq_attention_forward(q.data_ptr(), 3 * w, kk.data_ptr(), v.data_ptr(), 3 * w, out.data_ptr(), w,  # noqa: E731
+                                                                   seq, seq, heads, heads, 128, 0.0, ws.data_ptr(), nbytes.value,
+                                                                   sfq.stream_ptr()))
+        else:  # the library kernel on the same tensors, for the comparison line only
+            sh = lambda t: t.reshape(seq, heads, 128).transpose(0, 1)  # noqa: E731
+            fn = lambda i: torch.nn.functional.scaled_dot_product_attention(sh(q), sh(kk), sh(v))  # noqa: E731
     else:
         raise SystemExit("unknown case " + name)
     fn(0)
@@ -461,7 +480,8 @@ def run_case(name):
 
 def run_block_stack(blocks=40, rows=75600, hidden=5120, heads=40, ffn=13824):
     """benchmark configuration 4: NVFP4 DiT block stack, random init, 21x45x80 = 75600 tokens. Reports the Linear-path
-    milliseconds (norm+quant, GEMMs, gated residuals) and the whole-block milliseconds; attention is torch SDPA."""
+    milliseconds (norm+quant, GEMMs, gated residuals) and the whole-block milliseconds, attention included (this library's
+    tcgen05 kernel on the thirds of the fused projection)."""
     import torch
 
     from slopfab_b200.block import BlockWeights, Nvfp4Block, Nvfp4Linear
@@ -492,7 +512,9 @@ def run_block_stack(blocks=40, rows=75600, hidden=5120, heads=40, ffn=13824):
     print(json.dumps({"case": "config4_block_stack", "blocks": blocks, "tokens": rows, "block_ms": total / blocks,
                       "linear_path_ms_per_block": blk.linear_ms / blocks,
                       "linear_path_tflops": flops_linear / (blk.linear_ms / blocks * 1e-3) / 1e12,
-                      "attention": "torch.nn.functional.scaled_dot_product_attention (library, bf16)",
+                      "attention": "attention_kernel of this library (bf16 tcgen05, head_dim 128)",
+                      "attention_ms_per_block": (total - blk.linear_ms) / blocks,
+                      "attention_tflops": 4.0 * rows * rows * hidden / ((total - blk.linear_ms) / blocks * 1e-3) / 1e12,
                       "finite": bool(torch.isfinite(x.float()).all().item()), "device_status": sfq.device_status()}))
 
 

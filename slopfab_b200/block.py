@@ -4,13 +4,13 @@ Order of operations of the reference's ``run_block`` (src/dit/transformer_execut
 
     n1 = modulate(rmsnorm(x, norm1), scale_msa, shift_msa)      fused with the fp4 quantizer, ONE pass
     q, k, v = n1 Wq^T, n1 Wk^T, n1 Wv^T                         three NVFP4 GEMMs on one quantized n1
-    attention(q, k, v)                                          bf16, NOT part of this library (torch SDPA)
+    attention(q, k, v)                                          bf16 tcgen05 kernel of this library on the thirds of the
+                                                                fused projection as they lie (or a callable you pass)
     x += gate_msa * (attn Wo^T)                                 NVFP4 Linear, gated residual in its epilogue
     n2 = modulate(rmsnorm(x, norm2), scale_mlp, shift_mlp)      fused with the fp4 quantizer
     x += gate_mlp * (act(n2 W1^T) W2^T)                         GELU-tanh fused in the first GEMM's epilogue
 
-Head-wise q/k RMSNorm and RoPE sit between the projections and attention in the reference; they belong to
-the attention side and are left out here (this block measures the Linear path around a library attention).
+Head-wise q/k RMSNorm and RoPE sit between the projections and attention in the reference; they are left out here.
 The FFN is the plain GELU form of the benchmark configuration (the reference's H3 block is SwiGLU).
 """
 from __future__ import annotations
@@ -62,6 +62,8 @@ class Nvfp4Block:
         self.branch = torch.empty((rows, hidden), dtype=torch.bfloat16, device=device)
         self.h = torch.empty((rows, ffn), dtype=torch.bfloat16, device=device)
         self.linear_ms = 0.0
+        self.attn = torch.empty((rows, hidden), dtype=torch.bfloat16, device=device)
+        self.attn_ws = None  # V transposed, allocated on first use of the library's own attention
         # True: x += gate * branch inside the out / fc2 GEMM epilogues (same bits; measured 3 % slower per block than the
         # separate add_gated kernel at 75600 tokens, because the single-accumulator nvfp4 epilogue then waits on x)
         self.fuse_residual = False
@@ -90,12 +92,21 @@ class Nvfp4Block:
         self._gemm(w.qkv, self.qkv)
         if ev:
             ev[1].record()
-        q, k, v = (t.view(1, rows, heads, hidden // heads).transpose(1, 2) for t in self.qkv.split(hidden, dim=1))
         if attention is None:
-            attn = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+            # q, k, v are the column thirds of self.qkv (row pitch 3 * hidden): no split, no transpose
+            if hidden != heads * 128:
+                raise ValueError("the attention kernel is built for head_dim 128")
+            if self.attn_ws is None:
+                n = C.c_size_t()
+                check(lib.sfq_attention_workspace_bytes(rows, heads, 128, C.byref(n)))
+                self.attn_ws = torch.empty(n.value, dtype=torch.uint8, device=x.device)
+            base = self.qkv.data_ptr()
+            check(lib.sfq_attention_forward(base, 3 * hidden, base + 2 * hidden, base + 4 * hidden, 3 * hidden, ptr(self.attn), hidden,
+                                            rows, rows, heads, heads, 128, 0.0, ptr(self.attn_ws), self.attn_ws.numel(), stream_ptr()))
+            attn = self.attn
         else:
-            attn = attention(q, k, v)
-        attn = attn.transpose(1, 2).reshape(rows, hidden).contiguous()
+            q, k, v = (t.view(1, rows, heads, hidden // heads).transpose(1, 2) for t in self.qkv.split(hidden, dim=1))
+            attn = attention(q, k, v).transpose(1, 2).reshape(rows, hidden).contiguous()
         if ev:
             ev[2].record()
         self._quantize(attn, hidden, None)

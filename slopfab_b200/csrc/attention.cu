@@ -37,15 +37,17 @@ using namespace ptx;
 constexpr int kTile = 128;             // queries per CTA, keys per step, head_dim
 constexpr int kSlab = kTile * 128;     // 128 rows x 128 bytes: 64 bf16 columns of a tile
 constexpr int kTileBytes = 2 * kSlab;  // [128 x 128] bf16
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;  // producer, MMA issuer, eight softmax warps
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnShared {
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done, pair[4];
   uint32_t tmem_base;
   volatile int abort;
+  float row_max[2][2][kTile];  // [tile parity][half][row]: what the two halves of a row exchange
+  float row_sum[2][kTile];
 };
-constexpr int kAttnSmem = 1024 /* alignment slack */ + 6 * kTileBytes /* Q, K x2, V^T x2, P */ + 256;
+constexpr int kAttnSmem = 1024 /* alignment slack */ + 6 * kTileBytes /* Q, K x2, V^T x2, P */ + 4096;
 
 struct AttnArgs {
   __nv_bfloat16* out;
@@ -102,10 +104,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       mbar_init(smem_u32(&sh->v_full[i]), 1);
       mbar_init(smem_u32(&sh->v_empty[i]), 1);
       mbar_init(smem_u32(&sh->s_full[i]), 1);
-      mbar_init(smem_u32(&sh->s_empty[i]), 4);
+      mbar_init(smem_u32(&sh->s_empty[i]), 8);
     }
-    mbar_init(smem_u32(&sh->p_full), 4);
+    mbar_init(smem_u32(&sh->p_full), 8);
     mbar_init(smem_u32(&sh->pv_done), 1);
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sh->pair[i]), 64);
     sh->abort = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -143,15 +146,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16(kTile, kTile);
-      bool ok = attn_wait(smem_u32(&sh->q_full), 0, sh, g.status, 13);
-      auto issue_s = [&](int j) {  // S[j & 1] = Q K_j^T
-        const int st = j & 1;
-        if (!attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14)) return false;
-        if (!attn_wait(smem_u32(&sh->s_empty[st]), ((j >> 1) & 1) ^ 1, sh, g.status, 15)) return false;
-        tc_fence_after_sync();
+    // ------------------------------------------------------------ MMA issuer (converged warp, one elected lane issues)
+    constexpr uint32_t idesc = idesc_bf16(kTile, kTile);
+    const uint32_t full_mask = 0xffffffffu;
+    bool ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->q_full), 0, sh, g.status, 13));
+    auto issue_s = [&](int j) {  // S[j & 1] = Q K_j^T
+      const int st = j & 1;
+      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14))) return false;
+      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->s_empty[st]), ((j >> 1) & 1) ^ 1, sh, g.status, 15))) return false;
+      tc_fence_after_sync();
+      if (elect_one()) {
 #pragma unroll
         for (int kb = 0; kb < 8; ++kb) {
           const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
@@ -160,15 +164,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         }
         tc_commit(smem_u32(&sh->k_empty[st]));
         tc_commit(smem_u32(&sh->s_full[st]));
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < tiles && ok; ++j) {
-        if (j + 1 < tiles && !(ok = issue_s(j + 1))) break;
-        const int st = j & 1;
-        if (!(ok = attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16))) break;
-        if (!(ok = attn_wait(smem_u32(&sh->p_full), j & 1, sh, g.status, 17))) break;
-        tc_fence_after_sync();
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(0);
+    for (int j = 0; j < tiles && ok; ++j) {
+      if (j + 1 < tiles && !(ok = issue_s(j + 1))) break;
+      const int st = j & 1;
+      if (!(ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16)))) break;
+      if (!(ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->p_full), j & 1, sh, g.status, 17)))) break;
+      tc_fence_after_sync();
+      if (elect_one()) {
 #pragma unroll
         for (int kb = 0; kb < 8; ++kb) {  // O += P V_j: A = P [queries x keys], B = V^T [d x keys]
           const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
@@ -178,43 +185,55 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tc_commit(smem_u32(&sh->v_empty[st]));
         tc_commit(smem_u32(&sh->pv_done));
       }
+      __syncwarp();
     }
   } else {
-    // ------------------------------------------------------------ softmax, rescale, output (one query row per thread)
+    // ------------------------------------------------------------ softmax, rescale, output
+    // Two warps per 32-row quadrant of tensor memory (warps w and w + 4): each thread owns one query row and HALF of
+    // the tile's 128 keys (and half of the 128 output columns). Two warps per scheduler hide each other's latencies;
+    // the row maximum is the only thing the two halves exchange per tile (through shared memory and an mbarrier the
+    // 64 threads arrive on, waited for with the same bound as every other wait), the row sums are added once at the end.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 keys / 64 output columns
     const int row = quad * 32 + lane;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    const uint32_t pair_bar = smem_u32(&sh->pair[quad]);
     float m_used = -INFINITY;  // the maximum the accumulator and the running sum are expressed against (log2 units)
     float l = 0.0f;
     bool ok = true;
-    uint32_t r[4][32];
+    uint32_t r[2][32];
     for (int j = 0; j < tiles; ++j) {
       const int b = j & 1;
       if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->s_full[b]), (j >> 1) & 1, sh, g.status, 18)))) break;
       tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem + lane_base + b * kTile + c * 32, r[c]);
+      tmem_ld_32x32(tmem + lane_base + b * kTile + half * 64, r[0]);
+      tmem_ld_32x32(tmem + lane_base + b * kTile + half * 64 + 32, r[1]);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->s_empty[b]));
-      // scores in log2 units; keys past the end of the sequence never count
-      const int valid = g.seq_kv - j * kTile;  // >= 1
-      float m_tile = -INFINITY;
+      const int valid = g.seq_kv - j * kTile - half * 64;  // keys of this half that exist
+      if (valid < 64) {  // only ever in the last tile: keys past the end of the sequence never count
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[c][i]) * g.scale_log2;
-          if (c * 32 + i >= valid) s = -INFINITY;
-          r[c][i] = __float_as_uint(s);
-          m_tile = fmaxf(m_tile, s);
-        }
-      // P and (if rescaling) O belong to the previous step's product until it has completed
-      if (j > 0 && !(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (j - 1) & 1, sh, g.status, 19)))) break;
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])));
+      sh->row_max[b][half][row] = mx;
+      mbar_arrive(pair_bar);  // 64 arrivals: both halves of these 32 rows have published their maxima
+      if (!(ok = __all_sync(0xffffffffu, attn_wait(pair_bar, j & 1, sh, g.status, 22)))) break;
+      const float m_tile = fmaxf(mx, sh->row_max[b][half ^ 1][row]) * g.scale_log2;  // scale > 0: the maximum commutes with it
       const bool grow = m_tile > m_used + kRescaleThreshold;  // also true at j == 0 (m_used = -inf)
       if (__any_sync(0xffffffffu, grow && j > 0)) {
-        // the warp rescales its 32 rows of O together (the TMEM accesses are warp-wide); rows that did not grow use 1
+        // O belongs to the previous step's product until it has completed. The warp rescales its 32 rows x 64 columns
+        // together (the TMEM accesses are warp-wide); rows that did not grow use a factor of 1.
+        if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (j - 1) & 1, sh, g.status, 19)))) break;
         const float m_new = grow ? m_tile : m_used;
         const float f = grow ? fast_exp2(m_used - m_new) : 1.0f;
         l *= f;
@@ -222,55 +241,55 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tc_fence_after_sync();
         uint32_t o[32];
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32(tmem_o + lane_base + half * 64 + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st_32x32(tmem_o + lane_base + c * 32, o);
+          tmem_st_32x32(tmem_o + lane_base + half * 64 + c * 32, o);
         }
         tmem_st_wait();
         tc_fence_before_sync();
       } else if (grow) {
         m_used = m_tile;  // first tile: nothing accumulated yet
       }
-      // p = 2^(s - m_used) <= 2^8, rounded to bf16; the sum runs over the rounded values, the ones the product sees
-      uint8_t* prow = p_s + row * 128;
-      float sum = 0.0f;
+      // p = 2^(s * scale - m_used) <= 2^8 as bf16 pairs, kept in registers until the P buffer is free
+      float sum0 = 0.0f, sum1 = 0.0f;
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {  // 8 probabilities = 16 bytes = one swizzle unit
-          uint32_t w[4];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const float p0 = fast_exp2(__uint_as_float(r[c][q * 8 + 2 * h]) - m_used);
-            const float p1 = fast_exp2(__uint_as_float(r[c][q * 8 + 2 * h + 1]) - m_used);
-            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-            const float2 back = __bfloat1622float2(pb);
-            sum += back.x + back.y;
-            w[h] = *reinterpret_cast<const uint32_t*>(&pb);
-          }
-          const int col = c * 32 + q * 8;               // first key of the unit
-          const int unit = (col & 63) >> 3;              // 16-byte unit inside the 128-byte row of its slab
-          uint8_t* dst = prow + (col >> 6) * kSlab + ((unit ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), g.scale_log2, -m_used));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), g.scale_log2, -m_used));
+          sum0 += p0;
+          sum1 += p1;
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&pb);
         }
-      }
-      l += sum;
+      l += sum0 + sum1;
+      // the P buffer belongs to the previous step's product until it has completed
+      if (j > 0 && !(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (j - 1) & 1, sh, g.status, 21)))) break;
+      uint8_t* prow = p_s + half * kSlab + row * 128;  // this half's 64 keys are one 128-byte row of slab `half`
+#pragma unroll
+      for (int u = 0; u < 8; ++u)  // 8 probabilities = 16 bytes = one swizzle unit
+        *reinterpret_cast<uint4*>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
       fence_proxy_async();  // the tensor core reads P through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->p_full));
     }
     if (ok && (ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (tiles - 1) & 1, sh, g.status, 20)))) {
       tc_fence_after_sync();
-      const float inv = 1.0f / l;
-      const bool row_ok = q0 + row < g.seq_q;
-      __nv_bfloat16* dst = g.out + size_t(row_ok ? q0 + row : 0) * g.ld_out + head * kTile;
+      sh->row_sum[half][row] = l;
+      mbar_arrive(pair_bar);
+      ok = __all_sync(0xffffffffu, attn_wait(pair_bar, tiles & 1, sh, g.status, 23));
+      const float inv = 1.0f / (l + sh->row_sum[half ^ 1][row]);
+      const bool row_ok = ok && q0 + row < g.seq_q;
+      __nv_bfloat16* dst = g.out + size_t(row_ok ? q0 + row : 0) * g.ld_out + head * kTile + half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_o + lane_base + c * 32, o);
+        tmem_ld_32x32(tmem_o + lane_base + half * 64 + c * 32, o);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
