@@ -355,6 +355,14 @@ SFQ_API int sfq_linear_forward_f32(sfq_runner* r, const sfq_quant_weight* w, con
 SFQ_API int sfq_adaln_expand(const float* d_w, const float* d_bias, const float* d_code, float* d_out, int num_t,
                              int num_modality, int num_param, int channels, int rank, void* stream);
 
+/* launch_head_rmsnorm (include/slopfab/cuda/nn_kernels.cuh:129-134) and launch_rope_h3 (:95-112) as ONE in-place
+ * pass over x[rows, heads, 128] with a row pitch of `ld` elements, so that the q and k thirds of the fused projection
+ * are normalised and rotated where they lie (src/dit/transformer_execution.cpp:277-289: QK-norm first, then RoPE; v is
+ * left alone). d_norm_weight: bf16 [128] or null (no norm); d_cos / d_sin: fp32 [rows, 96] or both null (no rotation);
+ * the rotation pairs channel j with j + 48 over the first 96 channels and passes 96..127 through. Bit-exact. */
+SFQ_API int sfq_head_norm_rope(void* d_x_bf16, int ld, const void* d_norm_weight_bf16, const float* d_cos, const float* d_sin,
+                               int rows, int heads, int head_dim, float eps, void* stream);
+
 /* ---- full self-attention, head_dim 128 ---------------------------------------------------------------
  * attention_forward / attention_forward_query_chunk / attention_forward_gqa of
  * include/slopfab/cuda/attention.cuh:176-203: out[seq_q, heads*128] = softmax(q k^T * scale) v per head, no mask,

@@ -197,6 +197,10 @@ void launch_add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float
                       int dim, cudaStream_t stream);
 void launch_swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int inner, cudaStream_t stream);
 void launch_gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream);
+// QK-norm over the head dimension and MM-RoPE (include/slopfab/cuda/nn_kernels.cuh:95-134), head_dim 128, contiguous
+// [rows, heads, 128] as in the reference; sfq_head_norm_rope does both in one pass and takes a row pitch.
+void launch_head_rmsnorm(__nv_bfloat16* x, const __nv_bfloat16* w, int rows, int heads, int dim, float eps, cudaStream_t stream);
+void launch_rope_h3(__nv_bfloat16* x, const float* cos, const float* sin, int rows, int heads, int head_dim, cudaStream_t stream);
 // adaLN table expansion (src/dit/transformer_support.h:58, src/cuda/dit_kernels.cu:108-134): fp32 fma chain from the
 // bias, out[param][timestep][modality][channel]. Same checks and messages as the reference.
 void launch_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality,

@@ -87,6 +87,7 @@ _sig(lib.orc_w4a8_output_bf16, None, V, V, V, C.c_int, C.c_int, V)
 _sig(lib.orc_add_bias_bf16, None, V, V, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_gelu_tanh_bf16, None, V, C.c_size_t)
 _sig(lib.orc_swiglu_bf16, None, V, C.c_int, C.c_int, V)
+_sig(lib.orc_head_norm_rope, None, V, C.c_int, V, V, V, C.c_int, C.c_int, C.c_float)
 _sig(lib.orc_attention, None, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, V)
 _sig(lib.orc_adaln_expand, None, V, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int)
 _sig(lib.orc_lora_apply, None, V, C.c_int, V, V, C.c_int, C.c_int, C.c_int, C.c_int, V)
@@ -234,6 +235,13 @@ def packed_int8_linear(x_bf16, packed, s_rel, s_channel, codebook, bits, group, 
                                n, k, _p(bias), int(bias_is_bf16), act, _p(y), g("w8"), g("rot"), g("q"),
                                g("row_scale"), g("acc"))
     return (y, inter) if want_intermediates else y
+
+
+def head_norm_rope(x_bf16, heads, w_bf16=None, cos=None, sin=None, eps=1e-6):
+    """QK-norm then MM-RoPE on bf16 bits x [rows, >= heads*128] (row pitch = x.shape[1]); returns the new array."""
+    x = np.array(x_bf16, np.uint16, copy=True)
+    lib.orc_head_norm_rope(_p(x), x.shape[1], _p(w_bf16), _p(cos), _p(sin), x.shape[0], heads, eps)
+    return x
 
 
 def attention(q, k, v, heads, kv_heads, head_dim, scale):

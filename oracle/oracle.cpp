@@ -701,6 +701,56 @@ ORC_API void orc_add_gated_bf16(uint16_t* x, const uint16_t* branch, const float
     }
 }
 
+// Head-wise RMSNorm on the warp-per-row path (rmsnorm_warp_kernel, src/cuda/nn_kernels.cu:100-136: 16 lanes x 8 channels,
+// per-lane fma chain, xor butterfly 16, 8, 4, 2, 1 over 32 lanes of which 16 hold zero) followed by MM-RoPE
+// (rope_h3_kernel, src/cuda/nn_position.cu:15-68) on x [rows, heads, 128] with a row pitch; w and cos may be null.
+static float rope_flush(float v) {
+  uint32_t b; std::memcpy(&b, &v, 4);
+  if ((b & 0x7fffffffu) < 0x00800000u) { b &= 0x80000000u; std::memcpy(&v, &b, 4); }
+  return v;
+}
+static float rope_bf16_in(uint16_t bits) { return (bits & 0x7fffu) < 0x0080u ? bf16_to_f32(uint16_t(bits & 0x8000u)) : bf16_to_f32(bits); }
+static uint16_t rope_bf16_out(float v) {
+  const uint16_t bits = f32_to_bf16(v);
+  return (bits & 0x7fffu) < 0x0080u ? uint16_t(bits & 0x8000u) : bits;
+}
+ORC_API void orc_head_norm_rope(uint16_t* x, int ld, const uint16_t* w, const float* cos_tab, const float* sin_tab, int rows, int heads,
+                                float eps) {
+#pragma omp parallel for collapse(2)
+  for (int row = 0; row < rows; ++row)
+    for (int head = 0; head < heads; ++head) {
+      uint16_t* v = x + size_t(row) * ld + head * 128;
+      if (w != nullptr) {
+        float lane_sum[32] = {};
+        for (int lane = 0; lane < 16; ++lane)
+          for (int i = 0; i < 8; ++i) {
+            const float b = bf16_to_f32(v[lane * 8 + i]);
+            lane_sum[lane] = std::fmaf(b, b, lane_sum[lane]);
+          }
+        for (int offset = 16; offset > 0; offset >>= 1) {
+          float next[32];
+          for (int lane = 0; lane < 32; ++lane) next[lane] = lane_sum[lane] + lane_sum[lane ^ offset];
+          std::memcpy(lane_sum, next, sizeof(next));
+        }
+        const float inv = norm_rsqrt(lane_sum[0], 128u, eps);
+        for (int c = 0; c < 128; ++c) v[c] = f32_to_bf16((bf16_to_f32(v[c]) * inv) * bf16_to_f32(w[c]));
+      }
+      if (cos_tab != nullptr) {
+        for (int j = 0; j < 48; ++j) {
+          const float c = rope_flush(cos_tab[size_t(row) * 96 + j]), s = rope_flush(sin_tab[size_t(row) * 96 + j]);
+          const float lo = rope_bf16_in(v[j]), hi = rope_bf16_in(v[j + 48]);
+          const float left = rope_flush(lo * c), right = rope_flush(hi * s), base = rope_flush(hi * c);
+          const float product = lo * s;
+          uint32_t pb, ab, bb;
+          std::memcpy(&pb, &product, 4); std::memcpy(&ab, &lo, 4); std::memcpy(&bb, &s, 4);
+          const bool tiny = (pb & 0x7fffffffu) < 0x00800000u && (ab & 0x7fffffffu) != 0u && (bb & 0x7fffffffu) != 0u;
+          v[j] = rope_bf16_out(left - right);
+          v[j + 48] = rope_bf16_out(tiny ? base : std::fmaf(lo, s, base));
+        }
+      }
+    }
+}
+
 // Dense attention, no mask (cpu_attention, tests/detail/nn_kernels_fixture.h:193-231): fp64 scores, softmax and
 // weighted sum; q is [seq_q, heads*dim], k and v are [seq_kv, kv_heads*dim], all fp32 holding bf16 values.
 ORC_API void orc_attention(const float* q, const float* k, const float* v, int seq_q, int seq_kv, int heads, int kv_heads,

@@ -470,3 +470,13 @@ REF_API int ref_dev_adaln_expand(const float* w, const float* bias, const float*
     sync();
   });
 }
+
+// ---- QK-norm and MM-RoPE, the reference's two launches on a contiguous [rows, heads, dim] buffer
+REF_API int ref_dev_head_norm_rope(void* x, const void* w, const float* cos_tab, const float* sin_tab, int rows, int heads, int dim,
+                                   float eps) {
+  return guarded([&] {
+    if (w != nullptr) sc::launch_head_rmsnorm(static_cast<bf16*>(x), static_cast<const bf16*>(w), rows, heads, dim, eps, nullptr);
+    if (cos_tab != nullptr) sc::launch_rope_h3(static_cast<bf16*>(x), cos_tab, sin_tab, rows, heads, dim, nullptr);
+    sync();
+  });
+}

@@ -107,6 +107,7 @@ def _load() -> C.CDLL:
         "sfq_checkpoint_linear_host": (I, [V, C.c_char_p, I, I, P(QuantWeight)]),
         "sfq_linear_forward_f32": (I, [V, P(QuantWeight), V, I, V, V, SZ]),
         "sfq_adaln_expand": (I, [V, V, V, V, I, I, I, I, I, V]),
+        "sfq_head_norm_rope": (I, [V, I, V, V, V, I, I, I, C.c_float, V]),
         "sfq_attention_workspace_bytes": (I, [I, I, I, P(SZ)]),
         "sfq_attention_forward": (I, [V, I, V, V, I, V, I, I, I, I, I, I, C.c_float, V, SZ, V]),
         "sfq_lora_create": (I, [P(V)]),
@@ -133,7 +134,7 @@ EXPORTS = ("sfq_last_error sfq_version sfq_quant_weight_init sfq_device_status s
            "sfq_linear_activation_workspace_bytes sfq_linear_forward sfq_linear_prepare "
            "sfq_linear_forward_prepared sfq_linear_nvfp4_forward_static sfq_build_adaln_index sfq_weight_row_block sfq_checkpoint_open "
            "sfq_checkpoint_close sfq_checkpoint_count sfq_checkpoint_tensor sfq_checkpoint_metadata sfq_checkpoint_linear sfq_checkpoint_linear_host "
-           "sfq_linear_forward_f32 sfq_adaln_expand sfq_attention_workspace_bytes sfq_attention_forward sfq_lora_create sfq_lora_destroy sfq_lora_attach sfq_lora_attach_staged sfq_lora_apply sfq_lora_bytes").split()
+           "sfq_linear_forward_f32 sfq_adaln_expand sfq_head_norm_rope sfq_attention_workspace_bytes sfq_attention_forward sfq_lora_create sfq_lora_destroy sfq_lora_attach sfq_lora_attach_staged sfq_lora_apply sfq_lora_bytes").split()
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 
 

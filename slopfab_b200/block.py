@@ -10,7 +10,8 @@ Order of operations of the reference's ``run_block`` (src/dit/transformer_execut
     n2 = modulate(rmsnorm(x, norm2), scale_mlp, shift_mlp)      fused with the fp4 quantizer
     x += gate_mlp * (act(n2 W1^T) W2^T)                         GELU-tanh fused in the first GEMM's epilogue
 
-Head-wise q/k RMSNorm and RoPE sit between the projections and attention in the reference; they are left out here.
+Head-wise q/k RMSNorm and MM-RoPE sit between the projections and attention (QK-norm first, then RoPE; v untouched):
+one in-place pass per third of the fused projection, run when the weights carry q_norm / k_norm or `rope` is given.
 The FFN is the plain GELU form of the benchmark configuration (the reference's H3 block is SwiGLU).
 """
 from __future__ import annotations
@@ -48,6 +49,8 @@ class BlockWeights:
     fc2: Nvfp4Linear
     norm1: torch.Tensor   # bf16 [hidden]
     norm2: torch.Tensor
+    q_norm: torch.Tensor | None = None   # bf16 [128]: RMSNorm over the head dimension of q (and k_norm of k)
+    k_norm: torch.Tensor | None = None
 
 
 class Nvfp4Block:
@@ -80,7 +83,7 @@ class Nvfp4Block:
                                  w.out_features, w.in_features, stream_ptr()))
 
     def forward(self, x: torch.Tensor, w: BlockWeights, mod: dict, adaln_index: torch.Tensor, eps: float = 1e-5,
-                attention=None, time_linears: bool = False) -> torch.Tensor:
+                attention=None, time_linears: bool = False, rope=None) -> torch.Tensor:
         """x bf16 [rows, hidden] is updated in place and returned. `mod` holds fp32 [T*3, hidden] tables
         scale_msa, shift_msa, gate_msa, scale_mlp, shift_mlp, gate_mlp; adaln_index int32 [rows]."""
         rows, hidden, heads = self.rows, self.hidden, self.heads
@@ -92,6 +95,12 @@ class Nvfp4Block:
         self._gemm(w.qkv, self.qkv)
         if ev:
             ev[1].record()
+        if w.q_norm is not None or w.k_norm is not None or rope is not None:
+            cos, sin = (ptr(rope[0]), ptr(rope[1])) if rope is not None else (None, None)  # fp32 [rows, 96] each
+            for third, nw in ((0, w.q_norm), (1, w.k_norm)):
+                if nw is not None or rope is not None:
+                    check(lib.sfq_head_norm_rope(self.qkv.data_ptr() + third * hidden * 2, 3 * hidden, ptr(nw) if nw is not None else None,
+                                                 cos, sin, rows, heads, hidden // heads, eps, stream_ptr()))
         if attention is None:
             # q, k, v are the column thirds of self.qkv (row pitch 3 * hidden): no split, no transpose
             if hidden != heads * 128:

@@ -517,4 +517,124 @@ void quantize_nvfp4_block(const __nv_bfloat16* x, const NormArgs& norm, uint8_t*
   }
 }
 
+// ---- head-wise q/k RMSNorm and MM-RoPE, the two steps between the fused projection and attention ----
+// launch_head_rmsnorm (src/cuda/nn_kernels.cu:296-305 -> rmsnorm_warp_kernel, :100-136) followed by launch_rope_h3
+// (src/cuda/nn_position.cu:15-68,111-123), in place, one warp per (row, head), head_dim 128, on a row pitch so that
+// the q and k thirds of the fused projection are processed where they lie. Bit-exact: 16 lanes hold 8 channels each;
+// the sum of squares is the reference's per-lane chain and xor butterfly; the normalised value is rounded to bf16
+// before the rotation (the reference stores it between its two kernels); the rotation pairs channel j with j + 48
+// over the first 96 channels with the reference's subnormal canonicalisation at every step.
+namespace {
+__device__ __forceinline__ float rope_bf16_value(unsigned short bits) {
+  return (bits & 0x7fffu) < 0x0080u ? __uint_as_float(unsigned(bits & 0x8000u) << 16) : __uint_as_float(unsigned(bits) << 16);
+}
+__device__ __forceinline__ float rope_float_value(float value) {
+  const unsigned bits = __float_as_uint(value);
+  return (bits & 0x7fffffffu) < 0x00800000u ? __uint_as_float(bits & 0x80000000u) : value;
+}
+__device__ __forceinline__ unsigned short rope_bf16_result(float value) {
+  const unsigned short bits = __bfloat16_as_ushort(__float2bfloat16(value));
+  return (bits & 0x7fffu) < 0x0080u ? (unsigned short)(bits & 0x8000u) : bits;
+}
+__device__ __forceinline__ float rope_fma_product(float a, float b, float base) {
+  const float product = __fmul_rn(a, b);
+  const unsigned magnitude = __float_as_uint(product) & 0x7fffffffu;
+  if (magnitude < 0x00800000u && (__float_as_uint(a) & 0x7fffffffu) != 0u && (__float_as_uint(b) & 0x7fffffffu) != 0u) return base;
+  return fmaf(a, b, base);
+}
+
+__global__ void __launch_bounds__(256) head_norm_rope_kernel(__nv_bfloat16* __restrict__ x, int ld, const __nv_bfloat16* __restrict__ w,
+                                                             const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                                             int rows, int heads, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // (row, head)
+  if (unit >= (long long)rows * heads) return;
+  const int row = int(unit / heads), head = int(unit % heads);
+  __nv_bfloat16* v = x + size_t(row) * ld + head * 128;
+  const bool active = lane < 16;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (active) raw = *reinterpret_cast<const uint4*>(v + lane * 8);
+  unsigned short h[8];
+  {
+    const unsigned u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[2 * i] = (unsigned short)(u[i] & 0xFFFFu), h[2 * i + 1] = (unsigned short)(u[i] >> 16);
+  }
+  if (w != nullptr) {
+    float buf[8];
+    float sum_sq = 0.0f;
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        buf[i] = __uint_as_float(unsigned(h[i]) << 16);
+        sum_sq = fmaf(buf[i], buf[i], sum_sq);
+      }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) sum_sq = __fadd_rn(sum_sq, __shfl_xor_sync(0xFFFFFFFFu, sum_sq, offset));
+    float inv = lane == 0 ? norm_rsqrt(sum_sq, 128, eps) : 0.0f;
+    inv = __shfl_sync(0xFFFFFFFFu, inv, 0);
+    if (active) {
+      const uint4 wr = *reinterpret_cast<const uint4*>(w + lane * 8);
+      const unsigned wu[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float wf = __uint_as_float(((wu[i >> 1] >> (16 * (i & 1))) & 0xFFFFu) << 16);
+        h[i] = __bfloat16_as_ushort(__float2bfloat16(__fmul_rn(__fmul_rn(buf[i], inv), wf)));
+      }
+    }
+  }
+  if (cos_tab != nullptr) {
+    // lanes 0-5 hold channels j = 8*lane .. (the low halves), lanes 6-11 their partners j + 48, lanes 12-15 pass through
+    const bool low = lane < 6, high = lane >= 6 && lane < 12;
+    const int partner = low ? lane + 6 : lane - 6;
+    unsigned short other[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const unsigned mine = unsigned(h[2 * i]) | (unsigned(h[2 * i + 1]) << 16);
+      const unsigned got = __shfl_sync(0xFFFFFFFFu, mine, partner & 31);
+      other[2 * i] = (unsigned short)(got & 0xFFFFu), other[2 * i + 1] = (unsigned short)(got >> 16);
+    }
+    if (low || high) {
+      const int j0 = (low ? lane : lane - 6) * 8;
+      const float* cr = cos_tab + size_t(row) * 96 + j0;
+      const float* sr = sin_tab + size_t(row) * 96 + j0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = rope_float_value(cr[i]), s = rope_float_value(sr[i]);
+        const float lo = rope_bf16_value(low ? h[i] : other[i]);
+        const float hi = rope_bf16_value(low ? other[i] : h[i]);
+        if (low) {
+          const float left = rope_float_value(__fmul_rn(lo, c)), right = rope_float_value(__fmul_rn(hi, s));
+          h[i] = rope_bf16_result(__fsub_rn(left, right));
+        } else {
+          const float base = rope_float_value(__fmul_rn(hi, c));
+          h[i] = rope_bf16_result(rope_fma_product(lo, s, base));
+        }
+      }
+    }
+  }
+  if (active) {
+    uint4 o;
+    o.x = unsigned(h[0]) | (unsigned(h[1]) << 16), o.y = unsigned(h[2]) | (unsigned(h[3]) << 16);
+    o.z = unsigned(h[4]) | (unsigned(h[5]) << 16), o.w = unsigned(h[6]) | (unsigned(h[7]) << 16);
+    *reinterpret_cast<uint4*>(v + lane * 8) = o;
+  }
+}
+}  // namespace
+
+void head_norm_rope(__nv_bfloat16* x, int ld, const __nv_bfloat16* norm_weight, const float* cos_tab, const float* sin_tab, int rows,
+                    int heads, int head_dim, float eps, cudaStream_t stream) {
+  if (rows <= 0 || heads <= 0) throw std::runtime_error("head_norm_rope: rows and heads must be positive");
+  if (head_dim != 128) throw std::runtime_error("head_norm_rope: built for head_dim 128 (96 rotary channels + 32 passed through)");
+  if (x == nullptr || (norm_weight == nullptr && cos_tab == nullptr)) throw std::invalid_argument("head_norm_rope: nothing to do");
+  if ((cos_tab == nullptr) != (sin_tab == nullptr)) throw std::invalid_argument("head_norm_rope: cos and sin come together");
+  if (ld < heads * 128 || ld % 8 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 ||
+      (norm_weight != nullptr && reinterpret_cast<uintptr_t>(norm_weight) % 16 != 0))
+    throw std::invalid_argument("head_norm_rope: the row pitch must cover heads * 128 and keep 16-byte alignment");
+  const long long units = (long long)rows * heads;
+  head_norm_rope_kernel<<<unsigned((units + 7) / 8), 256, 0, stream>>>(x, ld, norm_weight, cos_tab, sin_tab, rows, heads, eps);
+  check_launch("head_norm_rope");
+}
+
 }  // namespace sfq

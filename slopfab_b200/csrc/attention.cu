@@ -220,11 +220,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
       }
-      float mx = -INFINITY;
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one of 32 steps
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])));
+        for (int i = 0; i < 32; i += 8)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(r[c][i + 2 * k]), __uint_as_float(r[c][i + 2 * k + 1])));
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       sh->row_max[b][half][row] = mx;
       mbar_arrive(pair_bar);  // 64 arrivals: both halves of these 32 rows have published their maxima
       if (!(ok = __all_sync(0xffffffffu, attn_wait(pair_bar, j & 1, sh, g.status, 22)))) break;

@@ -291,6 +291,13 @@ int sfq_gemm_bf16(const void* d_x_bf16, const void* d_w_bf16, const sfq_epilogue
                    to_gemm(ep, d_y_bf16, M, N, K), as_stream(stream));
   });
 }
+int sfq_head_norm_rope(void* d_x_bf16, int ld, const void* d_norm_weight_bf16, const float* d_cos, const float* d_sin, int rows, int heads,
+                       int head_dim, float eps, void* stream) {
+  return guarded([&] {
+    sfq::head_norm_rope(static_cast<bf16*>(d_x_bf16), ld, static_cast<const bf16*>(d_norm_weight_bf16), d_cos, d_sin, rows, heads, head_dim,
+                        eps, as_stream(stream));
+  });
+}
 int sfq_attention_workspace_bytes(int seq_kv, int kv_heads, int head_dim, size_t* out) {
   return guarded([&] {
     if (!out) throw std::invalid_argument("sfq_attention_workspace_bytes: null output");

@@ -74,4 +74,9 @@ void attention_forward(const __nv_bfloat16* q, int ld_q, const __nv_bfloat16* k,
                        int seq_q, int seq_kv, int heads, int kv_heads, int head_dim, float scale, void* workspace, size_t workspace_bytes,
                        cudaStream_t stream);
 
+// Head-wise RMSNorm (norm_weight [128], may be null) and MM-RoPE (cos / sin fp32 [rows, 96], may be null) in place on
+// x [rows, heads, 128] with a row pitch of ld elements.
+void head_norm_rope(__nv_bfloat16* x, int ld, const __nv_bfloat16* norm_weight, const float* cos_tab, const float* sin_tab, int rows,
+                    int heads, int head_dim, float eps, cudaStream_t stream);
+
 }  // namespace sfq

@@ -407,6 +407,14 @@ void LinearRunner::forward_f32(const QuantWeight& w, const float* x, int rows, f
 
 // ---- free launchers ------------------------------------------------------------------------
 
+void launch_head_rmsnorm(__nv_bfloat16* x, const __nv_bfloat16* w, int rows, int heads, int dim, float eps, cudaStream_t stream) {
+  if (w == nullptr) throw std::invalid_argument("launch_head_rmsnorm: null weight");
+  sfq::head_norm_rope(x, heads * dim, w, nullptr, nullptr, rows, heads, dim, eps, stream);
+}
+void launch_rope_h3(__nv_bfloat16* x, const float* cos, const float* sin, int rows, int heads, int head_dim, cudaStream_t stream) {
+  if (cos == nullptr || sin == nullptr) throw std::invalid_argument("launch_rope_h3: null table");
+  sfq::head_norm_rope(x, heads * head_dim, nullptr, cos, sin, rows, heads, head_dim, 0.0f, stream);
+}
 void launch_adaln_expand(const float* w, const float* bias, const float* code, float* out, int num_t, int num_modality, int num_param,
                          int channels, int rank, cudaStream_t stream) {
   sfq::adaln_expand(w, bias, code, out, num_t, num_modality, num_param, channels, rank, stream);

@@ -66,3 +66,32 @@ def test_block_matches_cpu_composition(fuse_residual):
     # bf16 attention on the device vs fp64 on the host moves a few fp4 codes downstream: a looser, whole-block bar
     max_abs, rel_l2, corr = oracle.compare_bf16(x1, bits(dx))
     assert rel_l2 <= 3e-2 and corr > 0.999, (max_abs, rel_l2, corr)
+
+
+def test_qk_norm_and_rope_run_in_place_on_the_fused_projection():
+    rows, hidden, heads, ffn = 160, 256, 2, 512
+    rng = np.random.default_rng(17)
+    (_, wq), (_, wo), (_, w1), (_, w2) = (_linear(3 * hidden, hidden, rng), _linear(hidden, hidden, rng), _linear(ffn, hidden, rng),
+                                          _linear(hidden, ffn, rng))
+    ones = oracle.to_bf16(np.ones(hidden, np.float32))
+    qn = oracle.to_bf16((1 + 0.1 * rng.standard_normal(128)).astype(np.float32))
+    kn = oracle.to_bf16((1 + 0.1 * rng.standard_normal(128)).astype(np.float32))
+    ang = rng.uniform(-3, 3, (rows, 96))
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    names = ["scale_msa", "shift_msa", "gate_msa", "scale_mlp", "shift_mlp", "gate_mlp"]
+    mod = {n: dev((0.1 * rng.standard_normal((3, hidden))).astype(np.float32)) for n in names}
+    a = dev((np.arange(rows) % 3).astype(np.int32))
+    x = gaussian_bf16((rows, hidden), seed=18)
+    plain = Nvfp4Block(rows, hidden, heads, ffn)
+    plain.forward(bf16_tensor(x), BlockWeights(wq, wo, w1, w2, bf16_tensor(ones), bf16_tensor(ones)), mod, a)
+    raw = bits(plain.qkv)  # the projection as the GEMM left it
+    full = Nvfp4Block(rows, hidden, heads, ffn)
+    y = bf16_tensor(x)
+    full.forward(y, BlockWeights(wq, wo, w1, w2, bf16_tensor(ones), bf16_tensor(ones), bf16_tensor(qn), bf16_tensor(kn)), mod, a,
+                 rope=(dev(cos), dev(sin)))
+    torch.cuda.synchronize()
+    got = bits(full.qkv)
+    assert np.array_equal(got[:, :hidden], oracle.head_norm_rope(np.ascontiguousarray(raw[:, :hidden]), heads, qn, cos, sin, 1e-5))
+    assert np.array_equal(got[:, hidden:2 * hidden], oracle.head_norm_rope(np.ascontiguousarray(raw[:, hidden:2 * hidden]), heads, kn, cos, sin, 1e-5))
+    assert np.array_equal(got[:, 2 * hidden:], raw[:, 2 * hidden:])
+    assert torch.isfinite(y.float()).all() and sfq.device_status() == 0

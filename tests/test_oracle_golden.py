@@ -357,3 +357,29 @@ def test_lora_statement_known_answer():
     b = np.array([[256.0]], np.float32)
     got = oracle.from_bf16(oracle.lora_apply(x, a, b, 0, 1, oracle.to_bf16(np.zeros((1, 1), np.float32))))
     assert got[0, 0] == 256.0
+
+
+def test_head_norm_rope_statement_against_plain_formulas():
+    """QK-norm then MM-RoPE: x / rms(x) * w per head, then channel j rotated with j + 48 over the first 96 channels and
+    96..127 passed through (include/slopfab/cuda/nn_kernels.cuh:95-134), here against float64 numpy."""
+    rng = np.random.default_rng(4)
+    rows, heads = 5, 3
+    x = oracle.to_bf16(rng.standard_normal((rows, heads * 128)).astype(np.float32))
+    w = oracle.to_bf16((1 + 0.1 * rng.standard_normal(128)).astype(np.float32))
+    ang = rng.uniform(-3, 3, (rows, 96))
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    got = oracle.from_bf16(oracle.head_norm_rope(x, heads, w, cos, sin, 1e-6)).reshape(rows, heads, 128).astype(np.float64)
+    xf = oracle.from_bf16(x).reshape(rows, heads, 128).astype(np.float64)
+    n = xf / np.sqrt((xf ** 2).mean(axis=2, keepdims=True) + 1e-6) * oracle.from_bf16(w).astype(np.float64)
+    c, s = cos[:, None, :48].astype(np.float64), sin[:, None, :48].astype(np.float64)
+    want = n.copy()
+    want[:, :, :48] = n[:, :, :48] * c - n[:, :, 48:96] * s
+    want[:, :, 48:96] = n[:, :, 48:96] * c + n[:, :, :48] * s
+    assert np.abs(got - want).max() <= 3e-2  # two bf16 roundings of O(1..4) values
+    assert np.array_equal(got[:, :, 96:], oracle.from_bf16(oracle.head_norm_rope(x, heads, w, None, None, 1e-6)).reshape(rows, heads, 128)[:, :, 96:])
+    # rotation alone by 90 degrees swaps the halves with a sign
+    x1 = oracle.to_bf16(np.arange(128, dtype=np.float32)[None, :] / 16)
+    quarter = oracle.from_bf16(oracle.head_norm_rope(x1, 1, None, np.zeros((1, 96), np.float32), np.ones((1, 96), np.float32)))
+    v = oracle.from_bf16(x1)
+    assert np.array_equal(quarter[0, :48], -v[0, 48:96]) and np.array_equal(quarter[0, 48:96], v[0, :48])
+    assert np.array_equal(quarter[0, 96:], v[0, 96:])
