@@ -467,7 +467,7 @@ def run_case(name):
                                                                    seq, seq, heads, heads, 128, 0.0, ws.data_ptr(), nbytes.value,
                                                                    sfq.stream_ptr()))
         else:  # the library kernel on the same tensors, for the comparison line only
-            sh = lambda t: t.reshape(seq, heads, 128).transpose(0, 1)  # noqa: E731
+            sh = lambda t: t.reshape(1, seq, heads, 128).transpose(1, 2)  # noqa: E731  [1, heads, seq, 128] views, no copy
             fn = lambda i: torch.nn.functional.scaled_dot_product_attention(sh(q), sh(kk), sh(v))  # noqa: E731
     else:
         raise SystemExit("unknown case " + name)
