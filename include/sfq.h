@@ -245,9 +245,17 @@ SFQ_API int sfq_gemm_nvfp4(const uint8_t* d_a_packed, const uint8_t* d_a_scale_t
  * src/cuda/linear.cu:243-246. K % 8 == 0. */
 SFQ_API int sfq_gemm_bf16(const void* d_x_bf16, const void* d_w_bf16, const sfq_epilogue* ep, void* d_y_bf16,
                           int M, int N, int K, void* stream);
-/* Tuning knobs of the three GEMMs, for experiments: tile_n in {0,128,256}, band_m row tiles
- * per raster band (0 = default), max_ctas (0 = one per SM). Process-wide. */
-SFQ_API void sfq_gemm_tuning(int tile_n, int band_m, int max_ctas);
+/* Test hooks. Both are thread-local, apply only to the three stand-alone sfq_gemm_* entry points above when called from
+ * the same thread (a runner, the LoRA branch and the static entry point never read them), and are switched off again by
+ * passing zeros / -1. No counterpart in the reference.
+ *   variant: tile_n 128 or 256 selects the one-CTA kernel with that tile width (0 = the default CTA-pair kernel),
+ *     band_m the row tiles per raster band (0 = default), max_ctas the grid size (0 = one CTA per SM).
+ *   lost load: the producer warp leaves out the loads of pipeline iteration `iteration` (>= 0) while still announcing
+ *     their bytes, and every bounded wait gives up after `wait_cycles` clocks instead of about a second. The launch then
+ *     ends by the kernels' own abort path -- status code in sfq_device_status, loads drained, TMEM freed -- which is
+ *     what the test of that path checks; the output of such a launch is unspecified. */
+SFQ_API void sfq_test_gemm_variant(int tile_n, int band_m, int max_ctas);
+SFQ_API void sfq_test_gemm_lost_load(int iteration, long long wait_cycles);
 
 /* ---- LinearRunner (include/slopfab/cuda/linear.cuh:182-242) ---------------- */
 
@@ -327,14 +335,39 @@ SFQ_API int sfq_checkpoint_linear_host(sfq_checkpoint* c, const char* name, int 
  * nested blocks. Pointers are not dereferenced (host or device). Host only. */
 SFQ_API int sfq_weight_row_block(const sfq_quant_weight* fused, int parts, int index, sfq_quant_weight* out);
 
-/* ---- caller side: row -> adaLN table index ------------------------------------- */
+/* ---- caller side: token packing -> adaLN table index --------------------------- */
 
-/* build_indices + build_row_timesteps (include/slopfab/dit/packing.h:81-176, src/dit/packing.cpp:213-248,407-489)
- * reduced to what the norm kernel consumes. Rows are [text | condition video | condition audio | audio | video];
- * outputs have num_text + num_condition_video + num_condition_audio + num_audio_rows + num_video_rows entries:
- * h_tags (video 0, text 1, audio 2), h_indices (position of the row's timestep in the ascending unique set),
- * h_adaln = index * 3 + tag (the d_adaln_index of sfq_norm), h_unique2 (up to two values), *h_num_unique.
- * Any output except h_adaln may be null. Host only. */
+/* SequenceLayout (include/slopfab/dit/packing.h:37-73) reduced to the extents the row order depends on. Rows are
+ * packed [text | condition video | condition audio | audio | video]. */
+typedef struct sfq_sequence_layout {
+  int32_t num_text;
+  int32_t num_condition_video;
+  int32_t num_condition_audio;
+  int32_t condition_audio_is_explicit; /* 0: the legacy convention, num_condition_video is also the audio prefix */
+  int32_t num_audio_rows;
+  int32_t num_video_rows;
+} sfq_sequence_layout;
+
+/* build_indices (src/dit/packing.cpp:213-248): h_text [num_text], h_audio [num_audio_rows], h_video [conditions +
+ * num_video_rows] (every condition row, then the targets), h_tags [total] (video 0, text 1, audio 2). Any output may
+ * be null. Host only. */
+SFQ_API int sfq_build_indices(const sfq_sequence_layout* layout, int32_t* h_text, int32_t* h_audio, int32_t* h_video,
+                              int32_t* h_tags);
+/* build_row_timesteps, the two-timestep form (src/dit/packing.cpp:407-489): h_indices [total] (position of the row's
+ * timestep in the ascending set of those that occur), h_adaln [total] = index * 3 + max(tag, 0) -- the d_adaln_index
+ * of sfq_norm -- and up to unique_capacity entries of the set. h_tags: the caller's tags (padding rows carry -1), or
+ * null for the layout's own. h_indices, h_unique, h_num_unique may be null. Host only. */
+SFQ_API int sfq_build_row_timesteps(const sfq_sequence_layout* layout, const int32_t* h_tags, float video_t, float audio_t,
+                                    int32_t* h_indices, int32_t* h_adaln, float* h_unique, int unique_capacity,
+                                    int* h_num_unique);
+/* The four-timestep form for reference-conditioned requests (src/dit/packing.cpp:491-523): the first
+ * num_condition_video entries of the video list carry condition_video_t, the first num_condition_audio entries of the
+ * audio list condition_audio_t, the rest of the audio list audio_t, everything else video_t. Up to four unique values. */
+SFQ_API int sfq_build_row_timesteps4(const sfq_sequence_layout* layout, const int32_t* h_tags, float video_t, float audio_t,
+                                     float condition_video_t, float condition_audio_t, int32_t* h_indices,
+                                     int32_t* h_adaln, float* h_unique, int unique_capacity, int* h_num_unique);
+/* sfq_build_indices + sfq_build_row_timesteps in one call with the layout spelled out (the layout's own tags, at most
+ * two unique values). Any output except h_adaln may be null. Host only. */
 SFQ_API int sfq_build_adaln_index(int num_text, int num_condition_video, int num_condition_audio,
                                   int condition_audio_is_explicit, int num_audio_rows, int num_video_rows,
                                   float video_t, float audio_t, int32_t* h_tags, int32_t* h_indices,
@@ -412,21 +445,29 @@ SFQ_API int sfq_lora_bytes(const sfq_lora* l, size_t* weight_bytes, size_t* scra
  *   - Limit: align256(rows * in_features / 2) + ceil(rows/128)*128 * in_features/16 must not exceed
  *     SFQ_STATIC_SCRATCH_BYTES (e.g. 2048 rows x 13824, or 5800 rows x 5120). Larger calls are refused with
  *     SFQ_ERR_INVALID_ARGUMENT and a message; split the rows or use sfq_linear_forward.
- *   - No cudaMalloc / cudaFree / allocating library call is made, on any call.
+ *   - The entry point itself calls no cudaMalloc / cudaFree / allocating library routine, on any call. The CUDA
+ *     runtime does its own one-time work the first time each kernel variant runs on a device (it loads the
+ *     module's code and this array, and the launchers set a shared-memory attribute and look up one driver entry
+ *     point), so make one warm-up call per device, with the bias / activation combination you will use, before
+ *     you freeze allocations.
  *   - The first call on each device looks up the device address of the array (a host-side query, no
  *     allocation). Make that first call outside of any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels can overlap on the GPU (different
  *     streams, or graph branches) race on it. Serialise them on one stream.
- *   - The array keeps the previous call's bytes; the call rewrites everything it later reads and clears its
- *     status word, so earlier calls never leak into the result.
+ *   - The array keeps the previous call's bytes; the call rewrites everything it later reads, so earlier calls
+ *     never leak into the result.
  *   - A kernel that abandons a bounded wait records it in the array's own status word, not in the word
- *     sfq_device_status reads.
+ *     sfq_device_status reads: read it with sfq_static_status. The first code recorded stays until it is read.
  * Weight layout, bias, activation and numerics are those of sfq_gemm_nvfp4 fed by
  * sfq_quantize_nvfp4_block(GEMM_FEED); results are bit-identical to the runner's native NVFP4 path. */
 SFQ_API int sfq_linear_nvfp4_forward_static(const void* d_x_bf16, int rows, const uint8_t* d_w_packed,
                                             const uint8_t* d_w_scale_tiled, float global_scale, const void* d_bias,
                                             int bias_format, int activation, void* d_y_bf16, int out_features,
                                             int in_features, void* stream);
+/* Reads and clears the status word of sfq_linear_nvfp4_forward_static on the current device (no counterpart in
+ * the reference): 0, or the code of the first bounded wait that one of its kernels abandoned since the last
+ * read. Synchronises the device; allocates nothing. */
+SFQ_API int sfq_static_status(int* h_code);
 
 #ifdef __cplusplus
 }

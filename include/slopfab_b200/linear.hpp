@@ -86,15 +86,24 @@ public:
   void adopt(void* device_memory, size_t bytes);
   void* alloc(size_t bytes);
   template <typename T> T* alloc_n(size_t count) { return static_cast<T*>(alloc(count * sizeof(T))); }
-  void clear() { cursor_ = 0; }
+  void clear() { rewind(0); }
   size_t capacity() const { return capacity_; }
   size_t used() const { return cursor_; }
   const void* base() const { return base_; }
 
+  // Extension (not in the reference): lets a holder of carved bytes learn that they were given back. protect(end)
+  // says "the bytes below `end` are in use"; epoch() changes (to a value no Workspace has had before) whenever the
+  // cursor later drops below a protected mark, and on every resize / adopt. LinearRunner keeps the W4A8/W6A8
+  // expansion of prepare() under this guard.
+  void protect(size_t end) {
+    if (end > guard_) guard_ = end;
+  }
+  uint64_t epoch() const { return epoch_; }
+
   class Scope {
   public:
     explicit Scope(Workspace& w) : ws_(w), mark_(w.cursor_) {}
-    ~Scope() { ws_.cursor_ = mark_; }
+    ~Scope() { ws_.rewind(mark_); }
     Scope(const Scope&) = delete;
     Scope& operator=(const Scope&) = delete;
 
@@ -104,10 +113,21 @@ public:
   };
 
 private:
+  static uint64_t next_epoch();
+  void rewind(size_t mark) {
+    if (mark < guard_) {
+      guard_ = 0;
+      epoch_ = next_epoch();
+    }
+    cursor_ = mark;
+  }
+
   uint8_t* base_ = nullptr;
   size_t capacity_ = 0;
   size_t cursor_ = 0;
   bool owned_ = false;
+  size_t guard_ = 0;
+  uint64_t epoch_ = next_epoch();
 };
 
 size_t linear_workspace_bytes(const QuantWeight& w, int rows, ComputeType compute);
@@ -143,6 +163,7 @@ public:
 
 private:
   bool takes_native_nvfp4(const QuantWeight& w) const;
+  bool cached_valid(const QuantWeight& w, const Workspace& ws) const;
   const int8_t* expanded_weight(const QuantWeight& w, Workspace& ws, bool keep, cudaStream_t stream);
   void run_packed_int8(const QuantWeight& w, const int8_t* codes, const __nv_bfloat16* x, int rows, __nv_bfloat16* y,
                        Workspace& ws, cudaEvent_t codes_ready);
@@ -158,6 +179,7 @@ private:
   const int8_t* cached_codes_ = nullptr;
   const void* cached_arena_ = nullptr;
   size_t cached_end_ = 0;
+  uint64_t cached_epoch_ = 0;
   // A plain forward() of a W4A8/W6A8 layer expands the weight on this second stream while the activation is
   // quantized on the caller's; the GEMM waits for both. Created on first use.
   cudaStream_t side_ = nullptr;

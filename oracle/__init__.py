@@ -21,13 +21,21 @@ _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libslopfab_ref.so")
 
 
+def reference_root() -> str | None:
+    """Root of the reference tree: $SLOPFAB_REFERENCE, else a directory named `reference` beside this repository;
+    None when neither exists (the GPU box: only the prebuilt oracle/_ref travels there)."""
+    for cand in (os.environ.get("SLOPFAB_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "cuda")):
+            return cand
+    return None
+
+
 def build(with_reference: bool = True) -> None:
     """Compile the checkers (oracle always; the reference when its tree is present)."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
-    if with_reference and os.path.isdir(os.environ.get("SLOPFAB_REFERENCE", "/root/reference")):
-        subprocess.run(["make", "-C", _HERE, "-j8", "ref",
-                        "REF=" + os.environ.get("SLOPFAB_REFERENCE", "/root/reference")],
-                       check=True, capture_output=True)
+    root = reference_root() if with_reference else None
+    if root is not None:
+        subprocess.run(["make", "-C", _HERE, "-j8", "ref", "REF=" + root], check=True, capture_output=True)
 
 
 if not os.path.exists(_LIB_PATH):

@@ -480,3 +480,43 @@ REF_API int ref_dev_head_norm_rope(void* x, const void* w, const float* cos_tab,
     sync();
   });
 }
+
+// ---- token packing (src/dit/packing.cpp): the reference's own build_indices / build_row_timesteps, host only.
+// `tags_override` (may be null) replaces the tags build_indices produced, e.g. to mark padding rows with -1.
+#include "slopfab/dit/packing.h"
+namespace {
+slopfab::dit::SequenceLayout make_layout(const int32_t* f) {
+  slopfab::dit::SequenceLayout l;
+  l.num_text = f[0];
+  l.num_condition_video = f[1];
+  l.num_condition_audio = f[2];
+  l.condition_audio_is_explicit = f[3] != 0;
+  l.num_audio_rows = f[4];
+  l.num_video_rows = f[5];
+  return l;
+}
+}  // namespace
+REF_API int ref_build_indices(const int32_t* layout6, int32_t* text, int32_t* audio, int32_t* video, int32_t* tags) {
+  return guarded([&] {
+    const auto idx = slopfab::dit::build_indices(make_layout(layout6));
+    std::memcpy(text, idx.text.data(), idx.text.size() * 4);
+    std::memcpy(audio, idx.audio.data(), idx.audio.size() * 4);
+    std::memcpy(video, idx.video.data(), idx.video.size() * 4);
+    std::memcpy(tags, idx.tags.data(), idx.tags.size() * 4);
+  });
+}
+// timesteps: 2 values {video, audio} or 4 values {video, audio, condition video, condition audio}.
+REF_API int ref_build_row_timesteps(const int32_t* layout6, const int32_t* tags_override, const float* timesteps, int count,
+                                    int32_t* indices, int32_t* adaln, float* unique, int* num_unique) {
+  return guarded([&] {
+    const auto l = make_layout(layout6);
+    auto idx = slopfab::dit::build_indices(l);
+    if (tags_override) idx.tags.assign(tags_override, tags_override + idx.tags.size());
+    const auto rt = count == 4 ? slopfab::dit::build_row_timesteps(l, idx, timesteps[0], timesteps[1], timesteps[2], timesteps[3])
+                               : slopfab::dit::build_row_timesteps(l, idx, timesteps[0], timesteps[1]);
+    std::memcpy(indices, rt.indices.data(), rt.indices.size() * 4);
+    std::memcpy(adaln, rt.adaln.data(), rt.adaln.size() * 4);
+    std::memcpy(unique, rt.unique.data(), rt.unique.size() * 4);
+    *num_unique = int(rt.unique.size());
+  });
+}

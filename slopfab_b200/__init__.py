@@ -43,6 +43,11 @@ class Norm(C.Structure):
     _fields_ = [("d_norm_weight", V), ("d_scale", V), ("d_shift", V), ("d_adaln_index", V), ("eps", F)]
 
 
+class SequenceLayout(C.Structure):
+    _fields_ = [("num_text", C.c_int32), ("num_condition_video", C.c_int32), ("num_condition_audio", C.c_int32),
+                ("condition_audio_is_explicit", C.c_int32), ("num_audio_rows", C.c_int32), ("num_video_rows", C.c_int32)]
+
+
 class SfqError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"sfq error {code}: {message}")
@@ -83,7 +88,8 @@ def _load() -> C.CDLL:
         "sfq_gemm_int8": (I, [V, V, P(Epilogue), V, I, I, I, V]),
         "sfq_gemm_nvfp4": (I, [V, V, V, V, P(Epilogue), V, I, I, I, V]),
         "sfq_gemm_bf16": (I, [V, V, P(Epilogue), V, I, I, I, V]),
-        "sfq_gemm_tuning": (None, [I, I, I]),
+        "sfq_test_gemm_variant": (None, [I, I, I]),
+        "sfq_test_gemm_lost_load": (None, [I, C.c_longlong]),
         "sfq_runner_create": (I, [V, P(V)]),
         "sfq_runner_destroy": (None, [V]),
         "sfq_runner_set_native": (I, [V, I]),
@@ -96,6 +102,10 @@ def _load() -> C.CDLL:
         "sfq_linear_prepare": (I, [V, P(QuantWeight), V, SZ, P(V), P(SZ)]),
         "sfq_linear_forward_prepared": (I, [V, P(QuantWeight), V, V, I, V, V, SZ]),
         "sfq_linear_nvfp4_forward_static": (I, [V, I, V, V, F, V, I, I, V, I, I, V]),
+        "sfq_static_status": (I, [P(I)]),
+        "sfq_build_indices": (I, [P(SequenceLayout), V, V, V, V]),
+        "sfq_build_row_timesteps": (I, [P(SequenceLayout), V, F, F, V, V, V, I, P(I)]),
+        "sfq_build_row_timesteps4": (I, [P(SequenceLayout), V, F, F, F, F, V, V, V, I, P(I)]),
         "sfq_build_adaln_index": (I, [I, I, I, I, I, I, F, F, V, V, V, V, P(I)]),
         "sfq_weight_row_block": (I, [P(QuantWeight), I, I, P(QuantWeight)]),
         "sfq_checkpoint_open": (I, [C.c_char_p, P(V)]),
@@ -129,10 +139,10 @@ EXPORTS = ("sfq_last_error sfq_version sfq_quant_weight_init sfq_device_status s
            "sfq_pack_w6a8 sfq_pack_int8 sfq_unpack_nvfp4_bf16 sfq_unpack_w4a8_int8 sfq_unpack_w6a8_int8 "
            "sfq_unpack_int8_bf16 sfq_unpack_int8_f16 sfq_unpack_f8e4m3_bf16 sfq_unpack_nf4_bf16 sfq_pre_quant_scale sfq_rmsnorm sfq_convrot sfq_quantize_int8_token "
            "sfq_quantize_nvfp4_block sfq_nvfp4_act_scale_bytes sfq_gelu_tanh sfq_swiglu sfq_add_gated sfq_gemm_int8 "
-           "sfq_gemm_nvfp4 sfq_gemm_bf16 sfq_gemm_tuning sfq_runner_create sfq_runner_destroy sfq_runner_set_native "
+           "sfq_gemm_nvfp4 sfq_gemm_bf16 sfq_test_gemm_variant sfq_test_gemm_lost_load sfq_runner_create sfq_runner_destroy sfq_runner_set_native "
            "sfq_runner_native sfq_runner_set_activation sfq_linear_workspace_bytes sfq_linear_dense_weight_bytes "
            "sfq_linear_activation_workspace_bytes sfq_linear_forward sfq_linear_prepare "
-           "sfq_linear_forward_prepared sfq_linear_nvfp4_forward_static sfq_build_adaln_index sfq_weight_row_block sfq_checkpoint_open "
+           "sfq_linear_forward_prepared sfq_linear_nvfp4_forward_static sfq_static_status sfq_build_indices sfq_build_row_timesteps sfq_build_row_timesteps4 sfq_build_adaln_index sfq_weight_row_block sfq_checkpoint_open "
            "sfq_checkpoint_close sfq_checkpoint_count sfq_checkpoint_tensor sfq_checkpoint_metadata sfq_checkpoint_linear sfq_checkpoint_linear_host "
            "sfq_linear_forward_f32 sfq_adaln_expand sfq_head_norm_rope sfq_attention_workspace_bytes sfq_attention_forward sfq_lora_create sfq_lora_destroy sfq_lora_attach sfq_lora_attach_staged sfq_lora_apply sfq_lora_bytes").split()
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
@@ -147,6 +157,13 @@ def device_status() -> int:
     """Reads and clears the device status word (synchronises). Non-zero = a kernel gave up a bounded wait."""
     code = I(0)
     check(lib.sfq_device_status(C.byref(code)))
+    return code.value
+
+
+def static_status() -> int:
+    """Reads and clears the status word of sfq_linear_nvfp4_forward_static (its kernels do not write the word above)."""
+    code = I(0)
+    check(lib.sfq_static_status(C.byref(code)))
     return code.value
 
 

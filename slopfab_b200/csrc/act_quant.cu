@@ -19,6 +19,7 @@
 // integer Newton iteration; the butterfly adds associate left to right; bf16
 // roundings sit where the reference stores bf16 between its kernels.
 #include "kernels.cuh"
+#include "runtime.h"
 
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
@@ -415,20 +416,12 @@ template <int MODE> void launch_fused(const FusedArgs& a, int grid_rows, cudaStr
     throw std::invalid_argument(std::string(what) + ": modulation needs scale, shift and the row index");
   const int threads = ((a.dim / 16 + 31) / 32) * 32;
   const size_t smem = size_t(threads) * 17 * 4 + (256 + 16) * 4 + (a.norm_w ? size_t(a.dim) * 2 : 0);
-  static size_t reserved = 0;  // per-instantiation high-water mark
-  if (smem > 48 * 1024 && smem > reserved) {
-    const cudaError_t e = cudaFuncSetAttribute(fused_act_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
-    reserved = smem;
-  }
+  reserve_dynamic_smem(reinterpret_cast<const void*>(&fused_act_kernel<MODE>), smem, what);
   // As many CTAs as stay resident at once; each walks rows with a stride of the grid size.
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_act_kernel<MODE>, threads, smem) != cudaSuccess || per_sm < 1)
     per_sm = 1;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = std::min(grid_rows, per_sm * sms);
+  const int grid = std::min(grid_rows, per_sm * device_sm_count());
   fused_act_kernel<MODE><<<grid, threads, smem, stream>>>(a);
   check_launch(what);
 }

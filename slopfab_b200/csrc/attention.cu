@@ -378,10 +378,7 @@ void attention_forward(const __nv_bfloat16* q, int ld_q, const __nv_bfloat16* k,
   if (workspace_bytes < attention_workspace_bytes(seq_kv, kv_heads, head_dim)) throw std::invalid_argument("sfq attention: workspace too small");
   if (out == q || out == k || out == v) throw std::invalid_argument("sfq attention: out may not alias q, k or v");
   if ((seq_q + kTile - 1) / kTile > 0x7FFFFFFF / 2 || heads > 65535) throw std::invalid_argument("sfq attention: too many query tiles or heads");
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] { attr_err = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem); });
-  if (attr_err != cudaSuccess) throw std::runtime_error(std::string("sfq attention: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
+  reserve_dynamic_smem(reinterpret_cast<const void*>(&attention_kernel), kAttnSmem, "sfq attention");
 
   const int ld_t = padded_keys(seq_kv);
   __nv_bfloat16* vt = static_cast<__nv_bfloat16*>(workspace);

@@ -114,7 +114,7 @@ sfq::GemmArgs to_gemm(const sfq_epilogue* ep, void* y, int M, int N, int K) {
     g.gate_index = ep->d_gate_index;
   }
   g.status = sfq::device_status_word();
-  sfq::apply_tuning(g);
+  sfq::apply_test_hooks(g);
   return g;
 }
 
@@ -313,6 +313,7 @@ int sfq_attention_forward(const void* d_q_bf16, int ld_q, const void* d_k_bf16, 
                            workspace_bytes, as_stream(stream));
   });
 }
-void sfq_gemm_tuning(int tile_n, int band_m, int max_ctas) { sfq::set_tuning(tile_n, band_m, max_ctas); }
+void sfq_test_gemm_variant(int tile_n, int band_m, int max_ctas) { sfq::set_test_gemm_variant(tile_n, band_m, max_ctas); }
+void sfq_test_gemm_lost_load(int iteration, long long wait_cycles) { sfq::set_test_gemm_lost_load(iteration, wait_cycles); }
 
 }  // extern "C"

@@ -22,7 +22,10 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <cmath>
+#include <cstdint>
 #include <cstring>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
@@ -112,6 +115,19 @@ struct sfq_checkpoint {
   std::unordered_map<std::string, void*> device_f32;  // fp32 conversions, by tensor name
   std::unordered_map<std::string, std::vector<float>> host_f32;  // the same conversions for the host view
   bool host_view = false;  // linear() hands out host pointers (into the mapping / host_f32) instead of uploading
+  std::mutex mutex;        // serialises linear(): the flag above and the caches are per handle
+  int upload_device = -1;  // the device the caches' pointers live on (set by the first upload)
+
+  // Uploads are cached by tensor name, so every pointer handed out belongs to one device: the one that was current at
+  // the first upload. Asking from another device is refused instead of returning foreign pointers.
+  void bind_device() {
+    int dev = -1;
+    check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (upload_device < 0) upload_device = dev;
+    if (dev != upload_device)
+      throw std::runtime_error("checkpoint: this handle uploaded its tensors to device " + std::to_string(upload_device) +
+                               "; open the file again for device " + std::to_string(dev));
+  }
 
   ~sfq_checkpoint() {
     for (auto& kv : device) cudaFree(kv.second);
@@ -171,6 +187,13 @@ struct sfq_checkpoint {
         if (v < 0) throw std::runtime_error("checkpoint: negative dimension in '" + kv.first + "'");
         t.shape.push_back(v);
       }
+      {  // the element count must not wrap: a wrapped product could agree with the byte count checked below
+        int64_t n = 1;
+        for (int64_t d : t.shape) {
+          if (d != 0 && n > INT64_MAX / d) throw std::runtime_error("checkpoint: the shape of '" + kv.first + "' overflows");
+          n *= d;
+        }
+      }
       const int64_t b = off->array[0].as_int(), e = off->array[1].as_int();
       if (b < 0 || e < b || size_t(e) > data_bytes) throw std::runtime_error("checkpoint: offsets of '" + kv.first + "' leave the file");
       t.data = data0 + b;
@@ -186,6 +209,7 @@ struct sfq_checkpoint {
   // ---- uploads ("ptr" and "f32" of the reference's loader)
   const void* upload(const std::string& name) {
     if (host_view) return at(name).data;
+    bind_device();
     const auto it = device.find(name);
     if (it != device.end()) return it->second;
     const Tensor& t = at(name);
@@ -229,6 +253,7 @@ struct sfq_checkpoint {
       if (hit == host_f32.end()) hit = host_f32.emplace(name, to_f32(*t)).first;
       return hit->second.data();
     }
+    bind_device();
     const auto it = device_f32.find(name);
     if (it != device_f32.end()) return static_cast<const float*>(it->second);
     const std::vector<float> host = to_f32(*t);
@@ -471,6 +496,7 @@ int sfq_checkpoint_metadata(const sfq_checkpoint* c, const char* key, char* buff
 int sfq_checkpoint_linear(sfq_checkpoint* c, const char* name, int out_features, int in_features, sfq_quant_weight* out) {
   return guarded([&] {
     if (c == nullptr || name == nullptr || out == nullptr) throw std::invalid_argument("sfq_checkpoint_linear: null argument");
+    std::lock_guard<std::mutex> lock(c->mutex);
     c->host_view = false;
     c->linear(name, out_features, in_features, out);
   });
@@ -479,6 +505,7 @@ int sfq_checkpoint_linear(sfq_checkpoint* c, const char* name, int out_features,
 int sfq_checkpoint_linear_host(sfq_checkpoint* c, const char* name, int out_features, int in_features, sfq_quant_weight* out) {
   return guarded([&] {
     if (c == nullptr || name == nullptr || out == nullptr) throw std::invalid_argument("sfq_checkpoint_linear_host: null argument");
+    std::lock_guard<std::mutex> lock(c->mutex);
     c->host_view = true;
     c->linear(name, out_features, in_features, out);
   });

@@ -11,6 +11,7 @@
 
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
+#include "runtime.h"
 
 namespace sfq {
 namespace {
@@ -35,6 +36,7 @@ struct Shared {  // lives after the stage ring
   uint64_t sf_full[8];   // nvfp4: the scale factors of stage s are in TMEM slot s
   uint32_t tmem_base;
   volatile int abort;
+  long long wait_cycles;  // limit of every bounded wait of this launch
   alignas(16) float col_scale[2][256];  // per-column epilogue operands of the tile being drained
   alignas(16) float bias[2][256];
 };
@@ -47,7 +49,7 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, Shar
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (sh->abort) return false;
-    if (clock_now() - start > kWaitCycles) {
+    if (clock_now() - start > sh->wait_cycles) {
       atomicCAS(status, 0, code);
       sh->abort = 1;
       return false;
@@ -214,15 +216,7 @@ CUtensorMap make_map(const void* base, size_t rows, size_t row_bytes, int box_ro
   return m;
 }
 
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 148;
-  }();
-  return n;
-}
+int sm_count() { return device_sm_count(); }
 
 }  // namespace
 }  // namespace sfq

@@ -35,7 +35,9 @@ struct GemmArgs {
   int max_ctas = 0;       // 0 = one CTA per SM
   int tile_n = 0;         // 128 or 256 select the one-CTA kernel with that tile width; 0 = default (CTA pairs, 256 x 256)
   int tail_split = -1;    // CTA-pair kernel: trailing tiles cut into two 128-column halves (-1 = let the launcher choose)
-  int debug = 0;          // experiment switches (environment SFQ_GEMM_DEBUG); 0 in normal use
+  // test hooks (see runtime.h); never set on a runner's path
+  int test_drop_iteration = -1;  // the producer skips the loads of this pipeline iteration (bytes still announced)
+  long long wait_cycles = 0;     // limit of every bounded wait in clocks; 0 = the default (about a second)
 };
 
 // All three throw std::invalid_argument / std::runtime_error before launching on a contract violation.

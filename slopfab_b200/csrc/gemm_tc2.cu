@@ -113,6 +113,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       mbar_init(smem_u32(&sh->acc_empty[a]), 16);  // leader: eight epilogue warps of each CTA
     }
     sh->abort = 0;
+    sh->wait_cycles = g.wait_cycles > 0 ? g.wait_cycles : kWaitCycles;
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -144,26 +145,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint8_t* stage = smem + s * C::kStageBytes;
             const uint32_t bar = smem_u32(&sh->full[s]);  // the loads redirect it to the leader's copy
             if (rank == 0) mbar_arrive_expect_tx(bar, narrow ? C::kTxBytesNarrow : C::kTxBytes);
-            tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
-            if (swiglu)
-              tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * (BN / 2) + int(rank) * inner, bar);
-            else if (!narrow)
-              tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * BN + int(rank) * (BN / 2), bar);
-            else
-              tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b_narrow, ks * kSlabBytes, tn * BN + n_off + int(rank) * (BN / 4),
-                               bar);
-            if constexpr (KIND == kNvfp4) {
-              // scale arrays as [128-row tile][K/64 atoms of 512 bytes], 8-byte elements: 256 elements = 4 atoms
-              tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB), &map_sfa, ks * 256, tm * 2 + int(rank), bar);
-              if (swiglu) {  // scales of the gate rows' tile and of the up rows' tile, one 128-row tile each
-                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256, tn, bar);
-                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa + C::kStageSfb / 2), &map_sfb_narrow,
-                                 ks * 256, inner / 128 + tn, bar);
-              } else if (!narrow) {
-                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
-              } else {
-                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256,
-                                 tn * 2 + n_off / 128, bar);
+            if (int(it) != g.test_drop_iteration) {  // test hook: that iteration announces its bytes and leaves the loads out
+              tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
+              if (swiglu)
+                tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * (BN / 2) + int(rank) * inner, bar);
+              else if (!narrow)
+                tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * BN + int(rank) * (BN / 2), bar);
+              else
+                tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b_narrow, ks * kSlabBytes, tn * BN + n_off + int(rank) * (BN / 4),
+                                 bar);
+              if constexpr (KIND == kNvfp4) {
+                // scale arrays as [128-row tile][K/64 atoms of 512 bytes], 8-byte elements: 256 elements = 4 atoms
+                tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB), &map_sfa, ks * 256, tm * 2 + int(rank), bar);
+                if (swiglu) {  // scales of the gate rows' tile and of the up rows' tile, one 128-row tile each
+                  tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256, tn, bar);
+                  tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa + C::kStageSfb / 2), &map_sfb_narrow,
+                                   ks * 256, inner / 128 + tn, bar);
+                } else if (!narrow) {
+                  tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb, ks * 256, tn * 2, bar);
+                } else {
+                  tma_load_2d_pair(smem_u32(stage + C::kStageA + C::kStageB + C::kStageSfa), &map_sfb_narrow, ks * 256,
+                                   tn * 2 + n_off / 128, bar);
+                }
               }
             }
           }
@@ -439,7 +442,8 @@ CUtensorMap make_scale_map(const void* base, size_t row_tiles, size_t k_atoms, i
 
 template <int KIND, int ACC, int EPI> int max_pairs() {  // the same for both TAIL variants
   // Clusters of two need both CTAs in one GPC; ask the runtime how many pairs fit at once.
-  static int n = [] {
+  static PerDevice<int> cache;
+  return cache.get([] {
     using C = PairCfg<KIND, ACC>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * sm_count());
@@ -459,21 +463,14 @@ template <int KIND, int ACC, int EPI> int max_pairs() {  // the same for both TA
       return 0;
     }
     return clusters;
-  }();
-  return n;
+  });
 }
 
 template <int KIND, int ACC, int EPI>
 bool launch_pair_epi(const void* a, const void* w, size_t row_bytes, const GemmArgs& g, cudaStream_t stream) {
   using C = PairCfg<KIND, ACC>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_pair_kernel<KIND, ACC, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(gemm_pair_kernel<KIND, ACC, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  });
-  if (attr_err != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
+  reserve_dynamic_smem(reinterpret_cast<const void*>(&gemm_pair_kernel<KIND, ACC, EPI, false>), C::kSmemBytes, "sfq gemm");
+  reserve_dynamic_smem(reinterpret_cast<const void*>(&gemm_pair_kernel<KIND, ACC, EPI, true>), C::kSmemBytes, "sfq gemm");
   const int pairs_fit = max_pairs<KIND, ACC, EPI>();
   if (pairs_fit <= 0) return false;  // no room for clusters of two: the caller uses the one-CTA kernel
   const CUtensorMap ma = make_map(a, size_t(g.M), row_bytes, kBM);
@@ -504,7 +501,6 @@ bool launch_pair_epi(const void* a, const void* w, size_t row_bytes, const GemmA
   const bool few_waves = KIND == kNvfp4 ? 2 * tiles <= pairs_cap : tiles < 8 * pairs_cap;
   ga.tail_split = g.tail_split >= 0 ? std::min(g.tail_split, tiles) : ((r > 0 && 2 * r <= pairs_cap && few_waves) ? r : 0);
   if (g.act == SFQ_ACT_SWIGLU) ga.tail_split = 0;  // a tile must keep its gate and up halves together
-  if (g.debug & 1) ga.tail_split = 0;  // experiment switch: whole tiles only
   const int pairs = std::min(tiles + ga.tail_split, pairs_cap);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);

@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <climits>
+#include <atomic>
 #include <stdexcept>
 #include <string>
 
@@ -70,7 +71,6 @@ sfq::GemmArgs epilogue_for(const QuantWeight& w, int rows, __nv_bfloat16* y, int
   g.act = activation;
   if (activation == SFQ_ACT_SWIGLU) g.ldy = w.out_features / 2;  // y is [rows, out_features / 2]
   g.status = sfq::device_status_word();
-  sfq::apply_tuning(g);
   return g;
 }
 
@@ -92,6 +92,11 @@ size_t QuantWeight::stored_bytes() const {  // src/cuda/linear.cu:9-18
 
 // ---- Workspace -----------------------------------------------------------------------------
 
+uint64_t Workspace::next_epoch() {
+  static std::atomic<uint64_t> counter{0};
+  return ++counter;
+}
+
 Workspace::~Workspace() {
   if (owned_ && base_) cudaFree(base_);
 }
@@ -107,6 +112,8 @@ void Workspace::resize(size_t bytes) {
   base_ = nullptr;
   capacity_ = 0;
   cursor_ = 0;
+  guard_ = 0;
+  epoch_ = next_epoch();
   owned_ = true;
   if (want == 0) return;
   void* p = nullptr;
@@ -124,6 +131,8 @@ void Workspace::adopt(void* device_memory, size_t bytes) {
   base_ = device_memory ? static_cast<uint8_t*>(device_memory) + skip : nullptr;
   capacity_ = bytes > skip ? bytes - skip : 0;
   cursor_ = 0;
+  guard_ = 0;
+  epoch_ = next_epoch();
   owned_ = false;
 }
 
@@ -214,9 +223,18 @@ void LinearRunner::ensure_side_stream() {
   if (e != cudaSuccess) throw std::runtime_error(std::string("LinearRunner: cannot create the side stream: ") + cudaGetErrorString(e));
 }
 
+// The expansion prepare() kept is trusted only while the same arena has not given those bytes back: a clear(), a Scope
+// that unwinds below them, a resize or an adopt each move the arena to a new epoch. (Like the dense weight the reference's
+// prepare() returns, it also assumes that the packed weight itself is not rewritten between prepare() and the calls that
+// follow it.)
+bool LinearRunner::cached_valid(const QuantWeight& w, const Workspace& ws) const {
+  return cached_key_ == w.data && cached_codes_ != nullptr && cached_arena_ == ws.base() && cached_epoch_ == ws.epoch() &&
+         ws.used() >= cached_end_;
+}
+
 const int8_t* LinearRunner::expanded_weight(const QuantWeight& w, Workspace& ws, bool keep, cudaStream_t stream) {
   // A previous prepare() on this weight in this arena, still below the cursor: reuse it.
-  if (cached_key_ == w.data && cached_arena_ == ws.base() && cached_codes_ != nullptr && ws.used() >= cached_end_)
+  if (cached_valid(w, ws))
     return cached_codes_;
   int8_t* codes = ws.alloc_n<int8_t>(size_t(w.out_features) * w.in_features);
   if (w.format == QuantFormat::kW6A8)
@@ -230,12 +248,15 @@ const int8_t* LinearRunner::expanded_weight(const QuantWeight& w, Workspace& ws,
     cached_codes_ = codes;
     cached_arena_ = ws.base();
     cached_end_ = ws.used();
+    ws.protect(cached_end_);  // the arena reports (through its epoch) when these bytes are handed out again
+    cached_epoch_ = ws.epoch();
   }
   return codes;
 }
 
 const __nv_bfloat16* LinearRunner::prepare(const QuantWeight& w, Workspace& ws) {
   if (!initialised_) throw std::runtime_error("LinearRunner::prepare: init() not called");
+  cached_key_ = nullptr;  // every prepare() starts a new chunk loop: whatever an older one kept is forgotten
   if (is_packed_int8(w.format)) {
     // Returns null like the reference (there is no dense bf16 form), but leaves the int8 expansion
     // carved in `ws` so the chunk loop that follows does not redo it.
@@ -284,8 +305,8 @@ void LinearRunner::forward(const QuantWeight& w, const __nv_bfloat16* x, int row
   if (!initialised_) throw std::runtime_error("LinearRunner::forward: init() not called");
   if (rows <= 0) return;
   Workspace::Scope scope(ws);
+  cached_key_ = nullptr;  // a plain forward never trusts an older expansion, of this weight or any other
   if (is_packed_int8(w.format)) {
-    cached_key_ = nullptr;  // a plain forward never trusts an older expansion
     forward_prepared(w, nullptr, x, rows, y, ws);
     return;
   }
@@ -300,7 +321,7 @@ void LinearRunner::forward_prepared(const QuantWeight& w, const __nv_bfloat16* w
 
   if (is_packed_int8(w.format)) {
     validate_packed_int8(w);
-    if (cached_key_ == w.data && cached_arena_ == ws.base() && cached_codes_ != nullptr && ws.used() >= cached_end_) {
+    if (cached_valid(w, ws)) {
       run_packed_int8(w, cached_codes_, x, rows, y, ws, nullptr);  // expansion kept by prepare()
       return;
     }

@@ -120,14 +120,12 @@ void LoraRunner::apply(const void* key, const __nv_bfloat16* input, int rows, __
       down.M = count, down.N = f.rank, down.K = f.in;
       down.y = hidden_, down.ldy = f.rank;
       down.status = sfq::device_status_word();
-      sfq::apply_tuning(down);
       sfq::gemm_bf16(input + size_t(row) * f.in, f.a_ptr, down, stream);
       sfq::GemmArgs up;  // y += hidden B^T
       up.M = count, up.N = f.out, up.K = f.rank;
       up.y = output + size_t(row) * f.out, up.ldy = f.out;
       up.gate = unit_gate_, up.gate_index = gate_index_;
       up.status = down.status;
-      sfq::apply_tuning(up);
       sfq::gemm_bf16(hidden_, f.b_ptr, up, stream);
     }
   }

@@ -13,6 +13,7 @@
 //     one 16-bit store per element and come back as two 16-byte rows, so the second float transpose disappears;
 //   * one block-wide barrier per row pair: every thread folds the per-warp maxima itself.
 #include "kernels.cuh"
+#include "runtime.h"
 
 #include <algorithm>
 #include <stdexcept>
@@ -326,19 +327,11 @@ quantize_int8_pairs_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __r
 template <int NC>
 void launch_pairs_wide(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, int threads, cudaStream_t stream) {
   const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 2 * 32 * sizeof(uint32_t);
-  static size_t reserved = 0;  // per instantiation
-  if (smem > 48 * 1024 && smem > reserved) {
-    const cudaError_t e = cudaFuncSetAttribute(quantize_int8_pairs_wide_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
-    reserved = smem;
-  }
+  reserve_dynamic_smem(reinterpret_cast<const void*>(&quantize_int8_pairs_wide_kernel<NC>), smem, "quantize_int8_token");
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_int8_pairs_wide_kernel<NC>, threads, smem) != cudaSuccess || per_sm < 1)
     per_sm = 1;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = std::min((rows + 1) / 2, per_sm * sms);
+  const int grid = std::min((rows + 1) / 2, per_sm * device_sm_count());
   quantize_int8_pairs_wide_kernel<NC><<<grid, threads, smem, stream>>>(x, q, row_scale, rows, dim);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
@@ -347,19 +340,11 @@ void launch_pairs_wide(const __nv_bfloat16* x, int8_t* q, float* row_scale, int 
 template <int MAXT, int MINB>
 void launch_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, int threads, cudaStream_t stream) {
   const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 2 * 32 * sizeof(uint32_t);
-  static size_t reserved = 0;  // per instantiation
-  if (smem > 48 * 1024 && smem > reserved) {
-    const cudaError_t e = cudaFuncSetAttribute(quantize_int8_pairs_kernel<MAXT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
-    reserved = smem;
-  }
+  reserve_dynamic_smem(reinterpret_cast<const void*>(&quantize_int8_pairs_kernel<MAXT, MINB>), smem, "quantize_int8_token");
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_int8_pairs_kernel<MAXT, MINB>, threads, smem) != cudaSuccess || per_sm < 1)
     per_sm = 1;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = std::min((rows + 1) / 2, per_sm * sms);
+  const int grid = std::min((rows + 1) / 2, per_sm * device_sm_count());
   quantize_int8_pairs_kernel<MAXT, MINB><<<grid, threads, smem, stream>>>(x, q, row_scale, rows, dim);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));

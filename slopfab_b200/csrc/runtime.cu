@@ -1,16 +1,23 @@
 #include "runtime.h"
 
 #include <cstdlib>
+#include <map>
 #include <mutex>
+#include <utility>
 #include <stdexcept>
 #include <string>
 
 namespace sfq {
 namespace {
-constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
 int* g_status[kMaxDevices] = {};
-int g_tile_n = 0, g_band_m = 0, g_max_ctas = 0;
+// Test hooks of the stand-alone GEMM entry points; each thread has its own, a runner never reads them.
+struct GemmHooks {
+  int tile_n = 0, band_m = 0, max_ctas = 0;
+  int drop_iteration = -1;
+  long long wait_cycles = 0;
+};
+thread_local GemmHooks t_hooks;
 
 int current_device() {
   int dev = -1;
@@ -51,22 +58,48 @@ bool device_is_sm100() {
   return major == 10;
 }
 
-void set_tuning(int tile_n, int band_m, int max_ctas) {
-  std::lock_guard<std::mutex> lock(g_mutex);
-  g_tile_n = (tile_n == 128 || tile_n == 256) ? tile_n : 0;
-  g_band_m = band_m > 0 ? band_m : 0;
-  g_max_ctas = max_ctas > 0 ? max_ctas : 0;
+int current_device_index() { return current_device(); }
+
+int device_sm_count() {
+  static PerDevice<int> cache;
+  return cache.get([] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  });
 }
 
-void apply_tuning(GemmArgs& g) {
-  g.tile_n = g_tile_n;
-  g.band_m = g_band_m;
-  g.max_ctas = g_max_ctas;
-  static const int debug = [] {
-    const char* e = std::getenv("SFQ_GEMM_DEBUG");
-    return e ? std::atoi(e) : 0;
-  }();
-  g.debug = debug;
+void reserve_dynamic_smem(const void* kernel, size_t bytes, const char* what) {
+  if (bytes <= 48 * 1024) return;  // within the default limit
+  static std::mutex m;
+  static std::map<std::pair<int, const void*>, size_t> reserved;
+  const int dev = current_device();
+  std::lock_guard<std::mutex> lock(m);
+  size_t& have = reserved[{dev, kernel}];
+  if (bytes <= have) return;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": cannot reserve shared memory: " + cudaGetErrorString(e));
+  have = bytes;
+}
+
+void set_test_gemm_variant(int tile_n, int band_m, int max_ctas) {
+  t_hooks.tile_n = (tile_n == 128 || tile_n == 256) ? tile_n : 0;
+  t_hooks.band_m = band_m > 0 ? band_m : 0;
+  t_hooks.max_ctas = max_ctas > 0 ? max_ctas : 0;
+}
+
+void set_test_gemm_lost_load(int iteration, long long wait_cycles) {
+  t_hooks.drop_iteration = iteration >= 0 ? iteration : -1;
+  t_hooks.wait_cycles = wait_cycles > 0 ? wait_cycles : 0;
+}
+
+void apply_test_hooks(GemmArgs& g) {
+  g.tile_n = t_hooks.tile_n;
+  g.band_m = t_hooks.band_m;
+  g.max_ctas = t_hooks.max_ctas;
+  g.test_drop_iteration = t_hooks.drop_iteration;
+  g.wait_cycles = t_hooks.wait_cycles;
 }
 
 }  // namespace sfq

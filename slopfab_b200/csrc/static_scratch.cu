@@ -85,10 +85,9 @@ int sfq_linear_nvfp4_forward_static(const void* d_x_bf16, int rows, const uint8_
     uint8_t* xq = base + kStatusBytes;
     uint8_t* xs = xq + packed_bytes;
     // The array keeps whatever the previous call left. The quantizer overwrites every byte the GEMM
-    // reads (packed rows, scale tiles including their zeroed padding rows); only the status word
-    // must start from zero.
-    const cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), s);
-    if (e != cudaSuccess) throw std::runtime_error(std::string("sfq_linear_nvfp4_forward_static: ") + cudaGetErrorString(e));
+    // reads (packed rows, scale tiles including their zeroed padding rows). The status word is zero
+    // when the module is loaded and is cleared only by sfq_static_status, so a code that one call's
+    // kernels recorded survives the calls after it until the host has read it.
     sfq::quantize_nvfp4_block(static_cast<const __nv_bfloat16*>(d_x_bf16), sfq::NormArgs{}, xq, xs, nullptr, rows,
                               in_features, SFQ_NVFP4_ACT_GEMM_FEED, s);
     sfq::GemmArgs g;
@@ -104,12 +103,39 @@ int sfq_linear_nvfp4_forward_static(const void* d_x_bf16, int rows, const uint8_
     g.a_scale_tiled = xs;
     g.w_scale_tiled = d_w_scale_tiled;
     g.status = status;
-    sfq::apply_tuning(g);
-    sfq::gemm_nvfp4(xq, d_w_packed, g, s);
+      sfq::gemm_nvfp4(xq, d_w_packed, g, s);
     return SFQ_OK;
   } catch (const std::invalid_argument& ex) {
     sfq_capi::set_error(ex.what());
     return SFQ_ERR_INVALID_ARGUMENT;
+  } catch (const std::exception& ex) {
+    sfq_capi::set_error(ex.what());
+    return SFQ_ERR_RUNTIME;
+  }
+}
+
+// Declared in include/sfq.h. Reads and clears the status word that the kernels of the entry point above
+// write: a plain copy through the address resolved by the first call on this device, no allocation.
+int sfq_static_status(int* h_code) {
+  try {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+      throw std::runtime_error(std::string("sfq: no usable CUDA device: ") + cudaGetErrorString(e));
+    unsigned char* base = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      base = g_device_address[dev];
+    }
+    int code = 0;
+    if (base != nullptr) {  // otherwise no call has run on this device yet: nothing can have been recorded
+      e = cudaDeviceSynchronize();
+      if (e == cudaSuccess) e = cudaMemcpy(&code, base, sizeof(int), cudaMemcpyDeviceToHost);
+      if (e == cudaSuccess && code != 0) e = cudaMemset(base, 0, sizeof(int));
+      if (e != cudaSuccess) throw std::runtime_error(std::string("sfq_static_status: ") + cudaGetErrorString(e));
+    }
+    if (h_code) *h_code = code;
+    return SFQ_OK;
   } catch (const std::exception& ex) {
     sfq_capi::set_error(ex.what());
     return SFQ_ERR_RUNTIME;

@@ -87,6 +87,57 @@ int main(int argc, char** argv) {
   cudaMemcpy(y.data(), dy, y.size() * 2, cudaMemcpyDeviceToHost);
   cudaMemcpy(y2.data(), dy2, y2.size() * 2, cudaMemcpyDeviceToHost);
   if (y != y2) return 5;
+
+  // An arena that was cleared and carved again between prepare() and forward_prepared() -- legal with the reference,
+  // which expands the packed weight on every call -- must not be trusted for the expansion prepare() kept: here a
+  // dense bf16 layer C is prepared over the same bytes, then A runs with the null pointer its prepare() returned.
+  {
+    ws.clear();
+    runner.prepare(w, ws);  // A's int8 expansion at the front of the arena
+    ws.clear();
+    std::vector<float> cw(size_t(out) * k, 3.0f);  // C: an fp32 weight whose bf16 form (0x4040...) overwrites A's codes
+    QuantWeight c;
+    c.format = QuantFormat::kF32;
+    c.in_features = k;
+    c.out_features = out;
+    c.data = upload(cw);
+    ws.reserve(linear_workspace_bytes(c, rows, ComputeType::kBF16) + linear_workspace_bytes(w, rows, ComputeType::kBF16));
+    ws.clear();
+    runner.prepare(w, ws);
+    ws.clear();
+    if (runner.prepare(c, ws) == nullptr) return 6;
+    cudaMemset(dy2, 0, rows * out * 2);
+    runner.forward_prepared(w, nullptr, dx, rows, dy2, ws);
+    if (cudaDeviceSynchronize() != cudaSuccess) return 7;
+    cudaMemcpy(y2.data(), dy2, y2.size() * 2, cudaMemcpyDeviceToHost);
+    if (y != y2) return 8;
+    ws.clear();
+  }
+
+  // One process driving two GPUs: the same Linear on device 1 after device 0 (kernel attributes such as the dynamic
+  // shared-memory limit are per device). Skipped on a single-GPU machine.
+  int devices = 0;
+  cudaGetDeviceCount(&devices);
+  if (devices >= 2) {
+    if (cudaSetDevice(1) != cudaSuccess) return 9;
+    QuantWeight w1 = w;
+    w1.data = upload(packed);
+    w1.block_scale = upload(scales);
+    w1.weight_scale = upload(channel);
+    w1.w4_codebook = upload(book);
+    auto* dx1 = reinterpret_cast<__nv_bfloat16*>(upload(x));
+    __nv_bfloat16* dy1 = nullptr;
+    cudaMalloc(&dy1, rows * out * 2);
+    LinearRunner second;
+    second.init(nullptr, nullptr);
+    Workspace ws1;
+    ws1.reserve(linear_workspace_bytes(w1, rows, ComputeType::kBF16));
+    second.forward(w1, dx1, rows, dy1, ws1);
+    if (cudaDeviceSynchronize() != cudaSuccess) return 10;
+    cudaMemcpy(y2.data(), dy1, y2.size() * 2, cudaMemcpyDeviceToHost);
+    if (y != y2) return 11;
+    cudaSetDevice(0);
+  }
   for (uint16_t v : y) printf("%u ", unsigned(v));
   printf("\n");
   return 0;

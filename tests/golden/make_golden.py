@@ -4,7 +4,7 @@ Run in a container that has the reference tree:  make -C oracle ref  &&
 python tests/golden/make_golden.py.  Every array is produced by a function of
 oracle/_ref/libslopfab_ref.so, i.e. by the reference's unmodified fixtures
 (tests/detail/nn_weight_fixture.h, tests/detail/nn_kernels_fixture.h,
-tests/harness.cpp, include/slopfab/dtype.h, src/core/int8_weight.cpp); nothing
+tests/harness.cpp, include/slopfab/dtype.h, src/core/int8_weight.cpp, src/dit/packing.cpp); nothing
 here comes from the oracle or from the product. The oracle is then pinned to
 these vectors by tests/test_oracle_golden.py wherever the reference tree is
 not available.
@@ -130,6 +130,39 @@ for g in (1, 4, 16, 64, 256):
 h = np.empty(256 * 256, np.float32)
 ref.ref_kron_h4_256(P(h))
 out["kron_h4_256"] = h.reshape(256, 256).astype(np.int8)
+
+# token packing: build_indices and both forms of build_row_timesteps (src/dit/packing.cpp) on a set of layouts, with
+# the layout's own tags and with padding rows (-1) written over some of them
+ref.ref_build_indices.argtypes = [C.c_void_p] * 5
+ref.ref_build_row_timesteps.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.POINTER(C.c_int)]
+PACK_LAYOUTS = [(4, 0, 0, 0, 500, 2000), (3, 0, 0, 0, 10, 7), (5, 6, 0, 0, 12, 9), (2, 4, 3, 1, 8, 5), (0, 0, 0, 0, 0, 11),
+                (1, 0, 0, 0, 6, 0), (2, 9, 0, 0, 4, 3), (7, 5, 4, 1, 3, 20), (6, 2, 0, 1, 9, 4)]
+PACK_TIMES = [(0.25, 0.75, 0.0, 1.0), (0.75, 0.25, 1.0, 0.0), (0.5, 0.5, 0.5, 0.5), (0.9, 0.1, 0.9, 0.3), (0.3, 0.6, 0.6, 0.3)]
+out["packing_layouts"] = np.array(PACK_LAYOUTS, np.int32)
+out["packing_times"] = np.array(PACK_TIMES, np.float32)
+prng = np.random.default_rng(416)
+for li, lay in enumerate(PACK_LAYOUTS):
+    L, Cv, Ca, ex, Sa, V = lay
+    total = L + Cv + Ca + Sa + V
+    l6 = np.array(lay, np.int32)
+    text, audio, video, tags = (np.zeros(n, np.int32) for n in (L, Sa, Cv + Ca + V, total))
+    assert ref.ref_build_indices(P(l6), P(text), P(audio), P(video), P(tags)) == 0
+    out[f"packing_{li}_text"], out[f"packing_{li}_audio"], out[f"packing_{li}_video"], out[f"packing_{li}_tags"] = text, audio, video, tags
+    padded = tags.copy()
+    padded[prng.random(total) < 0.2] = -1
+    out[f"packing_{li}_padded_tags"] = padded
+    for ti, tt in enumerate(PACK_TIMES):
+        for count in (2, 4):
+            for pad, use in (("own", None), ("pad", padded)):
+                idx, ada = np.zeros(total, np.int32), np.zeros(total, np.int32)
+                uniq = np.zeros(4, np.float32)
+                n = C.c_int(0)
+                t4 = np.array(tt, np.float32)
+                assert ref.ref_build_row_timesteps(P(l6), None if use is None else P(use), P(t4), count, P(idx), P(ada), P(uniq),
+                                                   C.byref(n)) == 0
+                key = f"packing_{li}_{ti}_{count}_{pad}"
+                out[key + "_indices"], out[key + "_adaln"], out[key + "_unique"] = idx, ada, uniq[:n.value].copy()
 
 np.savez_compressed(os.path.join(ROOT, "tests", "golden", "golden.npz"), **out)
 print("wrote", len(out), "arrays")

@@ -171,6 +171,41 @@ def test_adaln_index_known_answers():
             assert np.array_equal(ada, want_i * 3 + want_tag)
 
 
+def test_token_packing_matches_the_reference_packing_code(golden):
+    """build_indices and both forms of build_row_timesteps against vectors written by the reference's own
+    src/dit/packing.cpp (tests/golden/make_golden.py), padding tags (-1) and the four-timestep form included."""
+    layouts, times = golden["packing_layouts"], golden["packing_times"]
+    for li, lay in enumerate(layouts):
+        L, Cv, Ca, ex, Sa, V = (int(v) for v in lay)
+        total = L + Cv + Ca + Sa + V
+        layout = sfq.SequenceLayout(L, Cv, Ca, ex, Sa, V)
+        text, audio, video, tags = (np.full(n, -7, np.int32) for n in (L, Sa, Cv + Ca + V, total))
+        sfq.check(sfq.lib.sfq_build_indices(C.byref(layout), P(text), P(audio), P(video), P(tags)))
+        for name, got in (("text", text), ("audio", audio), ("video", video), ("tags", tags)):
+            assert np.array_equal(got, golden[f"packing_{li}_{name}"]), (li, name)
+        padded = np.ascontiguousarray(golden[f"packing_{li}_padded_tags"])
+        for ti, tt in enumerate(times):
+            for count in (2, 4):
+                for pad, use in (("own", None), ("pad", padded)):
+                    idx, ada = np.full(total, -7, np.int32), np.full(total, -7, np.int32)
+                    uniq = np.zeros(4, np.float32)
+                    n = C.c_int(0)
+                    tp = None if use is None else P(use)
+                    if count == 2:
+                        sfq.check(sfq.lib.sfq_build_row_timesteps(C.byref(layout), tp, tt[0], tt[1], P(idx), P(ada), P(uniq), 4,
+                                                                  C.byref(n)))
+                    else:
+                        sfq.check(sfq.lib.sfq_build_row_timesteps4(C.byref(layout), tp, tt[0], tt[1], tt[2], tt[3], P(idx), P(ada),
+                                                                   P(uniq), 4, C.byref(n)))
+                    key = f"packing_{li}_{ti}_{count}_{pad}"
+                    assert np.array_equal(idx, golden[key + "_indices"]), key
+                    assert np.array_equal(ada, golden[key + "_adaln"]), key
+                    assert np.array_equal(uniq[:n.value], golden[key + "_unique"]), key
+                    assert ada.min(initial=0) >= 0  # padding rows never index backwards into the table
+    bad = sfq.SequenceLayout(-1, 0, 0, 0, 0, 0)
+    assert sfq.lib.sfq_build_indices(C.byref(bad), None, None, None, None) == sfq.ERR_INVALID_ARGUMENT
+
+
 def test_weight_row_block_views_follow_build_block():
     # build_block (src/dit/transformer_load.cpp:660-737): q/k/v are views over one [3 * inner, hidden] upload, and every
     # row-indexed array moves with the view. Pointers are opaque here: use small integers as "addresses".

@@ -36,7 +36,7 @@ def test_gemm_int8_bit_exact(M, N, K, tile_n):
     bias = (0.01 * rng.standard_normal(N)).astype(np.float32)
     da, dw, drs, dcs, db = dev(a), dev(w), dev(rs), dev(cs), dev(bias)
     acc = oracle.int8_gemm(a, w)
-    sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
+    sfq.lib.sfq_test_gemm_variant(tile_n, 0, 0)
     try:
         for use_bias, act in ((False, sfq.ACT_NONE), (True, sfq.ACT_NONE), (True, sfq.ACT_GELU_TANH)):
             y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -56,7 +56,7 @@ def test_gemm_int8_bit_exact(M, N, K, tile_n):
                 bad = int((got != want).sum())
                 assert bad == 0, f"{bad} of {M * N} outputs differ (bias={use_bias}); first at {np.argwhere(got != want)[:4]}"
     finally:
-        sfq.lib.sfq_gemm_tuning(0, 0, 0)
+        sfq.lib.sfq_test_gemm_variant(0, 0, 0)
 
 
 def test_gemm_int8_multi_tile_persistence():
@@ -118,11 +118,11 @@ def _run_nvfp4(x, data, scale, g, M, N, K, bias=None, act=sfq.ACT_NONE):
 def test_gemm_nvfp4_matches_fp4_activation_oracle(M, N, K, tile_n):
     # shapes of nvfp4_gemm_matches_cpu_reference (tests/test_nn_kernels_nvfp4_synthetic.cu:455-480) plus config 1
     x, data, scale, g = _nvfp4_case(M, N, K, seed=M + N + K)
-    sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
+    sfq.lib.sfq_test_gemm_variant(tile_n, 0, 0)
     try:
         y = _run_nvfp4(x, data, scale, g, M, N, K)
     finally:
-        sfq.lib.sfq_gemm_tuning(0, 0, 0)
+        sfq.lib.sfq_test_gemm_variant(0, 0, 0)
     want = oracle.nvfp4_linear(x, data, scale, g, N, K)
     max_abs, rel_l2, corr = oracle.compare_bf16(want, bits(y))
     assert max_abs <= 2e-2 and rel_l2 <= 1e-3 and corr > 0.999, (max_abs, rel_l2, corr)
@@ -146,7 +146,7 @@ def test_gemm_gated_residual_epilogue(M, N, K, tile_n):
     idx = rng.integers(0, 5, size=M).astype(np.int32)
     x = gaussian_bf16((M, N), seed=M)
     da, dw, drs, dcs, db, dg, di = dev(a), dev(w), dev(rs), dev(cs), dev(bias), dev(gate), dev(idx)
-    sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
+    sfq.lib.sfq_test_gemm_variant(tile_n, 0, 0)
     try:
         branch = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
         ep = sfq.Epilogue(sfq.ptr(drs), sfq.ptr(dcs), 1.0, sfq.ptr(db), sfq.F32, sfq.ACT_NONE)
@@ -156,7 +156,7 @@ def test_gemm_gated_residual_epilogue(M, N, K, tile_n):
         sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(da), sfq.ptr(dw), C.byref(ep2), sfq.ptr(y), M, N, K, S))
         _status_clean()
     finally:
-        sfq.lib.sfq_gemm_tuning(0, 0, 0)
+        sfq.lib.sfq_test_gemm_variant(0, 0, 0)
     want = x.copy()
     bb = bits(branch)
     oracle.lib.orc_add_gated_bf16(P(want), P(bb), P(gate), P(idx), M, N)

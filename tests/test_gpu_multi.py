@@ -102,7 +102,17 @@ def test_column_split_and_token_sharding_on_two_gpus():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.join(timeout=300)
+    finally:
+        # a worker that is still alive holds its GPU and its communicator: end it before the verdict
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join()
+    assert [p.exitcode for p in procs] == [0, 0]
     assert out.get(timeout=5) is True

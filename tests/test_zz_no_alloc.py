@@ -38,6 +38,8 @@ def test_static_scratch_linear_matches_runner_twice_in_a_row():
                                                           sfq.ptr(got), N, K, sfq.stream_ptr()))
         torch.cuda.synchronize()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (M, N, K)
+        # the kernels of the static entry point report abandoned waits in the array's own word
+        assert sfq.static_status() == 0
     assert sfq.device_status() == 0
 
 
