@@ -191,6 +191,11 @@ SFQ_API int sfq_unpack_nf4_bf16(const uint8_t* d_packed, const uint8_t* d_absmax
                                 const float* d_nested_quant_map, const float* d_nested_absmax, int block_size,
                                 int nested_block_size, float nested_offset, void* d_out_bf16, int out_features,
                                 int in_features, void* stream);
+/* launch_dequant_nf4_f16, include/slopfab/cuda/linear.cuh:298-301: the same decode into fp16 over a flat element
+ * count (bit-exact). */
+SFQ_API int sfq_unpack_nf4_f16(const uint8_t* d_packed, const uint8_t* d_absmax, const float* d_quant_map,
+                               const float* d_nested_quant_map, const float* d_nested_absmax, int block_size,
+                               int nested_block_size, float nested_offset, void* d_out_f16, size_t n, void* stream);
 /* launch_pre_quant_scale, include/slopfab/cuda/linear.cuh:305-306: the AWQ activation pre-scale
  * dst[r, i] = bf16(src[r, i] * scale[i]) (bit-exact). */
 SFQ_API int sfq_pre_quant_scale(const void* d_src_bf16, const void* d_scale_bf16, void* d_dst_bf16, int rows, int dim,
@@ -206,6 +211,18 @@ SFQ_API int sfq_unpack_int8_f16(const int8_t* d_codes, const float* d_scale, voi
 SFQ_API int sfq_rmsnorm(const void* d_x_bf16, const sfq_norm* norm, void* d_out_bf16, int rows, int dim, void* stream);
 /* launch_convrot, include/slopfab/cuda/linear.cuh:251-252 (bit-exact). */
 SFQ_API int sfq_convrot(const void* d_x_bf16, void* d_out_bf16, int rows, int dim, int group, void* stream);
+
+/* launch_convrot_f32, include/slopfab/cuda/linear.cuh:253-254: the same rotation over fp32 rows (bit-exact). */
+SFQ_API int sfq_convrot_f32(const float* d_x, float* d_out, int rows, int dim, int group, void* stream);
+/* launch_w4a8_output_bf16 and launch_dequant_w4a8_output, include/slopfab/cuda/w4a8.cuh:30-36: an int32 accumulator
+ * [rows, cols] scaled by row and channel scales into bf16, or into fp32 over the accumulator itself (bit-exact). The
+ * runner never uses them: sfq_gemm_int8 applies the same arithmetic in its epilogue. */
+SFQ_API int sfq_int8_output_bf16(const int32_t* d_acc, const float* d_row_scale, const float* d_channel_scale,
+                                 void* d_y_bf16, int rows, int cols, void* stream);
+SFQ_API int sfq_int8_output_f32(int32_t* d_acc_inout, const float* d_row_scale, const float* d_channel_scale, int rows,
+                                int cols, void* stream);
+/* launch_quantize_f8e4m3, include/slopfab/cuda/linear.cuh:308-310: e4m3(x / input_scale), saturating (bit-exact). */
+SFQ_API int sfq_quantize_f8e4m3(const void* d_x_bf16, float input_scale, uint8_t* d_out, size_t n, void* stream);
 
 /* One pass: [RMSNorm / modulate] -> ConvRot-256 -> per-token int8. Replaces
  * launch_rmsnorm_modulate + launch_convrot + launch_quantize_w4a8_bf16
@@ -241,6 +258,14 @@ SFQ_API int sfq_gemm_int8(const int8_t* d_q, const int8_t* d_w8, const sfq_epilo
 SFQ_API int sfq_gemm_nvfp4(const uint8_t* d_a_packed, const uint8_t* d_a_scale_tiled, const uint8_t* d_w_packed,
                            const uint8_t* d_w_scale_tiled, const sfq_epilogue* ep, void* d_y_bf16,
                            int M, int N, int K, void* stream);
+/* nvfp4_gemm_forward_q with its own operand convention (include/slopfab/cuda/nvfp4_gemm.cuh:101-113): activations as
+ * launch_quantize_nvfp4_activations / sfq_quantize_nvfp4_block(REFERENCE) wrote them (low nibble = even element, scales
+ * row-major), no bias, no activation. They are converted into the GEMM_FEED layout in stream-ordered scratch that the
+ * call allocates and frees on `stream` (the reference signature has no workspace); sfq_gemm_nvfp4 is the form without
+ * that conversion. Refused like the reference when the device or the shape has no native path. */
+SFQ_API int sfq_gemm_nvfp4_reference_layout(const uint8_t* d_xq, const uint8_t* d_xs, const uint8_t* d_w_packed,
+                                            const uint8_t* d_w_scale_tiled, float global_scale, void* d_y_bf16, int rows,
+                                            int out_features, int in_features, void* stream);
 /* y = epilogue(x[M,K] * w[N,K]^T), bf16 operands, fp32 accumulate: the cuBLAS bf16 GemmEx of
  * src/cuda/linear.cu:243-246. K % 8 == 0. */
 SFQ_API int sfq_gemm_bf16(const void* d_x_bf16, const void* d_w_bf16, const sfq_epilogue* ep, void* d_y_bf16,
@@ -378,7 +403,8 @@ SFQ_API int sfq_build_adaln_index(int num_text, int num_condition_video, int num
 /* LinearRunner::forward_f32 (include/slopfab/cuda/linear.cuh:229-232, src/cuda/linear.cu:251-285): fp32 activations
  * and fp32 output; the weight as stored when fp32, else its dense bf16 form; fp32 accumulation on CUDA cores; the
  * bias added to the finished sum. The DiT uses this arm for the few timestep rows of the adaLN tables
- * (src/dit/transformer_execution.cpp:55,63). W4A8/W6A8, AWQ pre-scale and ConvRot weights are refused. */
+ * (src/dit/transformer_execution.cpp:55,63). AWQ pre-scale and ConvRot are applied to the fp32 activation first, as in
+ * the reference; W4A8/W6A8 weights are refused (they need bf16 activations). */
 SFQ_API int sfq_linear_forward_f32(sfq_runner* r, const sfq_quant_weight* w, const float* d_x_f32, int rows, float* d_y_f32,
                                    void* d_workspace, size_t workspace_bytes);
 

@@ -211,6 +211,35 @@ bool nvfp4_gemm_shape_supported(int out_features, int in_features) noexcept;
 size_t nvfp4_gemm_workspace_bytes(int rows, int in_features);
 void launch_quantize_nvfp4_activations(const __nv_bfloat16* x, uint8_t* packed, uint8_t* scales, int rows, int dim,
                                        cudaStream_t stream);
+// nvfp4_gemm_forward / _prevalidated / _q (include/slopfab/cuda/nvfp4_gemm.cuh:89-113): y = x W^T * global_scale with fp4
+// activations, no bias. The first two quantize x into `ws` (straight into the layout the tcgen05 GEMM reads) and throw
+// like the reference when the device or the shape has no native path (`_prevalidated` skips that test). `_q` takes
+// activations the caller quantized with launch_quantize_nvfp4_activations, i.e. in the REFERENCE's layout; it converts
+// them (nibbles exchanged, scales tiled) into stream-ordered scratch it allocates and frees on `stream`, because the
+// reference signature carries no workspace. A caller that shares one quantization between several GEMMs and cares
+// about that allocation uses sfq_quantize_nvfp4_block(GEMM_FEED) + sfq_gemm_nvfp4 instead.
+void nvfp4_gemm_forward(const __nv_bfloat16* x, const uint8_t* w_packed, const uint8_t* w_scale, float global_scale,
+                        __nv_bfloat16* y, int rows, int out_features, int in_features, Workspace& ws, cudaStream_t stream);
+void nvfp4_gemm_forward_prevalidated(const __nv_bfloat16* x, const uint8_t* w_packed, const uint8_t* w_scale,
+                                     float global_scale, __nv_bfloat16* y, int rows, int out_features, int in_features,
+                                     Workspace& ws, cudaStream_t stream);
+void nvfp4_gemm_forward_q(const uint8_t* xq, const uint8_t* xs, const uint8_t* w_packed, const uint8_t* w_scale,
+                          float global_scale, __nv_bfloat16* y, int rows, int out_features, int in_features,
+                          cudaStream_t stream);
+// include/slopfab/cuda/w4a8.cuh:30-36: the int32 accumulator of an int8 GEMM scaled to bf16, or to fp32 in place. (The
+// runner never materialises that accumulator: its GEMM epilogue applies the same arithmetic.)
+void launch_w4a8_output_bf16(const int32_t* input, const float* row_scale, const float* channel_scale, __nv_bfloat16* output,
+                             int rows, int cols, cudaStream_t stream);
+void launch_dequant_w4a8_output(int32_t* input_output, const float* activation_scale, const float* weight_scale, int rows,
+                                int cols, cudaStream_t stream);
+// include/slopfab/cuda/linear.cuh:253-313.
+void launch_convrot_f32(const float* in, float* out, int rows, int dim, int group, cudaStream_t stream);
+void launch_dequant_nf4_f16(const uint8_t* src, const uint8_t* absmax, const float* quant_map, const float* nested_quant_map,
+                            const float* nested_absmax, int block_size, int nested_block_size, float nested_offset,
+                            __half* dst, size_t n, cudaStream_t stream);
+void launch_quantize_f8e4m3(const __nv_bfloat16* src, float input_scale, uint8_t* dst, size_t n, cudaStream_t stream);
+void launch_widen_bf16(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t stream);
+void launch_narrow_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
 void launch_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out, int rows, int dim, float eps,
                     cudaStream_t stream);
 void launch_rmsnorm_modulate(const __nv_bfloat16* x, const __nv_bfloat16* w, const float* scale, const float* shift,

@@ -520,3 +520,30 @@ REF_API int ref_build_row_timesteps(const int32_t* layout6, const int32_t* tags_
     *num_unique = int(rt.unique.size());
   });
 }
+
+// ---- the remaining small launchers of the linear headers
+REF_API int ref_dev_convrot_f32(const float* in, float* out, int rows, int dim, int group) {
+  return guarded([&] {
+    sc::launch_convrot_f32(in, out, rows, dim, group, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_quantize_f8(const void* x, float input_scale, uint8_t* out, size_t n) {
+  return guarded([&] {
+    sc::launch_quantize_f8e4m3(static_cast<const bf16*>(x), input_scale, out, n, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_dequant_nf4_f16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                                    const float* nested_absmax, int block, int nested_block, float offset, void* dst, size_t n) {
+  return guarded([&] {
+    sc::launch_dequant_nf4_f16(src, absmax, map, nested_map, nested_absmax, block, nested_block, offset, static_cast<__half*>(dst), n, nullptr);
+    sync();
+  });
+}
+REF_API int ref_dev_output_f32(int32_t* io, const float* rows_s, const float* chan_s, int rows, int cols) {
+  return guarded([&] {
+    sc::launch_dequant_w4a8_output(io, rows_s, chan_s, rows, cols, nullptr);
+    sync();
+  });
+}

@@ -237,6 +237,36 @@ int sfq_convrot(const void* d_x_bf16, void* d_out_bf16, int rows, int dim, int g
     sfq::convrot(static_cast<const bf16*>(d_x_bf16), static_cast<bf16*>(d_out_bf16), rows, dim, group, as_stream(stream));
   });
 }
+int sfq_convrot_f32(const float* d_x, float* d_out, int rows, int dim, int group, void* stream) {
+  return guarded([&] { sc::launch_convrot_f32(d_x, d_out, rows, dim, group, as_stream(stream)); });
+}
+int sfq_int8_output_bf16(const int32_t* d_acc, const float* d_row_scale, const float* d_channel_scale, void* d_y_bf16, int rows, int cols,
+                         void* stream) {
+  return guarded([&] {
+    sc::launch_w4a8_output_bf16(d_acc, d_row_scale, d_channel_scale, static_cast<bf16*>(d_y_bf16), rows, cols, as_stream(stream));
+  });
+}
+int sfq_int8_output_f32(int32_t* d_acc_inout, const float* d_row_scale, const float* d_channel_scale, int rows, int cols, void* stream) {
+  return guarded([&] { sc::launch_dequant_w4a8_output(d_acc_inout, d_row_scale, d_channel_scale, rows, cols, as_stream(stream)); });
+}
+int sfq_quantize_f8e4m3(const void* d_x_bf16, float input_scale, uint8_t* d_out, size_t n, void* stream) {
+  return guarded([&] { sc::launch_quantize_f8e4m3(static_cast<const bf16*>(d_x_bf16), input_scale, d_out, n, as_stream(stream)); });
+}
+int sfq_unpack_nf4_f16(const uint8_t* d_packed, const uint8_t* d_absmax, const float* d_quant_map, const float* d_nested_quant_map,
+                       const float* d_nested_absmax, int block_size, int nested_block_size, float nested_offset, void* d_out_f16, size_t n,
+                       void* stream) {
+  return guarded([&] {
+    sc::launch_dequant_nf4_f16(d_packed, d_absmax, d_quant_map, d_nested_quant_map, d_nested_absmax, block_size, nested_block_size,
+                               nested_offset, static_cast<__half*>(d_out_f16), n, as_stream(stream));
+  });
+}
+int sfq_gemm_nvfp4_reference_layout(const uint8_t* d_xq, const uint8_t* d_xs, const uint8_t* d_w_packed, const uint8_t* d_w_scale_tiled,
+                                    float global_scale, void* d_y_bf16, int rows, int out_features, int in_features, void* stream) {
+  return guarded([&] {
+    sc::nvfp4_gemm_forward_q(d_xq, d_xs, d_w_packed, d_w_scale_tiled, global_scale, static_cast<bf16*>(d_y_bf16), rows, out_features,
+                             in_features, as_stream(stream));
+  });
+}
 int sfq_quantize_int8_token(const void* d_x_bf16, const sfq_norm* norm, int8_t* d_q, float* d_row_scale,
                             void* d_normed_out_bf16, int rows, int dim, int apply_convrot, void* stream) {
   return guarded([&] {

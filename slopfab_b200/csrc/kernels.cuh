@@ -30,6 +30,9 @@ void unpack_f8e4m3_bf16(const uint8_t* src, const float* scale, __nv_bfloat16* d
 void unpack_nf4_bf16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
                      const float* nested_absmax, int block, int nested_block, float offset, __nv_bfloat16* dst,
                      int out_features, int in_features, cudaStream_t stream);
+void unpack_nf4_f16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                    const float* nested_absmax, int block, int nested_block, float offset, __half* dst, size_t n,
+                    cudaStream_t stream);
 void convert_f16_bf16(const __half* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
 void convert_f32_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
 
@@ -54,6 +57,18 @@ void gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream);
 void swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int inner, cudaStream_t stream);
 void pre_quant_scale(const __nv_bfloat16* src, const __nv_bfloat16* scale, __nv_bfloat16* dst, int rows, int dim,
                      cudaStream_t stream);
+// The reference's remaining linear-header launchers (thin kernels, off the runner's own path).
+void convrot_f32(const float* in, float* out, int rows, int dim, int group, cudaStream_t stream);
+void pre_quant_scale_f32(const float* src, const __nv_bfloat16* scale, float* dst, int rows, int dim, cudaStream_t stream);
+void int8_output_bf16(const int32_t* acc, const float* row_scale, const float* channel_scale, __nv_bfloat16* out, int rows, int cols,
+                      cudaStream_t stream);
+void int8_output_f32_inplace(int32_t* io, const float* row_scale, const float* channel_scale, int rows, int cols, cudaStream_t stream);
+void quantize_f8e4m3(const __nv_bfloat16* src, float input_scale, uint8_t* dst, size_t n, cudaStream_t stream);
+void widen_bf16(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t stream);
+void narrow_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
+// fp4 activations from the reference's layout into the GEMM_FEED layout (nibbles exchanged, scales tiled and padded).
+void nvfp4_act_to_feed(const uint8_t* xq, const uint8_t* xs, uint8_t* feed_q, uint8_t* feed_scale_tiled, int rows, int dim,
+                       cudaStream_t stream);
 // quant_int8_pairs.cu: ConvRot-256 + per-token int8 without a norm in front; false when the shape is not covered.
 bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, cudaStream_t stream);
 void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate, const int32_t* index, int rows,

@@ -177,9 +177,11 @@ size_t linear_activation_workspace_bytes(const QuantWeight& w, int rows, Compute
     return align_up(r * w.in_features) + align_up(r * 4);
   }
   if (compute != ComputeType::kBF16) {
-    if (w.pre_quant_scale != nullptr || convrot_applies(w))
-      throw std::runtime_error("linear: AWQ pre-scale and ConvRot are not built for fp32 activations");
-    return 0;  // forward_f32 reads x and writes y directly
+    // forward_f32 reads x and writes y directly; the two optional fp32 front stages each take a copy of the activation
+    size_t f32 = 0;
+    if (w.pre_quant_scale != nullptr) f32 += align_up(r * w.in_features * sizeof(float));
+    if (convrot_applies(w)) f32 += align_up(r * w.in_features * sizeof(float));
+    return f32;
   }
   size_t total = 0;
   if (w.pre_quant_scale != nullptr) total += align_up(r * w.in_features * sizeof(__nv_bfloat16));
@@ -396,34 +398,42 @@ void LinearRunner::run_packed_int8(const QuantWeight& w, const int8_t* codes, co
 }
 
 // fp32 activations in, fp32 out (src/cuda/linear.cu:251-285): the weight is used as stored when it is fp32 and in
-// its dense bf16 form otherwise (the reference widens that copy to fp32 first; the values are the same), the product
-// runs on CUDA cores with fp32 accumulation, the bias is added to the finished sum. The reference's two optional
-// front stages in fp32 (AWQ pre-scale, ConvRot) are not built: such a weight is refused.
+// its dense bf16 form otherwise (the reference widens that copy to fp32 first; the values are the same), the
+// activation first takes the AWQ pre-scale and the ConvRot rotation in fp32 when the weight asks for them, the product
+// runs on CUDA cores with fp32 accumulation, the bias is added to the finished sum.
 void LinearRunner::forward_f32(const QuantWeight& w, const float* x, int rows, float* y, Workspace& ws) {
   if (!initialised_) throw std::runtime_error("LinearRunner::forward_f32: init() not called");
   if (rows <= 0) return;
   if (is_packed_int8(w.format)) throw std::invalid_argument("W4A8/W6A8 requires BF16 activations");
-  if (w.pre_quant_scale != nullptr || convrot_applies(w))
-    throw std::runtime_error("LinearRunner::forward_f32: AWQ pre-scale and ConvRot are not built for fp32 activations");
   Workspace::Scope scope(ws);
   const bool bias_bf16 = w.bias != nullptr && w.bias_format == QuantFormat::kBF16;
   if (w.bias != nullptr && w.bias_format != QuantFormat::kF32 && w.bias_format != QuantFormat::kBF16)
     throw std::runtime_error("linear: bias must be F32 or BF16");
-  if (w.format == QuantFormat::kF32) {
-    sfq::linear_f32(x, w.data, false, w.bias, bias_bf16, y, rows, w.out_features, w.in_features, stream_);
-    return;
-  }
-  const bool was_native = native_;
-  native_ = false;  // the dense form, whatever the runner's NVFP4 switch says
-  const __nv_bfloat16* dense = nullptr;
-  try {
-    dense = prepare(w, ws);
-  } catch (...) {
+  const void* weight = w.data;
+  const bool weight_bf16 = w.format != QuantFormat::kF32;
+  if (weight_bf16) {
+    const bool was_native = native_;
+    native_ = false;  // the dense form, whatever the runner's NVFP4 switch says
+    try {
+      weight = prepare(w, ws);
+    } catch (...) {
+      native_ = was_native;
+      throw;
+    }
     native_ = was_native;
-    throw;
   }
-  native_ = was_native;
-  sfq::linear_f32(x, dense, true, w.bias, bias_bf16, y, rows, w.out_features, w.in_features, stream_);
+  const float* xin = x;
+  if (w.pre_quant_scale != nullptr) {
+    float* xs = ws.alloc_n<float>(size_t(rows) * w.in_features);
+    sfq::pre_quant_scale_f32(xin, w.pre_quant_scale, xs, rows, w.in_features, stream_);
+    xin = xs;
+  }
+  if (convrot_applies(w)) {
+    float* xr = ws.alloc_n<float>(size_t(rows) * w.in_features);
+    sfq::convrot_f32(xin, xr, rows, w.in_features, w.convrot_group, stream_);
+    xin = xr;
+  }
+  sfq::linear_f32(xin, weight, weight_bf16, w.bias, bias_bf16, y, rows, w.out_features, w.in_features, stream_);
 }
 
 // ---- free launchers ------------------------------------------------------------------------
@@ -507,5 +517,92 @@ void launch_swiglu(const __nv_bfloat16* fused, __nv_bfloat16* out, int rows, int
   sfq::swiglu(fused, out, rows, inner, stream);
 }
 void launch_gelu_tanh(__nv_bfloat16* x, size_t n, cudaStream_t stream) { sfq::gelu_tanh(x, n, stream); }
+
+namespace {
+void nvfp4_gemm_feed(const uint8_t* xq, const uint8_t* xs_tiled, const uint8_t* w_packed, const uint8_t* w_scale, float global_scale,
+                     __nv_bfloat16* y, int rows, int out_features, int in_features, cudaStream_t stream) {
+  sfq::GemmArgs g;
+  g.M = rows;
+  g.N = out_features;
+  g.K = in_features;
+  g.y = y;
+  g.ldy = out_features;
+  g.global_scale = global_scale;
+  g.a_scale_tiled = xs_tiled;
+  g.w_scale_tiled = w_scale;
+  g.status = sfq::device_status_word();
+  sfq::gemm_nvfp4(xq, w_packed, g, stream);
+}
+void require_native_nvfp4(int out_features, int in_features) {  // the refusal of src/cuda/nvfp4_gemm.cu:536-547, device test moved to sm_100
+  if (!nvfp4_gemm_supported(out_features, in_features))
+    throw std::runtime_error("nvfp4_gemm: native NVFP4 requires a Blackwell (sm_100) GPU and " + std::to_string(out_features) + "x" +
+                             std::to_string(in_features) + " needs out % 128 == 0 and in % 64 == 0; the padded block-scale "
+                             "layout has never been observed and is not guessed at");
+}
+}  // namespace
+
+void nvfp4_gemm_forward_prevalidated(const __nv_bfloat16* x, const uint8_t* w_packed, const uint8_t* w_scale, float global_scale,
+                                     __nv_bfloat16* y, int rows, int out_features, int in_features, Workspace& ws, cudaStream_t stream) {
+  if (rows <= 0 || out_features <= 0) return;
+  Workspace::Scope scope(ws);
+  uint8_t* xq = ws.alloc_n<uint8_t>(size_t(rows) * (in_features / 2));
+  uint8_t* xs = ws.alloc_n<uint8_t>(sfq::nvfp4_act_scale_bytes(rows, in_features));
+  sfq::quantize_nvfp4_block(x, sfq::NormArgs{}, xq, xs, nullptr, rows, in_features, SFQ_NVFP4_ACT_GEMM_FEED, stream);
+  nvfp4_gemm_feed(xq, xs, w_packed, w_scale, global_scale, y, rows, out_features, in_features, stream);
+}
+
+void nvfp4_gemm_forward(const __nv_bfloat16* x, const uint8_t* w_packed, const uint8_t* w_scale, float global_scale, __nv_bfloat16* y,
+                        int rows, int out_features, int in_features, Workspace& ws, cudaStream_t stream) {
+  if (rows <= 0 || out_features <= 0) return;
+  require_native_nvfp4(out_features, in_features);
+  nvfp4_gemm_forward_prevalidated(x, w_packed, w_scale, global_scale, y, rows, out_features, in_features, ws, stream);
+}
+
+void nvfp4_gemm_forward_q(const uint8_t* xq, const uint8_t* xs, const uint8_t* w_packed, const uint8_t* w_scale, float global_scale,
+                          __nv_bfloat16* y, int rows, int out_features, int in_features, cudaStream_t stream) {
+  if (rows <= 0 || out_features <= 0) return;
+  require_native_nvfp4(out_features, in_features);
+  const size_t q_bytes = align_up(size_t(rows) * (in_features / 2));
+  const size_t s_bytes = sfq::nvfp4_act_scale_bytes(rows, in_features);
+  void* scratch = nullptr;
+  cudaError_t e = cudaMallocAsync(&scratch, q_bytes + s_bytes, stream);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("nvfp4_gemm_forward_q: scratch allocation failed: ") + cudaGetErrorString(e));
+  uint8_t* fq = static_cast<uint8_t*>(scratch);
+  uint8_t* fs = fq + q_bytes;
+  try {
+    sfq::nvfp4_act_to_feed(xq, xs, fq, fs, rows, in_features, stream);
+    nvfp4_gemm_feed(fq, fs, w_packed, w_scale, global_scale, y, rows, out_features, in_features, stream);
+  } catch (...) {
+    cudaFreeAsync(scratch, stream);
+    throw;
+  }
+  e = cudaFreeAsync(scratch, stream);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("nvfp4_gemm_forward_q: ") + cudaGetErrorString(e));
+}
+
+void launch_w4a8_output_bf16(const int32_t* input, const float* row_scale, const float* channel_scale, __nv_bfloat16* output, int rows,
+                             int cols, cudaStream_t stream) {
+  sfq::int8_output_bf16(input, row_scale, channel_scale, output, rows, cols, stream);
+}
+void launch_dequant_w4a8_output(int32_t* input_output, const float* activation_scale, const float* weight_scale, int rows, int cols,
+                                cudaStream_t stream) {
+  sfq::int8_output_f32_inplace(input_output, activation_scale, weight_scale, rows, cols, stream);
+}
+void launch_convrot_f32(const float* in, float* out, int rows, int dim, int group, cudaStream_t stream) {
+  sfq::convrot_f32(in, out, rows, dim, group, stream);
+}
+void launch_dequant_nf4_f16(const uint8_t* src, const uint8_t* absmax, const float* quant_map, const float* nested_quant_map,
+                            const float* nested_absmax, int block_size, int nested_block_size, float nested_offset, __half* dst, size_t n,
+                            cudaStream_t stream) {
+  if (!src || !absmax || !quant_map || !nested_quant_map || !nested_absmax || !dst)
+    throw std::runtime_error("launch_dequant_nf4_f16: null pointer");
+  if (block_size <= 0 || nested_block_size <= 0) throw std::runtime_error("launch_dequant_nf4_f16: invalid block sizes");
+  sfq::unpack_nf4_f16(src, absmax, quant_map, nested_quant_map, nested_absmax, block_size, nested_block_size, nested_offset, dst, n, stream);
+}
+void launch_quantize_f8e4m3(const __nv_bfloat16* src, float input_scale, uint8_t* dst, size_t n, cudaStream_t stream) {
+  sfq::quantize_f8e4m3(src, input_scale, dst, n, stream);
+}
+void launch_widen_bf16(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t stream) { sfq::widen_bf16(src, dst, n, stream); }
+void launch_narrow_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) { sfq::narrow_to_bf16(src, dst, n, stream); }
 
 }  // namespace slopfab::cuda

@@ -3,6 +3,8 @@
 // exist so that callers of the reference's launchers keep working unchanged.
 #include "kernels.cuh"
 
+#include <cuda_fp8.h>
+
 #include <stdexcept>
 #include <string>
 
@@ -115,6 +117,173 @@ void add_gated(__nv_bfloat16* x, const __nv_bfloat16* branch, const float* gate,
   else
     add_gated_kernel<<<dim3(rows, (dim + 255) / 256), 256, 0, stream>>>(x, branch, gate, index, dim);
   check_launch("add_gated");
+}
+
+// ---- small launchers of the reference's linear headers that the runner itself does not need -----------------
+namespace {
+// ConvRot over fp32 (convrot_kernel<float>, src/cuda/linear_weights.cu:422-471): H = kron^stages(h4) / sqrt(group) as
+// `stages` radix-4 butterfly passes at strides 1, 4, 16, ... over one group, each output a left-to-right sum of the
+// four inputs with the signs of the regular Hadamard h4, one multiplication by 1 / sqrt(group) at the end. One warp per
+// group, the group in shared memory, a butterfly read and written by the same lane.
+__global__ void __launch_bounds__(256) convrot_f32_kernel(const float* __restrict__ in, float* __restrict__ out, int group, int stages,
+                                                          float norm, size_t total_groups) {
+  extern __shared__ float rot_buf[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t g = size_t(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (g >= total_groups) return;  // whole warps leave; only __syncwarp below
+  float* buf = rot_buf + size_t(warp) * group;
+  const float* src = in + g * group;
+  for (int i = lane; i < group; i += 32) buf[i] = src[i];
+  __syncwarp();
+  int stride = 1;
+  for (int s = 0; s < stages; ++s, stride *= 4) {
+    for (int b = lane; b < group / 4; b += 32) {
+      const int i = (b / stride) * 4 * stride + (b % stride);
+      const float a = buf[i], bb = buf[i + stride], c = buf[i + 2 * stride], d = buf[i + 3 * stride];
+      buf[i] = __fsub_rn(__fadd_rn(__fadd_rn(a, bb), c), d);
+      buf[i + stride] = __fadd_rn(__fsub_rn(__fadd_rn(a, bb), c), d);
+      buf[i + 2 * stride] = __fadd_rn(__fadd_rn(__fsub_rn(a, bb), c), d);
+      buf[i + 3 * stride] = __fadd_rn(__fadd_rn(__fadd_rn(-a, bb), c), d);
+    }
+    __syncwarp();
+  }
+  float* dst = out + g * group;
+  for (int i = lane; i < group; i += 32) dst[i] = buf[i] * norm;
+}
+
+// dst[r, i] = src[r, i] * scale[i] in fp32 (pre_quant_scale_kernel<float>, src/cuda/linear_weights.cu:499-509).
+__global__ void pre_quant_scale_f32_kernel(const float* __restrict__ src, const __nv_bfloat16* __restrict__ scale, float* __restrict__ dst,
+                                           int dim) {
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  if (col >= dim) return;
+  const size_t i = size_t(blockIdx.x) * dim + col;
+  dst[i] = src[i] * __bfloat162float(scale[col]);
+}
+
+// bf16((float(acc) * row) * channel) (output_bf16, src/cuda/w4a8.cu:218-223), and the fp32 form written over the
+// accumulator itself (dequant_output_kernel, src/cuda/w4a8.cu:126-136).
+__global__ void int8_output_bf16_kernel(const int32_t* __restrict__ acc, const float* __restrict__ rows, const float* __restrict__ channels,
+                                        __nv_bfloat16* __restrict__ out, int cols) {
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  const size_t i = size_t(blockIdx.x) * cols + col;
+  out[i] = __float2bfloat16(__fmul_rn(__fmul_rn(float(acc[i]), rows[blockIdx.x]), channels[col]));
+}
+__global__ void int8_output_f32_kernel(int32_t* io, const float* __restrict__ rows, const float* __restrict__ channels, int cols) {
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  const size_t i = size_t(blockIdx.x) * cols + col;
+  const float v = __fmul_rn(__fmul_rn(float(io[i]), rows[blockIdx.x]), channels[col]);
+  reinterpret_cast<float*>(io)[i] = v;
+}
+
+// e4m3(bf16 * (1 / input_scale)), round to nearest even, saturating at 448 (quantize_f8_kernel,
+// src/cuda/linear_weights.cu:337-343 with the encoder of :41-68).
+__global__ void quantize_f8_kernel(const __nv_bfloat16* __restrict__ src, float inv_scale, uint8_t* __restrict__ dst, size_t n) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = uint8_t(__nv_cvt_float_to_fp8(__bfloat162float(src[i]) * inv_scale, __NV_SATFINITE, __NV_E4M3));
+}
+__global__ void widen_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, size_t n) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __bfloat162float(src[i]);
+}
+__global__ void narrow_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __float2bfloat16(src[i]);
+}
+
+// Quantized fp4 activations from the reference's layout (low nibble = even element, scales row-major [rows, dim/16];
+// launch_quantize_nvfp4_activations, include/slopfab/cuda/nvfp4_gemm.cuh:77-82) into the layout the tcgen05 GEMM
+// reads: nibbles of every byte exchanged, scales in 128-row x 4-block tiles of 512 bytes with the rows padded to a
+// multiple of 128 (pad rows zero). One thread per 16-element block of a padded row.
+__global__ void nvfp4_act_to_feed_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs, uint8_t* __restrict__ oq,
+                                         uint8_t* __restrict__ os, int rows, int blocks_per_row) {
+  const int kb = blockIdx.y * blockDim.x + threadIdx.x;
+  if (kb >= blocks_per_row) return;
+  const int r = blockIdx.x;
+  uint8_t scale = 0;
+  if (r < rows) {
+    const size_t b = size_t(r) * blocks_per_row + kb;
+    const uint64_t v = reinterpret_cast<const uint64_t*>(xq)[b];
+    reinterpret_cast<uint64_t*>(oq)[b] = ((v >> 4) & 0x0F0F0F0F0F0F0F0Full) | ((v & 0x0F0F0F0F0F0F0F0Full) << 4);
+    scale = xs[b];
+  }
+  const size_t tile = size_t(r / 128) * (blocks_per_row / 4) + kb / 4;
+  os[tile * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + kb % 4] = scale;
+}
+}  // namespace
+
+void convrot_f32(const float* in, float* out, int rows, int dim, int group, cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) return;
+  if (group <= 0 || dim % group != 0)
+    throw std::runtime_error("convrot: dim " + std::to_string(dim) + " is not a multiple of group " + std::to_string(group));
+  int stages = 0, n = 1;
+  while (n < group) n *= 4, ++stages;
+  if (n != group) throw std::runtime_error("convrot: group size must be a power of four, got " + std::to_string(group));
+  if (group > 4096) throw std::runtime_error("convrot: group " + std::to_string(group) + " needs more than 1024 threads per block");
+  if (!in || !out) throw std::invalid_argument("convrot_f32: null buffer");
+  const size_t groups = size_t(rows) * (dim / group);
+  const float norm = 1.0f / sqrtf(float(group));  // a power of two: exact
+  const int warps = group > 1024 ? 2 : 8;
+  convrot_f32_kernel<<<unsigned((groups + warps - 1) / warps), warps * 32, size_t(warps) * group * sizeof(float), stream>>>(in, out, group, stages,
+                                                                                                                       norm, groups);
+  check_launch("convrot_f32");
+}
+
+void pre_quant_scale_f32(const float* src, const __nv_bfloat16* scale, float* dst, int rows, int dim, cudaStream_t stream) {
+  if (rows <= 0 || dim <= 0) return;
+  if (scale == nullptr) throw std::runtime_error("pre_quant_scale: null scale");
+  if (!src || !dst) throw std::invalid_argument("pre_quant_scale: null buffer");
+  pre_quant_scale_f32_kernel<<<dim3(rows, (dim + 255) / 256), 256, 0, stream>>>(src, scale, dst, dim);
+  check_launch("pre_quant_scale_f32");
+}
+
+void int8_output_bf16(const int32_t* acc, const float* row_scale, const float* channel_scale, __nv_bfloat16* out, int rows, int cols,
+                      cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return;
+  if (!acc || !row_scale || !channel_scale || !out) throw std::invalid_argument("W4A8 output scaling received a null buffer");
+  int8_output_bf16_kernel<<<dim3(rows, (cols + 255) / 256), 256, 0, stream>>>(acc, row_scale, channel_scale, out, cols);
+  check_launch("int8_output_bf16");
+}
+
+void int8_output_f32_inplace(int32_t* io, const float* row_scale, const float* channel_scale, int rows, int cols, cudaStream_t stream) {
+  if (!io || !row_scale || !channel_scale) throw std::invalid_argument("W4A8 output dequantization received a null buffer");
+  if (rows <= 0 || cols <= 0) throw std::invalid_argument("W4A8 output dequantization received an invalid shape");
+  int8_output_f32_kernel<<<dim3(rows, (cols + 255) / 256), 256, 0, stream>>>(io, row_scale, channel_scale, cols);
+  check_launch("int8_output_f32");
+}
+
+void quantize_f8e4m3(const __nv_bfloat16* src, float input_scale, uint8_t* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  if (input_scale == 0.0f)
+    throw std::runtime_error("launch_quantize_f8e4m3: input_scale is zero, which marks a layer that has no activation scale");
+  if (!src || !dst) throw std::invalid_argument("quantize_f8e4m3: null buffer");
+  quantize_f8_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(src, 1.0f / input_scale, dst, n);
+  check_launch("quantize_f8e4m3");
+}
+
+void widen_bf16(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  widen_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(src, dst, n);
+  check_launch("widen_bf16");
+}
+
+void narrow_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  narrow_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(src, dst, n);
+  check_launch("narrow_to_bf16");
+}
+
+void nvfp4_act_to_feed(const uint8_t* xq, const uint8_t* xs, uint8_t* feed_q, uint8_t* feed_scale_tiled, int rows, int dim,
+                       cudaStream_t stream) {
+  if (rows <= 0) return;
+  if (dim <= 0 || dim % 64 != 0) throw std::invalid_argument("nvfp4_act_to_feed: dim must be a multiple of 64");
+  if (!xq || !xs || !feed_q || !feed_scale_tiled) throw std::invalid_argument("nvfp4_act_to_feed: null buffer");
+  if (reinterpret_cast<uintptr_t>(xq) % 8 != 0 || reinterpret_cast<uintptr_t>(feed_q) % 8 != 0)
+    throw std::invalid_argument("nvfp4_act_to_feed: packed activations must be 8-byte aligned");
+  const int blocks = dim / 16, padded = (rows + 127) / 128 * 128;
+  nvfp4_act_to_feed_kernel<<<dim3(padded, (blocks + 127) / 128), 128, 0, stream>>>(xq, xs, feed_q, feed_scale_tiled, rows, blocks);
+  check_launch("nvfp4_act_to_feed");
 }
 
 // ---- fp32 Linear (the reference's fp32-compute arm, src/cuda/linear.cu:251-285: fp32 GEMM + add_bias) ----

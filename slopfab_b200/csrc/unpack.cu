@@ -240,10 +240,15 @@ unpack_f8_kernel(const uint8_t* __restrict__ src, const float* __restrict__ scal
 // bitsandbytes NF4, double-quantized block scales, high nibble = even element
 // (dequant_nf4_kernel / dequant_nf4_vec_kernel, src/cuda/linear_weights.cu:273-315):
 // value = map[code] * (nested_map[absmax[block]] * nested_absmax[block / nested_block] + offset).
+template <class T> __device__ __forceinline__ T narrow_to(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 narrow_to<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half narrow_to<__half>(float v) { return __float2half_rn(v); }
+
+template <class T>
 __global__ void __launch_bounds__(kThreads)
 unpack_nf4_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ absmax, const float* __restrict__ map,
                   const float* __restrict__ nested_map, const float* __restrict__ nested_absmax, int block,
-                  int nested_block, float offset, __nv_bfloat16* __restrict__ dst, size_t n) {
+                  int nested_block, float offset, T* __restrict__ dst, size_t n) {
   __shared__ float lut[16];
   if (threadIdx.x < 16) lut[threadIdx.x] = map[threadIdx.x];
   __syncthreads();
@@ -253,12 +258,12 @@ unpack_nf4_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ a
   const size_t b = even / size_t(block);
   const float scale = __fmaf_rn(nested_map[absmax[b]], nested_absmax[b / size_t(nested_block)], offset);
   const uint8_t packed = src[byte];
-  dst[even] = __float2bfloat16(lut[packed >> 4] * scale);
+  dst[even] = narrow_to<T>(lut[packed >> 4] * scale);
   if (even + 1 < n) {
     // an odd block size could put the odd element in the next block; recompute when it does
     const size_t b1 = (even + 1) / size_t(block);
     const float s1 = b1 == b ? scale : __fmaf_rn(nested_map[absmax[b1]], nested_absmax[b1 / size_t(nested_block)], offset);
-    dst[even + 1] = __float2bfloat16(lut[packed & 15] * s1);
+    dst[even + 1] = narrow_to<T>(lut[packed & 15] * s1);
   }
 }
 
@@ -284,9 +289,22 @@ void unpack_nf4_bf16(const uint8_t* src, const uint8_t* absmax, const float* map
     throw std::runtime_error("linear: nf4 weight without complete double-quant state");
   if (block <= 0 || nested_block <= 0) throw std::invalid_argument("unpack_nf4: block sizes must be positive");
   const size_t n = size_t(out_features) * in_features;
-  unpack_nf4_kernel<<<blocks_for((n + 1) / 2, kThreads), kThreads, 0, stream>>>(src, absmax, map, nested_map, nested_absmax,
-                                                                               block, nested_block, offset, dst, n);
+  unpack_nf4_kernel<__nv_bfloat16><<<blocks_for((n + 1) / 2, kThreads), kThreads, 0, stream>>>(src, absmax, map, nested_map, nested_absmax,
+                                                                                              block, nested_block, offset, dst, n);
   check_launch("unpack_nf4");
+}
+
+// The fp16 form over a flat element count (launch_dequant_nf4_f16, src/cuda/linear_weights.cu:317-335).
+void unpack_nf4_f16(const uint8_t* src, const uint8_t* absmax, const float* map, const float* nested_map,
+                    const float* nested_absmax, int block, int nested_block, float offset, __half* dst, size_t n,
+                    cudaStream_t stream) {
+  if (n == 0) return;
+  if (!src || !absmax || !map || !nested_map || !nested_absmax || !dst)
+    throw std::runtime_error("linear: nf4 weight without complete double-quant state");
+  if (block <= 0 || nested_block <= 0) throw std::invalid_argument("unpack_nf4: block sizes must be positive");
+  unpack_nf4_kernel<__half><<<blocks_for((n + 1) / 2, kThreads), kThreads, 0, stream>>>(src, absmax, map, nested_map, nested_absmax, block,
+                                                                                       nested_block, offset, dst, n);
+  check_launch("unpack_nf4_f16");
 }
 
 void convert_f16_bf16(const __half* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {

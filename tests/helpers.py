@@ -104,7 +104,10 @@ def ref_dev():
             "ref_dev_quantize_nvfp4_act": [V, V, V, I, I], "ref_dev_rmsnorm": [V, V, V, V, V, V, I, I, F],
             "ref_dev_gelu_tanh": [V, SZ], "ref_dev_swiglu": [V, V, I, I], "ref_dev_add_gated": [V, V, V, V, I, I],
             "ref_dev_linear_forward": [C.POINTER(RefWeight), V, I, V, I, I, C.POINTER(F)],
-            "ref_dev_packed_int8_accumulate": [C.POINTER(RefWeight), V, I, V, V, V, V, V]}
+            "ref_dev_packed_int8_accumulate": [C.POINTER(RefWeight), V, I, V, V, V, V, V],
+            "ref_dev_convrot_f32": [V, V, I, I, I], "ref_dev_quantize_f8": [V, F, V, SZ],
+            "ref_dev_dequant_nf4_f16": [V, V, V, V, V, I, I, F, V, SZ], "ref_dev_output_f32": [V, V, V, I, I],
+            "ref_dev_linear_forward_f32": [C.POINTER(RefWeight), V, I, V]}
     for name, args in sigs.items():
         fn = getattr(ref, name)
         fn.restype = I

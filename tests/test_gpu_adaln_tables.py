@@ -92,9 +92,6 @@ def test_forward_f32_against_the_fp64_product(fmt, rows, n, k):
 def test_forward_f32_refuses_what_it_does_not_build():
     t = torch.zeros(256 * 256, dtype=torch.float32, device="cuda")
     runner = sfq.LinearRunner()
-    w = sfq.new_weight(format=sfq.F32, data=sfq.ptr(t), out_features=256, in_features=256, convrot=1, convrot_group=256)
-    with pytest.raises(sfq.SfqError, match="ConvRot"):
-        runner.forward_f32(w, t.view(256, 256))
     w = sfq.new_weight(format=sfq.W4A8, data=sfq.ptr(t), out_features=256, in_features=256)
     with pytest.raises(sfq.SfqError, match="BF16 activations"):
         runner.forward_f32(w, t.view(256, 256))
