@@ -1,26 +1,40 @@
 """Benchmark of the quantized-Linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--extra]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
 
-Workload (config.workload): benchmark configuration 2 -- the W4A8 attention projection, M=4096 tokens,
-K=N=5120, weights ~N(0,0.02) packed by the library's W4A8 packer, activations bf16 ~N(0,1) with
-0.1 % outliers x20, fp32 bias, seed 1. A step is one LinearRunner.forward: expand the packed weight,
-fused ConvRot + per-token int8, tcgen05 int8 GEMM with the scale/bias epilogue (3 launches).
+Workload (config.workload): benchmark configuration 5 -- the DiT Linears K/N = 5120/5120 (attention projection),
+5120/13824 (FFN up) and 13824/5120 (FFN down) at M = 31x45x80 = 111600 token rows, each as NVFP4 (native fp4
+activations) and as W4A8, the token rows SHARDED over the N ranks of the launch with replicated weights and no
+collective on the data path (strong scaling: the total work is fixed). Weights ~N(0,0.02) packed by the library's own
+packers, activations bf16 ~N(0,1) with 0.1 % outliers x20, seed 4. A step is one pass over the six Linears through
+LinearRunner.forward on the rank's rows: quantizer + GEMM for NVFP4, weight expansion + quantizer + GEMM for W4A8
+(15 launches).
 
-value  whole-job TFLOP/s (2*M*N*K per step per GPU) with inputs resident in HBM, K steps between CUDA
-       events, max over ranks. Inputs rotate over several distinct buffers whose total exceeds L2.
-e2e    the same metric through the same call with HOST buffers: pinned x -> device, forward, y -> host,
-       both copies inside the timed region.
-roofline   the dominant kernel (the int8 GEMM) timed alone with CUDA events; tensor-bound.
-cpu_baseline / --impl reference   the reference's host path (decode to dense fp32, x * W^T) restated in
-       oracle/ and timed on the host cores over a bounded row sample.
-Multi-GPU: tokens are sharded, weights replicated, no collective on the data path (weak scaling).
+value      whole-job TFLOP/s (2*M*N*K summed over the six Linears, M the full 111600) with inputs resident in HBM,
+           K steps between CUDA events, max over ranks. Every operand is far larger than L2 (126 MB).
+e2e        the same metric through the same calls with HOST buffers: pinned x -> device, forward, y -> host for every
+           Linear of the step, the copies inside the timed region, three streams so that consecutive Linears overlap
+           copy-in, compute and copy-out.
+linears    per Linear: ms, TFLOP/s, and the fraction of the derived (2x / 4x the measured dense bf16 burst) and of the
+           nominal (4.5 / 9 PFLOP/s) tensor peaks per GPU.
+roofline   the dominant kernel -- the NVFP4 CTA-pair GEMM at the FFN-up shape -- timed alone; tensor-bound.
+column_split   the FFN-up column split: every rank quantizes its rows, ONE all-gather of the quantized activation (run
+           as pairwise steps on a communication stream, overlapped with the GEMMs of the blocks already here), each rank
+           computes its output columns for all tokens. Reported beside the blocking form, with the collective's own time.
+dit_block  (N=1) benchmark configuration 4: one NVFP4 DiT block at 75600 tokens, Linear-path and whole-block ms.
+gpu_reference  (N=1) the reference's own LinearRunner (its kernels + cuBLAS, compiled unmodified for sm_100a as the
+           test checker) timed on the same Linears on this GPU: reference leg only, never on the product path.
+cpu_baseline / --impl reference   the reference's host path (decode to dense fp32, x * W^T) restated in oracle/ and timed
+           on all host cores over a bounded row sample of each of the six Linears.
+Other modes: --config2, --config3, --block-stack, --case NAME, --extra (see their help).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -31,12 +45,31 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
+# ---- the headline workload: configuration 5
+TOKENS = 31 * 45 * 80
+SHAPES = (("attn_proj", 5120, 5120), ("ffn_up", 5120, 13824), ("ffn_down", 13824, 5120))  # name, K (in), N (out)
+KINDS = ("nvfp4", "w4a8")
+SEED5 = 4
+WORKLOAD5 = ("config5: NVFP4 and W4A8 DiT Linears K/N 5120/5120, 5120/13824, 13824/5120 at M=111600 tokens, "
+             "token-sharded over the ranks, weights replicated, bf16 in/out")
+CPU_SAMPLE_ROWS5 = 128
+NOMINAL_TFLOPS = {"nvfp4": 9000.0, "w4a8": 4500.0}
+PEAK_MULT = {"nvfp4": 4.0, "w4a8": 2.0}  # derived peaks: multiples of the measured dense bf16 burst
+
+# ---- configuration 2 (--config2)
 M, N, K = 4096, 5120, 5120
 SEED = 1
 WORKLOAD = "config2: W4A8 attention projection M=4096 K=N=5120, bf16 in/out, fp32 bias"
 METRIC = "quantized_linear_tflops"
 UNIT = "TFLOP/s"
 CPU_SAMPLE_ROWS = 256
+
+
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def load_peaks():
@@ -67,13 +100,13 @@ class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, period_ms: int = 100):
+        self.index, self.rows, self.proc, self.period_ms = index, [], None, period_ms
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -136,7 +169,7 @@ def cpu_baseline(np, data, steps=1, warmup=0):
             "ms_per_sample": dt * 1e3}
 
 
-def run_reference(args):
+def run_reference_config2(args):
     import numpy as np
 
     rank = int(os.environ.get("RANK", "0"))
@@ -153,8 +186,6 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one config-2 GEMM launch (ncu capture of `--case gemm_int8_c2`).
-C2_GEMM_DRAM_BYTES = 52883456 + 14948352
 
 
 def time_region(torch, fn, iters):
@@ -168,7 +199,7 @@ def time_region(torch, fn, iters):
     return a.elapsed_time(b)
 
 
-def run_ours(args):
+def run_config2(args):
     import ctypes as C
 
     import numpy as np
@@ -325,7 +356,7 @@ def run_ours(args):
             "gpu_launches": 3 * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<int8> (CTA pair, 256x256 tile)", "achieved": gemm_tflops,
-                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / int8_peak, "traffic": C2_GEMM_DRAM_BYTES,
+                         "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / int8_peak, "traffic": profile_value("bench_config2_w4a8_launch_list.md", "dram_bytes_per_launch"),
                          "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this GEMM on cold "
                                          "operands (ncu, profiles/bench_config2_w4a8_launch_list.md); algorithmic bytes "
                                          f"{M * K + N * K + 2 * M * N}; part of the 42 MB output is still in L2 when the kernel ends",
@@ -375,7 +406,7 @@ def extra_measurements(torch, np, sfq, peaks):
                                                          C.byref(ep4), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
         reps = 20 if m <= 4096 else 5
         for tile_n in (0, 256):  # 0 = default (CTA pairs on 256x256 tiles), 256 = one CTA per 128x256 tile
-            sfq.lib.sfq_gemm_tuning(tile_n, 0, 0)
+            sfq.lib.sfq_test_gemm_variant(tile_n, 0, 0)
             for kind, f, mult in (("int8", fn, 2), ("nvfp4", fn4, 4)):
                 for i in range(2):
                     f(i)
@@ -384,7 +415,7 @@ def extra_measurements(torch, np, sfq, peaks):
                 tf = 2.0 * m * n * k / ms / 1e9
                 out[f"{kind}_{name}_{'pair' if tile_n == 0 else 'bn%d' % tile_n}"] = {"ms": round(ms, 4), "tflops": round(tf, 1),
                                                     f"frac_of_{mult}x_bf16": round(tf / (mult * peaks["bf16_tflops"]), 3)}
-        sfq.lib.sfq_gemm_tuning(0, 0, 0)
+        sfq.lib.sfq_test_gemm_variant(0, 0, 0)
         del a8, w8, aq, wq, asf, wsf, y
         torch.cuda.empty_cache()
     out["device_status"] = sfq.device_status()
@@ -400,7 +431,6 @@ def run_case(name):
     import slopfab_b200 as sfq
 
     torch.cuda.set_device(0)
-    sfq.lib.sfq_gemm_tuning(int(os.environ.get("SFQ_TILE_N", "0")), 0, 0)  # experiments: 128 or 256
     m, n, k = 16384, 5120, 5120
     reps = 3
     y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
@@ -434,6 +464,27 @@ def run_case(name):
         fn = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
                                                         C.byref(ep), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
         work = 2.0 * m * n * k
+    elif name == "gemm_nvfp4_ffn_up":
+        # the benchmark's dominant kernel at a quarter of its rows (27900 x 5120 -> 13824): 0.9 GB on the device
+        m, n = TOKENS // 4, 13824
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        aq = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda")
+        wq = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+        asf = torch.randint(0x30, 0x40, (sfq.lib.sfq_nvfp4_act_scale_bytes(m, k),), dtype=torch.uint8, device="cuda")
+        wsf = torch.randint(0x30, 0x40, (n * k // 16,), dtype=torch.uint8, device="cuda")
+        ep = sfq.Epilogue(None, None, 1e-3, None, sfq.F32, sfq.ACT_NONE)
+        fn = lambda i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(aq), sfq.ptr(asf), sfq.ptr(wq), sfq.ptr(wsf),  # noqa: E731
+                                                        C.byref(ep), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
+        work = 2.0 * m * n * k
+    elif name == "unpack_w4a8":
+        n = 13824
+        packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda").view(torch.int8)
+        s_rel = torch.randint(0x28, 0x39, (n * k // 16,), dtype=torch.uint8, device="cuda")
+        book = torch.arange(16, dtype=torch.float32, device="cuda") - 8.0
+        outs = [torch.empty((n, k), dtype=torch.int8, device="cuda") for _ in range(3)]
+        fn = lambda i: sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(packed), sfq.ptr(s_rel), sfq.ptr(book), sfq.ptr(outs[i % 3]), n, k,  # noqa: E731
+                                                              16, sfq.stream_ptr()))
+        work = n * k / 2 + n * k / 16 + n * k
     elif name in ("quantize_int8", "quantize_nvfp4", "quantize_int8_k13824"):
         m = 32768
         if name == "quantize_int8_k13824":  # the FFN-down input of config 3
@@ -574,130 +625,465 @@ def run_config3(rows=32760, hidden=5120, ffn=13824, group=64, reps=5):
                       "finite": bool(torch.isfinite(y.float()).all().item()), "device_status": sfq.device_status()}))
 
 
-def run_config5(steps=5):
-    """benchmark configuration 5: NVFP4 and W4A8 DiT Linears at M = 31x45x80 = 111600 tokens, token-sharded over the ranks
-    of this launch (weights replicated, no collective), plus the FFN-up column split with one all-gather. Launch
-    under torch.distributed.run for more than one GPU. One JSON line per (kind, shape, scheme), aggregate TFLOP/s."""
+def profile_value(filename, key):
+    """A `key = <integer>` line of a summary under profiles/ (the figures an ncu capture gave), or None."""
+    path = os.path.join(ROOT, "profiles", filename)
+    if not os.path.exists(path):
+        return None
+    m = re.search(r"^\s*" + re.escape(key) + r"\s*=\s*(\d+)", open(path).read(), re.M)
+    return int(m.group(1)) if m else None
+
+
+def set_pack_threads(n):
+    """The host packers run under OpenMP; a launcher that exports OMP_NUM_THREADS=1 would make them crawl."""
+    import ctypes as C
+
+    try:
+        C.CDLL("libgomp.so.1").omp_set_num_threads(int(n))
+    except OSError:
+        pass
+
+
+def config5_weights_host(torch, np):
+    """The three weights ~N(0, 0.02), seed 4, in both storage forms, packed on the host by the library's packers.
+    The same bytes serve both arms of the benchmark."""
+    from helpers import pack_nvfp4, pack_w4a8
+
+    out = {}
+    for i, (name, k, n) in enumerate(SHAPES):
+        g = torch.Generator().manual_seed(SEED5 * 100 + i)
+        w = (0.02 * torch.randn((n, k), generator=g)).numpy()
+        data, scale, gs = pack_nvfp4(w)
+        packed, s_rel, s_ch, book = pack_w4a8(w)
+        out[name] = {"nvfp4": (data, scale, np.float32(gs)), "w4a8": (packed, s_rel, s_ch, book)}
+    return out
+
+
+def config5_activation(torch, rows, k, seed, device):
+    """bf16 ~N(0,1) with 0.1 % of the elements x20 (the distribution of configurations 1-2)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn((rows, k), device=device, generator=g)
+    x = torch.where(torch.rand((rows, k), device=device, generator=g) < 1e-3, x * 20.0, x)
+    return x.to(torch.bfloat16)
+
+
+def cpu_baseline5(np, torch, weights, steps=1, warmup=0):
+    """Reference host path on a bounded sample of every Linear of the step: decode W to dense fp32 (rotate x for W4A8),
+    y = x W^T, all host threads."""
+    import ctypes as C
+
+    import oracle
+
+    oracle.lib.orc_set_num_threads(host_threads())
+    rows = CPU_SAMPLE_ROWS5
+    P = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+    xs = {}
+    for k in (5120, 13824):
+        x = config5_activation(torch, rows, k, SEED5 + 7, "cpu")
+        xs[k] = np.ascontiguousarray(x.view(torch.int16).numpy().view(np.uint16))
+    ys = {n: np.empty((rows, n), np.float32) for n in (5120, 13824)}
+
+    def once():
+        for name, k, n in SHAPES:
+            data, scale, gs = weights[name]["nvfp4"]
+            oracle.lib.orc_host_dequant_matmul(0, P(xs[k]), rows, P(data), P(scale), None, None, float(gs), 16, n, k, P(ys[n]))
+            packed, s_rel, s_ch, book = weights[name]["w4a8"]
+            oracle.lib.orc_host_dequant_matmul(4, P(xs[k]), rows, P(packed), P(s_rel), P(s_ch), P(book), 1.0, 16, n, k, P(ys[n]))
+
+    for _ in range(warmup):
+        once()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        once()
+    dt = (time.perf_counter() - t0) / steps
+    flops = sum(2.0 * rows * n * k for _, k, n in SHAPES) * len(KINDS)
+    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": oracle.lib.orc_num_threads(), "kind": "port",
+            "sample": f"{rows} of {TOKENS} rows of each of the six Linears, weight decode included, per step",
+            "ms_per_sample": dt * 1e3}
+
+
+def gpu_reference5(torch, weights_dev, xs, rows, iters=3):
+    """The reference's own LinearRunner (unmodified sources compiled for sm_100a under oracle/_ref: dequantize + cuBLAS
+    bf16 for NVFP4, its six-launch integer path + cuBLAS int8 for W4A8) timed on the same Linears and rows on this GPU.
+    Reference leg only. Returns {linear: {kind: ms}} or a reason string."""
+    import ctypes as C
+
+    import slopfab_b200 as sfq
+    from helpers import ref_dev, ref_weight_from
+
+    ref = ref_dev()
+    if ref is None:
+        return "oracle/_ref was not built (the reference tree was absent at build time)"
+    out = {}
+    for name, k, n in SHAPES:
+        y = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
+        out[name] = {}
+        for kind in KINDS:
+            rw = ref_weight_from(weights_dev[name][kind][0])
+            ms = C.c_float(0.0)
+            rc = ref.ref_dev_linear_forward(C.byref(rw), sfq.ptr(xs[k]), rows, sfq.ptr(y), 0, iters, C.byref(ms))
+            if rc != 0:
+                return "the reference's LinearRunner failed: " + ref.ref_last_error().decode("utf-8", "replace")
+            out[name][kind] = ms.value
+        del y
+    return out
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU implementation of the path on this box's host cores, rank 0 only."""
+    import numpy as np
+    import torch
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    set_pack_threads(host_threads())
+    weights = config5_weights_host(torch, np)
+    base = cpu_baseline5(np, torch, weights, steps=max(1, args.steps), warmup=min(max(args.warmup, 0), 2))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_sample"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD5, "seed": SEED5}, "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def dit_block_ms(torch, sfq, blocks=2, rows=75600, hidden=5120, heads=40, ffn=13824):
+    """Configuration 4 on one GPU: `blocks` NVFP4 DiT blocks at 75600 tokens after one warm-up block."""
+    from slopfab_b200.block import BlockWeights, Nvfp4Block, Nvfp4Linear
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((rows, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    names = ["scale_msa", "shift_msa", "gate_msa", "scale_mlp", "shift_mlp", "gate_mlp"]
+    mod = {n: 0.1 * torch.randn((3, hidden), device="cuda", generator=g) for n in names}
+    index = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    ones = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    ws = [BlockWeights(Nvfp4Linear.random(3 * hidden, hidden, seed=4 * b), Nvfp4Linear.random(hidden, hidden, seed=4 * b + 1),
+                       Nvfp4Linear.random(ffn, hidden, seed=4 * b + 2), Nvfp4Linear.random(hidden, ffn, seed=4 * b + 3), ones, ones)
+          for b in range(blocks)]
+    blk = Nvfp4Block(rows, hidden, heads, ffn)
+    blk.forward(x.clone(), ws[0], mod, index)
+    torch.cuda.synchronize()
+    blk.linear_ms = 0.0
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for w in ws:
+        blk.forward(x, w, mod, index, time_linears=True)
+    b.record()
+    b.synchronize()
+    total = a.elapsed_time(b)
+    flops_linear = 2.0 * rows * hidden * (3 * hidden + hidden + 2 * ffn)
+    out = {"workload": "config4: one NVFP4 DiT block, 75600 tokens, hidden 5120, 40 heads x128, FFN 13824 (GELU), adaLN-modulated "
+                       "RMSNorm, attention in bf16 (this library's tcgen05 kernel)",
+           "blocks_timed": blocks, "block_ms": total / blocks, "linear_path_ms": blk.linear_ms / blocks,
+           "linear_path_tflops": flops_linear / (blk.linear_ms / blocks * 1e-3) / 1e12,
+           "attention_ms": (total - blk.linear_ms) / blocks,
+           "attention_tflops": 4.0 * rows * rows * hidden / ((total - blk.linear_ms) / blocks * 1e-3) / 1e12,
+           "finite": bool(torch.isfinite(x.float()).all().item())}
+    del blk, ws, x
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args):
+    """The headline run: configuration 5 on the ranks of this launch (see the module docstring)."""
+    import ctypes as C
+
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     import slopfab_b200 as sfq
+    from helpers import dev
     from slopfab_b200.parallel import ColumnSplitPlan, column_shard, token_shard
 
-    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = load_peaks()
-    M = 31 * 45 * 80
-    _, m = token_shard(M, world, rank)
-    g = torch.Generator(device="cuda").manual_seed(4)
-    import ctypes as C
+    steps, warmup = max(1, args.steps), max(args.warmup, 3)
+    _, m = token_shard(TOKENS, world, rank)
 
-    def timed(fn):
-        for i in range(2):
-            fn()
+    def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(steps):
-            fn()
-        b.record()
-        b.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / steps], dtype=torch.float64, device="cuda")
+
+    def max_over_ranks(values):
+        t = torch.tensor(values, dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.item()
+        return t.tolist()
 
-    for kname, k, n in (("attn_proj", 5120, 5120), ("ffn_up", 5120, 13824), ("ffn_down", 13824, 5120)):
-        x = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
-        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-        # ---- W4A8: int8 expansion held (what prepare() keeps for a chunk loop), fused quantizer + GEMM per call
-        w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
-        cs = torch.rand(n, device="cuda", generator=g) * 0.01
-        q = torch.empty((m, k), dtype=torch.int8, device="cuda")
-        rs = torch.empty(m, device="cuda")
-        ep8 = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
-
-        def w4a8():
-            sfq.check(sfq.lib.sfq_quantize_int8_token(sfq.ptr(x), None, sfq.ptr(q), sfq.ptr(rs), None, m, k, 1, sfq.stream_ptr()))
-            sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(q), sfq.ptr(w8), C.byref(ep8), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
-
-        # ---- NVFP4 native
-        wq = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
-        wsf = torch.randint(0x30, 0x40, (n * k // 16,), dtype=torch.uint8, device="cuda", generator=g)
-        xq = torch.empty((m, k // 2), dtype=torch.uint8, device="cuda")
-        xsf = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(m, k), dtype=torch.uint8, device="cuda")
-        ep4 = sfq.Epilogue(None, None, 1e-3, None, sfq.F32, sfq.ACT_NONE)
-
-        def nvfp4():
-            sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(x), None, sfq.ptr(xq), sfq.ptr(xsf), None, m, k,
-                                                       sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
-            sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(xq), sfq.ptr(xsf), sfq.ptr(wq), sfq.ptr(wsf), C.byref(ep4), sfq.ptr(y), m, n, k,
-                                             sfq.stream_ptr()))
-
-        flops = 2.0 * M * n * k
-        for kind, fn, mult in (("w4a8", w4a8, 2), ("nvfp4", nvfp4, 4)):
-            ms = timed(fn)
-            if rank == 0:
-                tf = flops / (ms * 1e-3) / 1e12
-                print(json.dumps({"case": "config5", "kind": kind, "linear": kname, "scheme": "token-sharded", "n_gpus": world,
-                                  "tokens": M, "ms": ms, "tflops": tf,
-                                  "frac_of_peak": tf / (world * mult * peaks["bf16_tflops"]),
-                                  "peak_note": f"{mult} x measured dense bf16 burst per GPU"}), flush=True)
-        if kname == "ffn_up" and M % world == 0:
-            c0, nl = column_shard(n, world, rank)
-            plans = {"w4a8": ColumnSplitPlan("w4a8", m, k, nl, (w8[c0:c0 + nl].contiguous(), cs[c0:c0 + nl].contiguous()), world),
-                     "nvfp4": ColumnSplitPlan("nvfp4", m, k, nl, (wq[c0:c0 + nl].contiguous(),
-                                                                  wsf.view(n // 128, -1)[c0 // 128:(c0 + nl) // 128].contiguous().view(-1), 1e-3), world)}
-            for kind, mult in (("w4a8", 2), ("nvfp4", 4)):
-                ms = timed(lambda: plans[kind].forward(x))
-                if rank == 0:
-                    tf = flops / (ms * 1e-3) / 1e12
-                    print(json.dumps({"case": "config5", "kind": kind, "linear": kname, "scheme": "column-split, one all-gather",
-                                      "n_gpus": world, "tokens": M, "ms": ms, "tflops": tf,
-                                      "frac_of_peak": tf / (world * mult * peaks["bf16_tflops"]),
-                                      "gathered_bytes_per_gpu": plans[kind].block * (world - 1)}), flush=True)
-            del plans
-        del x, y, w8, q, wq, wsf, xq, xsf
-        torch.cuda.empty_cache()
-    st = sfq.device_status()
+    # ---- weights: packed once on rank 0 by the library's packers, then replicated to every GPU
+    host = None
     if rank == 0:
-        print(json.dumps({"case": "config5", "device_status": st}))
+        set_pack_threads(min(host_threads(), 32))
+        host = config5_weights_host(torch, np)
+    wdev = {}
+    for name, k, n in SHAPES:
+        sizes = {"nvfp4": [(n, k // 2), (n * k // 16,)], "w4a8": [(n, k // 2), (n * k // 16,), (n,), (16,)]}
+        dtypes = {"nvfp4": [torch.uint8, torch.uint8], "w4a8": [torch.int8, torch.uint8, torch.float32, torch.float32]}
+        wdev[name] = {}
+        for kind in KINDS:
+            if rank == 0:
+                arrays = host[name][kind][:2] if kind == "nvfp4" else host[name][kind]
+                tensors = [dev(np.ascontiguousarray(a)) for a in arrays]
+            else:
+                tensors = [torch.empty(sh, dtype=dt, device="cuda") for sh, dt in zip(sizes[kind], dtypes[kind])]
+            gs = torch.tensor([float(host[name]["nvfp4"][2]) if rank == 0 else 0.0], dtype=torch.float32, device="cuda")
+            if world > 1:
+                for t in tensors:
+                    dist.broadcast(t, 0)
+                dist.broadcast(gs, 0)
+            if kind == "nvfp4":
+                w = sfq.new_weight(format=sfq.NVFP4, data=sfq.ptr(tensors[0]), out_features=n, in_features=k,
+                                   block_scale=sfq.ptr(tensors[1]), global_scale=gs.item())
+            else:
+                w = sfq.new_weight(format=sfq.W4A8, data=sfq.ptr(tensors[0]), out_features=n, in_features=k,
+                                   block_scale=sfq.ptr(tensors[1]), weight_scale=sfq.ptr(tensors[2]), w4_codebook=sfq.ptr(tensors[3]),
+                                   packed_group_size=16, convrot=1, convrot_group=256)
+            wdev[name][kind] = (w, tensors)
+    # ---- activations and outputs of this rank's token rows, resident in HBM
+    xs = {k: config5_activation(torch, m, k, SEED5 + 1000 * rank + k, "cuda") for k in (5120, 13824)}
+    ys = {n: torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for n in (5120, 13824)}
+    runners = {"nvfp4": sfq.LinearRunner(), "w4a8": sfq.LinearRunner()}
+    runners["nvfp4"].set_native(True)
+    for kind in KINDS:
+        runners[kind].reserve(max(runners[kind].workspace_bytes(wdev[name][kind][0], m) for name, _, _ in SHAPES))
+    calls = [(kind, name, k, n) for kind in KINDS for name, k, n in SHAPES]
+    launches_per_step = sum(2 if kind == "nvfp4" else 3 for kind, *_ in calls)
+    flops_step = sum(2.0 * TOKENS * n * k for _, _, k, n in calls)  # the whole job's, all ranks together
+
+    def step(_i=0):
+        for kind, name, k, n in calls:
+            runners[kind].forward(wdev[name][kind][0], xs[k], ys[n])
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    with ClockSampler(local, period_ms=50) as clocks:
+        barrier()
+        ms = time_region(torch, step, steps)
+        barrier()
+    ms_max = max_over_ranks([ms])[0]
+    value = flops_step * steps / (ms_max * 1e-3) / 1e12
+
+    # ---- per Linear: the same call alone
+    table = []
+    reps = 8 if world == 1 else 16
+    for kind, name, k, n in calls:
+        fn = lambda _i, kind=kind, name=name, k=k, n=n: runners[kind].forward(wdev[name][kind][0], xs[k], ys[n])  # noqa: E731
+        fn(0)
+        barrier()
+        t = max_over_ranks([time_region(torch, fn, reps) / reps])[0]
+        tf = 2.0 * TOKENS * n * k / (t * 1e-3) / 1e12
+        derived = PEAK_MULT[kind] * peaks["bf16_tflops"]
+        table.append({"linear": name, "kind": kind, "K": k, "N": n, "ms": t, "tflops": tf, "tflops_per_gpu": tf / world,
+                      "frac_of_derived_peak": tf / world / derived, "frac_of_nominal_peak": tf / world / NOMINAL_TFLOPS[kind]})
+
+    # ---- the dominant kernel alone: the NVFP4 CTA-pair GEMM at the FFN-up shape on pre-quantized operands
+    k_up, n_up = 5120, 13824
+    xq = torch.empty((m, k_up // 2), dtype=torch.uint8, device="cuda")
+    xsf = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(m, k_up), dtype=torch.uint8, device="cuda")
+    sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(xs[k_up]), None, sfq.ptr(xq), sfq.ptr(xsf), None, m, k_up,
+                                               sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
+    w_up, t_up = wdev["ffn_up"]["nvfp4"]
+    ep4 = sfq.Epilogue(None, None, w_up.global_scale, None, sfq.F32, sfq.ACT_NONE)
+    gemm_fn = lambda _i: sfq.check(sfq.lib.sfq_gemm_nvfp4(sfq.ptr(xq), sfq.ptr(xsf), sfq.ptr(t_up[0]), sfq.ptr(t_up[1]), C.byref(ep4),  # noqa: E731
+                                                          sfq.ptr(ys[n_up]), m, n_up, k_up, sfq.stream_ptr()))
+    quant_fn = lambda _i: sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(xs[k_up]), None, sfq.ptr(xq), sfq.ptr(xsf), None, m, k_up,  # noqa: E731
+                                                                     sfq.NVFP4_ACT_GEMM_FEED, sfq.stream_ptr()))
+    for i in range(3):
+        gemm_fn(i)
+    torch.cuda.synchronize()
+    gemm_ms = time_region(torch, gemm_fn, 10) / 10
+    quant_ms = time_region(torch, quant_fn, 10) / 10
+    del xq, xsf
+
+    # ---- end to end: host buffers, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        wide = 13824
+        hx = {k: torch.empty((m, k), dtype=torch.bfloat16, pin_memory=True) for k in (5120, 13824)}
+        for k in hx:
+            hx[k].copy_(xs[k])
+        hy = [torch.empty((m, wide), dtype=torch.bfloat16, pin_memory=True) for _ in range(2)]
+        dxb = [torch.empty((m, wide), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        dyb = [torch.empty((m, wide), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        s_in, s_out, s_comp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        ev_in, ev_comp, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
+
+        def e2e_step(_i):
+            for j, (kind, name, k, n) in enumerate(calls):
+                b = j % 2
+                dx = dxb[b].view(-1)[: m * k].view(m, k)
+                dy = dyb[b].view(-1)[: m * n].view(m, n)
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_comp[b])  # the Linear that last read this input buffer is done
+                    dx.copy_(hx[k], non_blocking=True)
+                    ev_in[b].record(s_in)
+                s_comp.wait_event(ev_in[b])
+                s_comp.wait_event(ev_out[b])  # the copy-out that last read this output buffer is done
+                runners[kind].forward(wdev[name][kind][0], dx, dy)
+                ev_comp[b].record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[b])
+                    hy[b].view(-1)[: m * n].view(m, n).copy_(dy, non_blocking=True)
+                    ev_out[b].record(s_out)
+
+        def e2e_region(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record(s_comp)
+            s_in.wait_event(a)
+            for i in range(iters):
+                e2e_step(i)
+            s_comp.wait_stream(s_out)
+            s_comp.wait_stream(s_in)
+            b.record(s_comp)
+            b.synchronize()
+            return a.elapsed_time(b)
+
+        e2e_region(1)
+        barrier()
+        e2e_steps = max(2, min(steps, 4))
+        e2e_ms = max_over_ranks([e2e_region(e2e_steps) / e2e_steps])[0]
+        barrier()
+        h2d = sum(2 * m * k for _, _, k, _ in calls)
+        d2h = sum(2 * m * n for _, _, _, n in calls)
+        e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "note": "bytes are this rank's; every rank moves its own rows, all ranks through the one host memory system"}
+        del hx, hy, dxb, dyb
+        torch.cuda.empty_cache()
+
+    # ---- FFN-up column split with its one all-gather (secondary scheme)
+    column = {}
+    if TOKENS % world == 0 and not args.no_column_split:
+        c0, nl = column_shard(n_up, world, rank)
+        for kind in KINDS:
+            w, t = wdev["ffn_up"][kind]
+            if kind == "w4a8":
+                w8 = torch.empty((nl, k_up), dtype=torch.int8, device="cuda")
+                sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(t[0][c0:c0 + nl].contiguous()), sfq.ptr(t[1].view(n_up, -1)[c0:c0 + nl].contiguous()),
+                                                       sfq.ptr(t[3]), sfq.ptr(w8), nl, k_up, 16, sfq.stream_ptr()))
+                weight = (w8, t[2][c0:c0 + nl].contiguous())
+            else:
+                weight = (t[0][c0:c0 + nl].contiguous(), t[1].view(n_up // 128, -1)[c0 // 128:(c0 + nl) // 128].contiguous().view(-1),
+                          w.global_scale)
+            entry = {}
+            for pipeline in (("overlap", "blocking") if world > 1 else ("blocking",)):
+                plan = ColumnSplitPlan(kind, m, k_up, nl, weight, world, pipeline=pipeline, rank=rank)
+                fwd = lambda _i, plan=plan: plan.forward(xs[k_up])  # noqa: E731
+                gat = lambda _i, plan=plan: plan.gather_only()  # noqa: E731
+                for i in range(2):
+                    fwd(i)
+                barrier()
+                t_all = time_region(torch, fwd, 5) / 5
+                barrier()
+                t_gather = time_region(torch, gat, 5) / 5 if world > 1 else 0.0
+                barrier()
+                t_all, t_gather = max_over_ranks([t_all, t_gather])
+                tf = 2.0 * TOKENS * n_up * k_up / (t_all * 1e-3) / 1e12
+                entry[pipeline] = {"ms": t_all, "tflops": tf, "collective_alone_ms": t_gather,
+                                   "gathered_bytes_per_gpu": plan.gathered_bytes}
+                del plan
+                torch.cuda.empty_cache()
+            token = next(r for r in table if r["linear"] == "ffn_up" and r["kind"] == kind)
+            best = min(entry, key=lambda p: entry[p]["ms"])
+            entry["best"] = best
+            entry["vs_token_sharding"] = entry[best]["tflops"] / token["tflops"]
+            # what the collective adds on top of quantizer + GEMMs (which cost about what token sharding's call costs)
+            entry["exposed_collective_ms"] = max(0.0, entry[best]["ms"] - token["ms"])
+            column[kind] = entry
+            del weight
+            torch.cuda.empty_cache()
+    status = sfq.device_status()
+
+    # ---- single-GPU extras: the reference's GPU path, configuration 4's block, the CPU baseline
+    gpu_ref = block = base = None
+    if world == 1 and rank == 0:
+        if not args.no_gpu_reference:
+            gpu_ref = gpu_reference5(torch, wdev, xs, m)
+            if isinstance(gpu_ref, dict):
+                for r in table:
+                    ref_ms = gpu_ref[r["linear"]][r["kind"]]
+                    r["reference_kernels_ms"] = ref_ms
+                    r["speedup_over_reference_kernels"] = ref_ms / r["ms"]
+        del xs, ys
+        torch.cuda.empty_cache()
+        if not args.no_block:
+            block = dit_block_ms(torch, sfq)
+        status = status or sfq.device_status()
+        if not args.no_cpu:
+            base = cpu_baseline5(np, torch, host, steps=2, warmup=1)
+
+    if rank == 0:
+        derived4 = PEAK_MULT["nvfp4"] * peaks["bf16_tflops"]
+        gemm_tf = 2.0 * m * n_up * k_up / (gemm_ms * 1e-3) / 1e12
+        cap_rows = profile_value("gemm_pair_kernel_nvfp4_ffn_up.md", "rows")
+        cap_bytes = profile_value("gemm_pair_kernel_nvfp4_ffn_up.md", "dram_bytes_per_launch")
+        traffic = int(cap_bytes * (m / cap_rows)) if cap_rows and cap_bytes else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4+int8", "data": "synthetic", "config": {"workload": WORKLOAD5, "seed": SEED5},
+            "detail": {"tokens": TOKENS, "rows_on_rank0": m, "linears_per_step": len(calls),
+                       "l2": "every operand of every Linear is larger than the 126 MB L2 (the smallest, one rank's activation at "
+                             "8 GPUs, is 143 MB), and six different Linears run between two uses of the same buffers",
+                       "parallelism": f"token-sharded x{world}, weights replicated, no collective on the data path",
+                       "timed_region_ms": ms_max},
+            "e2e": e2e, "gpu_launches": launches_per_step * steps, "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<nvfp4> (CTA pair, 256-wide tiles) at FFN-up, this rank's rows",
+                         "achieved": gemm_tf, "peak": derived4, "unit": "TFLOP/s", "frac": gemm_tf / derived4, "traffic": traffic,
+                         "ms_per_launch": gemm_ms, "frac_of_nominal_9000": gemm_tf / NOMINAL_TFLOPS["nvfp4"],
+                         "peak_note": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): MEASURED_PEAKS holds no fp4 "
+                                      "figure; the kernel is timed alone over 10 launches",
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in "
+                                         "profiles/gemm_pair_kernel_nvfp4_ffn_up.md, scaled by rows; algorithmic bytes "
+                                         f"{int(m * k_up * 0.5625 + n_up * k_up * 0.5625 + 2.0 * m * n_up)}"},
+            "linears": table,
+            "streaming": {"quantize_nvfp4_ffn_up_GBps": (2.0 * m * k_up + m * k_up / 2 + m * k_up / 16) / (quant_ms * 1e-3) / 1e9,
+                          "hbm_peak_GBps": peaks["hbm_gbs"], "peak_source": peaks["source"]},
+            "column_split": column or None, "dit_block": block, "gpu_reference": gpu_ref if not isinstance(gpu_ref, dict) else "see linears[*].reference_kernels_ms",
+            "device_status": status,
+        }
+        if base is not None:
+            line["cpu_baseline"] = base
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config5", action="store_true",
-                    help="run benchmark configuration 5 (M=111600 scaling sweep) on the ranks of this launch and exit")
+    ap.add_argument("--config2", action="store_true", help="run benchmark configuration 2 (W4A8 attention projection, M=4096, weak scaling) and exit")
     ap.add_argument("--config3", action="store_true", help="run benchmark configuration 3 (W6A8 FFN pair, M=32760) and exit")
     ap.add_argument("--block-stack", type=int, default=0, metavar="BLOCKS",
                     help="run benchmark configuration 4 (NVFP4 DiT block stack at 75600 tokens) with this many blocks and exit")
-    ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu) and exit: gemm_int8, "
-                    "gemm_nvfp4, quantize_int8, quantize_nvfp4")
+    ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu) and exit: gemm_int8, gemm_int8_c2, "
+                    "gemm_nvfp4, gemm_nvfp4_ffn_up, quantize_int8, quantize_int8_k13824, quantize_nvfp4, unpack_w4a8, attention")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--extra", action="store_true", help="also time the GEMMs at the other DiT shapes (1 GPU)")
+    ap.add_argument("--extra", action="store_true", help="with --config2: also time the GEMMs at the other DiT shapes (1 GPU)")
+    for flag in ("e2e", "column-split", "gpu-reference", "block", "cpu"):
+        ap.add_argument("--no-" + flag, action="store_true", help="leave this part of the default run out")
     args = ap.parse_args()
     if args.config3:
         run_config3()
-        return
-    if args.config5:
-        run_config5()
-        return
-    if args.case:
+    elif args.case:
         run_case(args.case)
-        return
-    if args.block_stack:
+    elif args.block_stack:
         run_block_stack(args.block_stack)
-        return
-    if args.impl == "reference":
+    elif args.config2:
+        run_reference_config2(args) if args.impl == "reference" else run_config2(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

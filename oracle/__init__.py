@@ -105,6 +105,7 @@ _sig(lib.orc_rmsnorm_spec_f32, None, V, V, V, V, V, C.c_int, C.c_int, C.c_float,
 _sig(lib.orc_matmul_nt, None, V, V, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_matmul_nt_fast, None, V, V, C.c_int, C.c_int, C.c_int, V)
 _sig(lib.orc_num_threads, C.c_int)
+_sig(lib.orc_set_num_threads, None, C.c_int)
 _sig(lib.orc_nvfp4_linear, None, V, C.c_int, V, V, C.c_float, C.c_int, C.c_int, V, C.c_int, V)
 _sig(lib.orc_nvfp4_linear_dequant, None, V, C.c_int, V, V, C.c_float, C.c_int, C.c_int, V, V)
 _sig(lib.orc_packed_int8_linear, None, V, C.c_int, V, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int,

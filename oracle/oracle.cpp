@@ -910,6 +910,16 @@ ORC_API void orc_matmul_nt_fast(const float* A, const float* B, int M, int N, in
     }
 }
 
+// Sets the OpenMP team size of the timed host path. A launcher such as torch.distributed.run exports
+// OMP_NUM_THREADS=1 to its workers; the CPU baseline must state, and use, the cores the box really has.
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -12,7 +12,9 @@ Order of operations of the reference's ``run_block`` (src/dit/transformer_execut
 
 Head-wise q/k RMSNorm and MM-RoPE sit between the projections and attention (QK-norm first, then RoPE; v untouched):
 one in-place pass per third of the fused projection, run when the weights carry q_norm / k_norm or `rope` is given.
-The FFN is the plain GELU form of the benchmark configuration (the reference's H3 block is SwiGLU).
+The FFN is the plain GELU form of the benchmark configuration by default; `ffn_form="swiglu"` runs the reference's H3
+form instead (src/dit/transformer_execution.cpp:433-441): fc1 is the fused [gate | up] weight with 2 * ffn rows and the
+SwiGLU epilogue writes silu(gate) * up, ffn columns wide, so the [rows, 2 * ffn] intermediate never exists.
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ from dataclasses import dataclass
 
 import torch
 
-from . import (ACT_GELU_TANH, ACT_NONE, F32, NVFP4_ACT_GEMM_FEED, Epilogue, Norm, check, lib, ptr, stream_ptr)
+from . import (ACT_GELU_TANH, ACT_NONE, ACT_SWIGLU, F32, NVFP4_ACT_GEMM_FEED, Epilogue, Norm, check, lib, ptr, stream_ptr)
 
 
 @dataclass
@@ -56,8 +58,10 @@ class BlockWeights:
 class Nvfp4Block:
     """Scratch and launch plumbing for blocks of one geometry."""
 
-    def __init__(self, rows: int, hidden: int, heads: int, ffn: int, device="cuda"):
-        self.rows, self.hidden, self.heads, self.ffn = rows, hidden, heads, ffn
+    def __init__(self, rows: int, hidden: int, heads: int, ffn: int, device="cuda", ffn_form: str = "gelu"):
+        if ffn_form not in ("gelu", "swiglu"):
+            raise ValueError("ffn_form must be 'gelu' or 'swiglu'")
+        self.rows, self.hidden, self.heads, self.ffn, self.ffn_form = rows, hidden, heads, ffn, ffn_form
         kmax = max(hidden, ffn)
         self.xq = torch.empty((rows, kmax // 2), dtype=torch.uint8, device=device)
         self.xs = torch.empty(lib.sfq_nvfp4_act_scale_bytes(rows, kmax), dtype=torch.uint8, device=device)
@@ -126,7 +130,12 @@ class Nvfp4Block:
             check(lib.sfq_add_gated(ptr(x), ptr(self.branch), ptr(mod["gate_msa"]), ptr(adaln_index), rows, hidden, stream_ptr()))
         n2 = Norm(ptr(w.norm2), ptr(mod["scale_mlp"]), ptr(mod["shift_mlp"]), ptr(adaln_index), eps)
         self._quantize(x, hidden, n2)
-        self._gemm(w.fc1, self.h, ACT_GELU_TANH)
+        if self.ffn_form == "swiglu":
+            if w.fc1.out_features != 2 * self.ffn:
+                raise ValueError("the SwiGLU form needs fc1 = [gate | up] with 2 * ffn rows")
+            self._gemm(w.fc1, self.h, ACT_SWIGLU)
+        else:
+            self._gemm(w.fc1, self.h, ACT_GELU_TANH)
         self._quantize(self.h, self.ffn, None)
         if self.fuse_residual:
             self._gemm(w.fc2, x, gate=mod["gate_mlp"], gate_index=adaln_index)

@@ -29,12 +29,13 @@ def _cpu_attention(qkv_bits, rows, heads, hidden):
     return oracle.to_bf16(out.astype(np.float32))
 
 
-@pytest.mark.parametrize("fuse_residual", [False, True])
-def test_block_matches_cpu_composition(fuse_residual):
+@pytest.mark.parametrize("fuse_residual,ffn_form", [(False, "gelu"), (True, "gelu"), (False, "swiglu")])
+def test_block_matches_cpu_composition(fuse_residual, ffn_form):
     rows, hidden, heads, ffn = 160, 256, 2, 512
     rng = np.random.default_rng(7)
+    fc1_rows = 2 * ffn if ffn_form == "swiglu" else ffn  # the reference's H3 block: fc1 = [gate | up]
     (cq, wq), (co, wo), (c1, w1), (c2, w2) = (_linear(3 * hidden, hidden, rng), _linear(hidden, hidden, rng),
-                                              _linear(ffn, hidden, rng), _linear(hidden, ffn, rng))
+                                              _linear(fc1_rows, hidden, rng), _linear(hidden, ffn, rng))
     norm1 = oracle.to_bf16(np.ones(hidden, np.float32))
     norm2 = oracle.to_bf16((1 + 0.05 * rng.standard_normal(hidden)).astype(np.float32))
     names = ["scale_msa", "shift_msa", "gate_msa", "scale_mlp", "shift_mlp", "gate_mlp"]
@@ -43,7 +44,7 @@ def test_block_matches_cpu_composition(fuse_residual):
     x = gaussian_bf16((rows, hidden), seed=8)
     weights = BlockWeights(wq, wo, w1, w2, bf16_tensor(norm1), bf16_tensor(norm2))
     mod_d = {n: dev(v) for n, v in mod_h.items()}
-    block = Nvfp4Block(rows, hidden, heads, ffn)
+    block = Nvfp4Block(rows, hidden, heads, ffn, ffn_form=ffn_form)
     block.fuse_residual = fuse_residual  # gated residuals as their own kernel, or inside the GEMM epilogues
     dx = bf16_tensor(x)
     block.forward(dx, weights, mod_d, dev(a))
@@ -60,7 +61,12 @@ def test_block_matches_cpu_composition(fuse_residual):
     x1 = x.copy()
     oracle.lib.orc_add_gated_bf16(x1.ctypes.data, branch.ctypes.data, mod_h["gate_msa"].ctypes.data, a.ctypes.data, rows, hidden)
     n2 = oracle.rmsnorm_bf16(x1, norm2, 1e-5, mod_h["scale_mlp"], mod_h["shift_mlp"], a)
-    h = oracle.nvfp4_linear(n2, c1[0], c1[1], c1[2], ffn, hidden, act=oracle.ACT_GELU_TANH)
+    if ffn_form == "swiglu":
+        fused = oracle.nvfp4_linear(n2, c1[0], c1[1], c1[2], 2 * ffn, hidden)
+        h = np.empty((rows, ffn), np.uint16)
+        oracle.lib.orc_swiglu_bf16(fused.ctypes.data, rows, ffn, h.ctypes.data)
+    else:
+        h = oracle.nvfp4_linear(n2, c1[0], c1[1], c1[2], ffn, hidden, act=oracle.ACT_GELU_TANH)
     y2 = oracle.nvfp4_linear(h, c2[0], c2[1], c2[2], hidden, ffn)
     oracle.lib.orc_add_gated_bf16(x1.ctypes.data, y2.ctypes.data, mod_h["gate_mlp"].ctypes.data, a.ctypes.data, rows, hidden)
     # bf16 attention on the device vs fp64 on the host moves a few fp4 codes downstream: a looser, whole-block bar

@@ -96,7 +96,13 @@ def test_config4_linears_nvfp4_full_token_count():
     runner = sfq.LinearRunner()
     runner.set_native(True)
     picks = _rows(M, 12, seed=4)
-    for name, n, k in (("out", H, H), ("fc1", F, H)):
+    xf = None
+    for name, n, k in (("out", H, H), ("fc1", F, H), ("qkv", 3 * H, H), ("fc2", H, F)):
+        if k == F and xf is None:  # fc2 reads an FFN-wide activation
+            del dx
+            torch.cuda.empty_cache()
+            xf = gaussian_bf16((M, F), seed=5)
+            x, dx = xf, bf16_tensor(xf)
         data, scale, g = pack_nvfp4((0.02 * rng.standard_normal((n, k))).astype(np.float32))
         keep = [dev(data), dev(scale)]
         w = sfq.new_weight(format=sfq.NVFP4, data=sfq.ptr(keep[0]), out_features=n, in_features=k,
@@ -108,3 +114,40 @@ def test_config4_linears_nvfp4_full_token_count():
         assert max_abs <= 2e-2 and rel_l2 <= 1e-3, (name, max_abs, rel_l2, corr)
         del y
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("kind", ["nvfp4", "w4a8"])
+@pytest.mark.parametrize("name,k,n", [("attn_proj", 5120, 5120), ("ffn_up", 5120, 13824), ("ffn_down", 13824, 5120)])
+def test_config5_linears_at_one_gpus_share_of_the_tokens(kind, name, k, n):
+    # the scaling sweep's Linears at the rows one of eight GPUs owns: 111600 / 8 = 13950 (not a multiple of any tile
+    # height), distributions of configs 1-2 (activations N(0,1) with 0.1 % outliers x20, weights N(0,0.02)), seed 4
+    from slopfab_b200.parallel import token_shard
+    M = token_shard(31 * 45 * 80, 8, 3)[1]
+    assert M == 13950
+    rng = np.random.default_rng(4)
+    wf = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    x = gaussian_bf16((M, k), seed=4, outliers=True)
+    dx = bf16_tensor(x)
+    picks = _rows(M, 16, seed=5)
+    runner = sfq.LinearRunner()
+    if kind == "nvfp4":
+        data, scale, g = pack_nvfp4(wf)
+        keep = [dev(data), dev(scale)]
+        w = sfq.new_weight(format=sfq.NVFP4, data=sfq.ptr(keep[0]), out_features=n, in_features=k, block_scale=sfq.ptr(keep[1]),
+                           global_scale=g)
+        runner.set_native(True)
+        y = runner.forward(w, dx)
+        assert sfq.device_status() == 0
+        want = oracle.nvfp4_linear(np.ascontiguousarray(x[picks]), data, scale, g, n, k)
+        max_abs, rel_l2, corr = oracle.compare_bf16(want, bits(y)[picks])
+        assert max_abs <= 2e-2 and rel_l2 <= 1e-3, (name, max_abs, rel_l2, corr)
+    else:
+        packed, s_rel, s_ch, book = pack_w4a8(wf)
+        w, keep = _int8_weight(sfq.W4A8, packed, s_rel, s_ch, book, None, 16, n, k)
+        y = runner.forward(w, dx)
+        assert sfq.device_status() == 0
+        want = oracle.packed_int8_linear(np.ascontiguousarray(x[picks]), packed.view(np.uint8), s_rel, s_ch, book, 4, 16, n, k)
+        got = bits(y)[picks]
+        assert np.array_equal(got, want), f"{name}: {int((got != want).sum())} of {want.size} sampled outputs differ"
+    # the last, partial row tile holds real rows only: nothing past row M - 1 was written
+    assert torch.isfinite(y.float()).all()

@@ -58,8 +58,9 @@ def _worker(rank, world, port, out):
         xe = gaussian_bf16((Me, K), seed=9)
         me = Me // world
         xl = bf16_tensor(np.ascontiguousarray(xe[rank * me:(rank + 1) * me]))
-        plan = ColumnSplitPlan("w4a8", me, K, cc, (w8[c0:c0 + cc].contiguous(), keep[2][c0:c0 + cc].contiguous()), world)
-        got = plan.forward(xl)
+        plans = {p: ColumnSplitPlan("w4a8", me, K, cc, (w8[c0:c0 + cc].contiguous(), keep[2][c0:c0 + cc].contiguous()), world, pipeline=p)
+                 for p in ("overlap", "blocking")}
+        got = plans["overlap"].forward(xl)
         q = torch.empty((Me, K), dtype=torch.int8, device="cuda")
         rs = torch.empty(Me, device="cuda")
         xa = bf16_tensor(xe)
@@ -69,12 +70,18 @@ def _worker(rank, world, port, out):
         sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(q), sfq.ptr(w8), C.byref(ep), sfq.ptr(want), Me, N, K, sfq.stream_ptr()))
         torch.cuda.synchronize()
         ok = ok and torch.equal(got.view(torch.int16), want[:, c0:c0 + cc].contiguous().view(torch.int16))
+        # both pipelines, and each a second time over its own buffers (the gather slots and events are reused)
+        for p in ("overlap", "blocking", "overlap"):
+            again = plans[p].forward(xl)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(again.view(torch.int16), want[:, c0:c0 + cc].contiguous().view(torch.int16))
         wf = (0.02 * np.random.default_rng(10).standard_normal((N, K))).astype(np.float32)
         data, scale, gs = pack_nvfp4(wf)
         dd, ds = dev(data), dev(scale)
         plan4 = ColumnSplitPlan("nvfp4", me, K, cc, (dd[c0:c0 + cc].contiguous(),
                                                      ds.view(N // 128, -1)[c0 // 128:(c0 + cc) // 128].contiguous().view(-1), gs), world)
         got4 = plan4.forward(xl)
+        got4 = plan4.forward(xl)  # second call: slots rewritten while the previous call's events are still around
         xq = torch.empty((Me, K // 2), dtype=torch.uint8, device="cuda")
         xs = torch.empty(sfq.lib.sfq_nvfp4_act_scale_bytes(Me, K), dtype=torch.uint8, device="cuda")
         sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(xa), None, sfq.ptr(xq), sfq.ptr(xs), None, Me, K,
