@@ -166,8 +166,13 @@ __device__ __forceinline__ void flush_chunk(const uint4 (&packed)[4], uint4* sta
           rp[h] = __floats2bfloat162_rn(__fmaf_rn(gg[2 * h], b.x, x.x), __fmaf_rn(gg[2 * h + 1], b.y, x.y));
         }
         val = res;
+        *out = val;
+      } else {
+        // A plain output tile is written once and not read again by this kernel: store it with the streaming (evict-first)
+        // policy, so that the gigabytes of y that pass through L2 do not push out the weight and activation slabs the
+        // other tiles are about to re-read (measured at 27900 x 5120 -> 13824: 618 MB of DRAM reads for 120 MB of operands).
+        __stcs(out, val);
       }
-      *out = val;
     }
   }
   __syncwarp();  // the block is reused by the next chunk

@@ -11,11 +11,11 @@
 //   * the absolute maximum runs on bf16x2 words (both rows per max.bf16x2);
 //   * the rotated values are quantized in the transposed layout; the int8 bytes of both rows go to shared memory as
 //     one 16-bit store per element and come back as two 16-byte rows, so the second float transpose disappears;
-//   * one block-wide barrier per row pair: every thread folds the per-warp maxima itself;
-//   * for K <= 5120 that barrier is split-phase (an mbarrier: a warp arrives when its maximum is written and only
-//     waits after it has rotated the NEXT row pair), so no warp idles while the slowest one finishes.
+//   * one block-wide barrier per row pair: every thread folds the per-warp maxima itself. (A split-phase form of that
+//     barrier -- an mbarrier a warp arrives on when its maximum is written and waits on only after it has rotated the
+//     NEXT row pair, 92 registers, two CTAs per SM -- was built and measured: 3.04 TB/s against 3.2 for this form at
+//     32768 x 5120, same bits. The kernel is bound by its instruction count, not by warps idling at the barrier.)
 #include "kernels.cuh"
-#include "ptx.cuh"
 #include "runtime.h"
 
 #include <algorithm>
@@ -216,155 +216,6 @@ quantize_int8_pairs_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restri
   }
 }
 
-// The same arithmetic, software-pipelined over row pairs: iteration i rotates pair i ("front": load, butterflies,
-// transposes, bf16 rounding, the warp's maximum, ARRIVE on the pair's barrier) and only then finishes pair i - 1
-// ("back": WAIT for that pair's barrier, fold the maxima, quantize, store). The barrier is an mbarrier with one
-// arrival per warp, so arriving never blocks and the wait finds the phase complete unless some warp is more than a
-// whole front stage behind. Three barriers and three sets of per-warp maxima rotate: a warp can write the maxima of
-// pair i + 3 only after every warp has arrived for pair i + 2, which each does after it has finished pair i.
-// The rotated bf16 pairs of the previous row pair stay in registers across the next pair's front stage, hence two
-// CTAs per SM instead of three.
-template <int MAXT>
-__global__ void __launch_bounds__(MAXT, 2)
-quantize_int8_pairs_pipelined_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ row_scale,
-                                     int rows, int dim, int* __restrict__ status) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nwarps = blockDim.x >> 5;
-  const int chunks = dim >> 4;
-  const bool active = tid < chunks;
-  f2* tile = reinterpret_cast<f2*>(smem) + (tid >> 4) * kGroupTile;  // this thread's group
-  uint8_t* bytes = smem + size_t(blockDim.x >> 4) * kGroupTile * 8 + (tid >> 4) * kGroupBytesOut;
-  uint8_t* tail = smem + size_t(blockDim.x >> 4) * (kGroupTile * 8 + kGroupBytesOut);  // 16-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);                                  // [3]
-  uint32_t* partial = reinterpret_cast<uint32_t*>(tail + 32);                          // [3][32]
-  const int T = tid & 15;
-  const int pairs = (rows + 1) >> 1;
-  if (tid == 0) {
-    for (int b = 0; b < 3; ++b) ptx::mbar_init(ptx::smem_u32(bars + b), uint32_t(nwarps));
-    ptx::fence_barrier_init();
-  }
-  __syncthreads();
-
-  auto load = [&](int pair, uint4 (&r)[4]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) r[i] = make_uint4(0, 0, 0, 0);
-    if (active && pair < pairs) {
-      const int r0 = 2 * pair;
-      const uint4* s0 = reinterpret_cast<const uint4*>(x + size_t(r0) * dim) + tid * 2;
-      r[0] = __ldg(s0);
-      r[1] = __ldg(s0 + 1);
-      if (r0 + 1 < rows) {
-        const uint4* s1 = reinterpret_cast<const uint4*>(x + size_t(r0 + 1) * dim) + tid * 2;
-        r[2] = __ldg(s1);
-        r[3] = __ldg(s1 + 1);
-      }
-    }
-  };
-  // front stage: raw bf16 of a row pair -> rotated, bf16-rounded pairs w[16] (transposed layout), arrival on `slot`
-  auto front = [&](const uint4 (&raw)[4], uint32_t (&w)[16], int slot) {
-    f2 v[16];
-    {
-      const uint32_t a[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
-      const uint32_t b[8] = {raw[2].x, raw[2].y, raw[2].z, raw[2].w, raw[3].x, raw[3].y, raw[3].z, raw[3].w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        v[2 * i] = pku(a[i] << 16, b[i] << 16);
-        v[2 * i + 1] = pku(a[i] & 0xFFFF0000u, b[i] & 0xFFFF0000u);
-      }
-    }
-    two_stages(v);
-#pragma unroll
-    for (int e = 0; e < 16; ++e) tile[17 * T + e] = v[e];
-    __syncwarp();
-#pragma unroll
-    for (int t = 0; t < 16; ++t) v[t] = tile[17 * t + T];  // v[t] = element 16 t + T of the group
-    __syncwarp();  // the tile is rewritten by the next pair's front stage
-    two_stages(v);
-    const f2 sixteenth = pk(0.0625f, 0.0625f);
-    uint32_t amax = 0;
-#pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      float lo, hi;
-      upk(mul2(v[t], sixteenth), lo, hi);
-      w[t] = to_bf16x2(lo, hi);
-      amax = max_bf16x2(amax, w[t] & 0x7FFF7FFFu);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = max_bf16x2(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-    if (lane == 0) {
-      partial[slot * 32 + warp] = amax;
-      ptx::mbar_arrive(ptx::smem_u32(bars + slot));  // release: the store above is visible to whoever sees the phase complete
-    }
-  };
-  // back stage: the row maxima once every warp has arrived, then quotient, integer rounding and the stores
-  auto back = [&](const uint32_t (&w)[16], int slot, uint32_t parity, int pair) {
-    const uint32_t bar = ptx::smem_u32(bars + slot);
-    bool done = ptx::mbar_try_wait(bar, parity);
-    for (int spin = 0; !done && spin < (1 << 24); ++spin) done = ptx::mbar_try_wait(bar, parity);
-    if (!done) atomicCAS(status, 0, 7);  // bounded: record it and go on (the output of this launch is then unspecified)
-    uint32_t m = 0;
-    for (int i = 0; i < nwarps; ++i) m = max_bf16x2(m, partial[slot * 32 + i]);
-    const float m0 = __uint_as_float(m << 16), m1 = __uint_as_float(m & 0xFFFF0000u);
-    const float scale0 = fmaxf(div127(m0), 1e-30f), scale1 = fmaxf(div127(m1), 1e-30f);
-    const int r0 = 2 * pair;
-    if (tid == 0) {
-      row_scale[r0] = scale0;
-      if (r0 + 1 < rows) row_scale[r0 + 1] = scale1;
-    }
-    const float d0 = __bfloat162float(__float2bfloat16(scale0)), d1 = __bfloat162float(__float2bfloat16(scale1));
-    const f2 rcp = pk(__frcp_rn(d0), __frcp_rn(d1));
-    const f2 negd = pk(-d0, -d1);
-#pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const f2 xv = pku(w[t] << 16, w[t] & 0xFFFF0000u);
-      const f2 a = mul2(xv, rcp);
-      const f2 qv = fma2(fma2(a, negd, xv), rcp, a);
-      float lo, hi;
-      upk(qv, lo, hi);
-      const uint32_t qb = to_bf16x2(lo, hi);  // the quotient is rounded to bf16 before the integer rounding
-      const int i0 = __float2int_rn(__uint_as_float(qb << 16));
-      const int i1 = __float2int_rn(__uint_as_float(qb & 0xFFFF0000u));
-      uint32_t two;  // byte 0 = row r, byte 1 = row r+1, both saturated to int8
-      asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(two) : "r"(i1), "r"(i0), "r"(0));
-      reinterpret_cast<uint16_t*>(bytes)[16 * t + T] = uint16_t(two);
-    }
-    __syncwarp();
-    if (active) {
-      const uint4 p0 = reinterpret_cast<const uint4*>(bytes)[2 * T], p1 = reinterpret_cast<const uint4*>(bytes)[2 * T + 1];
-      uint4 o0, o1;
-      o0.x = __byte_perm(p0.x, p0.y, 0x6420), o1.x = __byte_perm(p0.x, p0.y, 0x7531);
-      o0.y = __byte_perm(p0.z, p0.w, 0x6420), o1.y = __byte_perm(p0.z, p0.w, 0x7531);
-      o0.z = __byte_perm(p1.x, p1.y, 0x6420), o1.z = __byte_perm(p1.x, p1.y, 0x7531);
-      o0.w = __byte_perm(p1.z, p1.w, 0x6420), o1.w = __byte_perm(p1.z, p1.w, 0x7531);
-      reinterpret_cast<uint4*>(q + size_t(r0) * dim)[tid] = o0;
-      if (r0 + 1 < rows) reinterpret_cast<uint4*>(q + size_t(r0 + 1) * dim)[tid] = o1;
-    }
-    __syncwarp();  // the byte block is rewritten by the next back stage
-  };
-
-  int pair = blockIdx.x;
-  if (pair >= pairs) return;  // the same verdict in every thread of the CTA
-  uint4 cur[4], nxt[4];
-  load(pair, cur);
-  uint32_t w_prev[16];
-  int prev_pair = -1, slot = 0, prev_slot = 0;
-  uint32_t parity = 0, prev_parity = 0;  // parity of the phase the current use of `slot` completes
-  for (; pair < pairs; pair += gridDim.x) {
-    load(pair + gridDim.x, nxt);
-    uint32_t w[16];
-    front(cur, w, slot);
-    if (prev_pair >= 0) back(w_prev, prev_slot, prev_parity, prev_pair);
-#pragma unroll
-    for (int t = 0; t < 16; ++t) w_prev[t] = w[t];
-    prev_pair = pair, prev_slot = slot, prev_parity = parity;
-    if (++slot == 3) slot = 0, parity ^= 1;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
-  }
-  back(w_prev, prev_slot, prev_parity, prev_pair);
-}
-
 // Wide rows (6144 < K <= 16384): the same arithmetic with NC chunks of 16 elements per thread. A thread rotates its
 // chunks one after the other, keeps the rotated bf16 pairs of all of them (16 words per chunk), and quantizes them
 // after the single block-wide maximum. Chunk k of thread t is chunk k * blockDim.x + t of the row, so a rotation
@@ -502,19 +353,6 @@ void launch_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows,
   if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
 }
 
-template <int MAXT>
-void launch_pairs_pipelined(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, int threads, cudaStream_t stream) {
-  const size_t smem = size_t(threads / 16) * (kGroupTile * 8 + kGroupBytesOut) + 32 + 3 * 32 * sizeof(uint32_t);
-  reserve_dynamic_smem(reinterpret_cast<const void*>(&quantize_int8_pairs_pipelined_kernel<MAXT>), smem, "quantize_int8_token");
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_int8_pairs_pipelined_kernel<MAXT>, threads, smem) != cudaSuccess || per_sm < 1)
-    per_sm = 1;
-  const int grid = std::min((rows + 1) / 2, per_sm * device_sm_count());
-  quantize_int8_pairs_pipelined_kernel<MAXT><<<grid, threads, smem, stream>>>(x, q, row_scale, rows, dim, device_status_word());
-  const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) throw std::runtime_error(std::string("quantize_int8_token: ") + cudaGetErrorString(e));
-}
-
 }  // namespace
 
 bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale, int rows, int dim, cudaStream_t stream) {
@@ -534,7 +372,7 @@ bool quantize_int8_rot_pairs(const __nv_bfloat16* x, int8_t* q, float* row_scale
   }
   const int threads = ((dim / 16 + 31) / 32) * 32;
   if (threads <= 320)
-    launch_pairs_pipelined<320>(x, q, row_scale, rows, dim, threads, stream);
+    launch_pairs<320, 3>(x, q, row_scale, rows, dim, threads, stream);
   else
     launch_pairs<384, 2>(x, q, row_scale, rows, dim, threads, stream);
   return true;
