@@ -97,17 +97,47 @@ def make_inputs(np, rows, seed, rank=0):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs: NVML from a thread of this
+    process every few milliseconds (a short multi-GPU step lasts tens of milliseconds), `nvidia-smi` as the fallback.
+    Reading only: no setting of the GPU is touched."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index: int, period_ms: int = 100):
+    def __init__(self, index: int, period_ms: int = 5):
         self.index, self.rows, self.proc, self.period_ms = index, [], None, period_ms
+        self.stop, self.thread, self.source = threading.Event(), None, None
+
+    def _nvml_loop(self, nv, handle, mx):
+        bits = [nv.nvmlClocksThrottleReasonHwSlowdown, nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                nv.nvmlClocksThrottleReasonSwThermalSlowdown, nv.nvmlClocksThrottleReasonSwPowerCap]
+        while not self.stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.rows.append([str(mhz), str(mx)] + ["Active" if reasons & b else "Not Active" for b in bits])
+            except Exception:  # noqa: BLE001  (a failed sample is skipped, not fatal)
+                pass
+            self.stop.wait(self.period_ms / 1e3)
 
     def __enter__(self):
         try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[self.index]) if visible and all(v.strip().isdigit() for v in visible.split(",")) else self.index
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            mx = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle, mx), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:  # noqa: BLE001
+            self.source = "nvidia-smi"
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
+                                          "--format=csv,noheader,nounits", "-lms", str(max(self.period_ms, 20))],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -120,28 +150,30 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        elif self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
         mhz, mx, reasons = [], 0, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in list(self.rows):
             try:
                 mhz.append(float(r[0]))
                 mx = max(mx, float(r[1]))
             except (ValueError, IndexError):
                 continue
-            for name, v in zip(names, r[2:6]):
+            for name, v in zip(self.NAMES, r[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         busy = [m for m in mhz if m >= 0.5 * mx] or mhz
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(mhz)}
+                "reasons": sorted(reasons), "samples": len(mhz), "source": self.source}
 
 
 def cpu_baseline(np, data, steps=1, warmup=0):
@@ -868,7 +900,7 @@ def run_ours(args):
     for i in range(warmup):
         step(i)
     barrier()
-    with ClockSampler(local, period_ms=50) as clocks:
+    with ClockSampler(local) as clocks:
         barrier()
         ms = time_region(torch, step, steps)
         barrier()

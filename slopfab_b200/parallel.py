@@ -105,47 +105,40 @@ def column_split_w4a8_forward(x_local: torch.Tensor, w8_cols: torch.Tensor, col_
     return column_split_int8_forward(quantize, gemm, x_local.contiguous(), group)
 
 
-def exchange_steps(world: int, rank: int) -> list[tuple[int, int]]:
-    """The all-gather of one block per rank as world - 1 pairwise steps: in step s (1-based) this rank sends its own
-    block to rank + s and receives the block of rank - s (mod world). Every rank sends and receives exactly one block
-    per step, so all links are busy in every step, and after step s a rank holds the blocks of s + 1 sources."""
-    if world <= 0 or not 0 <= rank < world:
-        raise ValueError("exchange_steps: bad arguments")
-    return [((rank + s) % world, (rank - s) % world) for s in range(1, world)]
-
-
-def gather_blocks_stepwise(blocks: list[torch.Tensor], rank: int, group=None, on_block=None) -> None:
-    """Fills blocks[src] for every src != rank from the rank that owns it (blocks[rank] is this rank's own, already
-    written), one exchange_steps step at a time. on_block(src) is called after the step that delivered blocks[src] has
-    been waited for: on CUDA tensors that wait only orders the CURRENT stream behind the transfer (the host runs
-    on), so the caller can record an event there and release that block's consumer while later steps are still moving."""
-    world = len(blocks)
-    for dst, src in exchange_steps(world, rank):
-        ops = [dist.P2POp(dist.isend, blocks[rank], dst, group), dist.P2POp(dist.irecv, blocks[src], src, group)]
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-        if on_block is not None:
-            on_block(src)
+def row_chunks(rows: int, chunks: int, multiple: int = 128) -> list[tuple[int, int]]:
+    """(first row, row count) of at most `chunks` contiguous pieces of `rows` rows; every piece starts on a multiple of
+    `multiple` rows (128 keeps the fp4 scale tiles of a piece whole), the last one takes the ragged end."""
+    if rows < 0 or chunks <= 0 or multiple <= 0:
+        raise ValueError("row_chunks: bad arguments")
+    units = (rows + multiple - 1) // multiple
+    pieces = []
+    for c in range(min(chunks, max(units, 1))):
+        u0, uc = token_shard(units, min(chunks, max(units, 1)), c)
+        r0, r1 = u0 * multiple, min(rows, (u0 + uc) * multiple)
+        if r1 > r0:
+            pieces.append((r0, r1 - r0))
+    return pieces
 
 
 class ColumnSplitPlan:
     """FFN-up column split with preallocated buffers and equal token counts per rank (the benchmark's case).
 
-    Every rank quantizes its own `m` token rows into one block [quantized rows | their scales]; the blocks of all ranks
-    are brought into ordinary local memory (the one all-gather of the scheme) and the local weight columns are
-    multiplied block by block, one GEMM launch per source rank, so no block waits for a repack. Kinds: "w4a8" (int8 rows
-    + fp32 row scales; `weight` = (int8 [n_local, K], col_scale fp32 [n_local])) and "nvfp4" (fp4 rows + 128x4-tiled
-    e4m3 scales; `weight` = (u8 [n_local, K/2], tiled scales, global_scale)).
+    Every rank quantizes its own `m` token rows into blocks [quantized rows | their scales]; the blocks of all ranks are
+    brought into ordinary local memory by NCCL all-gather (the one collective of the scheme) and the local weight columns
+    are multiplied block by block, one GEMM launch per source rank and row chunk, so no block waits for a repack. Kinds:
+    "w4a8" (int8 rows + fp32 row scales; `weight` = (int8 [n_local, K], col_scale fp32 [n_local])) and "nvfp4" (fp4
+    rows + 128x4-tiled e4m3 scales; `weight` = (u8 [n_local, K/2], tiled scales, global_scale)).
 
-    pipeline="overlap" (default): the rank's own block is multiplied at once, while a communication stream runs the
-      gather as exchange_steps' pairwise steps; one event per delivered block releases that block's GEMM, so the
-      transfers hide behind the GEMMs of the blocks that are already here.
-    pipeline="blocking": one all_gather_into_tensor, then the GEMMs (the form measured first; kept for comparison).
-    Kernels only ever read local memory: a peer's block is multiplied after it has landed in `recv`.
+    pipeline="overlap" (default): the rows are cut into `chunks` pieces (128-row aligned). The rank's own pieces are
+      multiplied at once, straight from the send buffers, while a communication stream gathers piece after piece; one
+      event per gathered piece releases the GEMMs of the peers' rows of that piece, so the later pieces travel behind
+      the GEMMs of the earlier ones.
+    pipeline="blocking": one all_gather_into_tensor of everything, then the GEMMs.
+    Kernels only ever read local memory: a peer's rows are multiplied after they have landed in `recv`.
     """
 
     def __init__(self, kind: str, m: int, k: int, n_local: int, weight, world: int, device="cuda", activation: int = 0,
-                 pipeline: str = "overlap", rank: int | None = None):
+                 pipeline: str = "overlap", rank: int | None = None, chunks: int = 2):
         from . import lib
 
         if kind not in ("w4a8", "nvfp4"):
@@ -155,83 +148,92 @@ class ColumnSplitPlan:
         self.kind, self.m, self.k, self.n, self.world, self.weight, self.activation = kind, m, k, n_local, world, weight, activation
         self.pipeline = pipeline
         self.rank = rank if rank is not None else (dist.get_rank() if world > 1 else 0)
-        if kind == "w4a8":
-            self.q_bytes, self.s_bytes = m * k, 4 * m
-        else:
-            self.q_bytes, self.s_bytes = m * k // 2, lib.sfq_nvfp4_act_scale_bytes(m, k)
-        self.q_bytes_padded = (self.q_bytes + 255) // 256 * 256
-        self.block = self.q_bytes_padded + (self.s_bytes + 255) // 256 * 256
-        self.send = torch.zeros(self.block, dtype=torch.uint8, device=device)
-        self.recv = torch.zeros(world * self.block, dtype=torch.uint8, device=device)
-        self.blocks = [self.recv[r * self.block:(r + 1) * self.block] for r in range(world)]
+        self.pieces = row_chunks(m, chunks if (pipeline == "overlap" and world > 1) else 1)
+        pad = lambda b: (b + 255) // 256 * 256  # noqa: E731
+        self.q_pad, self.sub = [], []
+        for _, rows in self.pieces:
+            q = rows * k if kind == "w4a8" else rows * k // 2
+            sc = 4 * rows if kind == "w4a8" else lib.sfq_nvfp4_act_scale_bytes(rows, k)
+            self.q_pad.append(pad(q))
+            self.sub.append(pad(q) + pad(sc))
+        self.send = [torch.zeros(b, dtype=torch.uint8, device=device) for b in self.sub]
+        self.recv = [torch.zeros(world * b, dtype=torch.uint8, device=device) for b in self.sub]
         self.y = torch.empty((world * m, n_local), dtype=torch.bfloat16, device=device)
-        self.comm_stream = torch.cuda.Stream(device=device) if (world > 1 and pipeline == "overlap") else None
-        self.ev_quantized = torch.cuda.Event() if self.comm_stream is not None else None
-        self.ev_block = [torch.cuda.Event() for _ in range(world)] if self.comm_stream is not None else None
-        self.gathered_bytes = self.block * (world - 1)
+        overlap = world > 1 and pipeline == "overlap"
+        self.comm_stream = torch.cuda.Stream(device=device) if overlap else None
+        self.ev_quantized = torch.cuda.Event() if overlap else None
+        self.ev_piece = [torch.cuda.Event() for _ in self.pieces] if overlap else None
+        self.gathered_bytes = sum(self.sub) * (world - 1)
 
-    def _quantize(self, x_local, q_ptr, s_ptr):
+    def _quantize(self, x_local, c):
         from . import NVFP4_ACT_GEMM_FEED, check, lib, ptr, stream_ptr
 
+        r0, rows = self.pieces[c]
+        x_ptr = ptr(x_local) + r0 * self.k * 2
+        q_ptr = ptr(self.send[c])
+        s_ptr = q_ptr + self.q_pad[c]
         if self.kind == "w4a8":
-            check(lib.sfq_quantize_int8_token(ptr(x_local), None, q_ptr, s_ptr, None, self.m, self.k, 1, stream_ptr()))
+            check(lib.sfq_quantize_int8_token(x_ptr, None, q_ptr, s_ptr, None, rows, self.k, 1, stream_ptr()))
         else:
-            check(lib.sfq_quantize_nvfp4_block(ptr(x_local), None, q_ptr, s_ptr, None, self.m, self.k, NVFP4_ACT_GEMM_FEED, stream_ptr()))
+            check(lib.sfq_quantize_nvfp4_block(x_ptr, None, q_ptr, s_ptr, None, rows, self.k, NVFP4_ACT_GEMM_FEED, stream_ptr()))
 
-    def _gemm_block(self, base: int, r: int):
+    def _gemm(self, qb: int, c: int, src: int):
+        """y[rows of piece c of source rank src, :] from the quantized block at device address qb."""
         import ctypes as C
 
         from . import F32, Epilogue, check, lib, ptr, stream_ptr
 
-        m, k, n = self.m, self.k, self.n
-        qb = base + r * self.block
-        sb = qb + self.q_bytes_padded
-        yb = ptr(self.y) + r * m * n * 2
+        r0, rows = self.pieces[c]
+        k, n = self.k, self.n
+        sb = qb + self.q_pad[c]
+        yb = ptr(self.y) + (src * self.m + r0) * n * 2
         if self.kind == "w4a8":
             w8, col_scale = self.weight
             ep = Epilogue(sb, ptr(col_scale), 1.0, None, F32, self.activation)
-            check(lib.sfq_gemm_int8(qb, ptr(w8), C.byref(ep), yb, m, n, k, stream_ptr()))
+            check(lib.sfq_gemm_int8(qb, ptr(w8), C.byref(ep), yb, rows, n, k, stream_ptr()))
         else:
             data, scale, g = self.weight
             ep = Epilogue(None, None, g, None, F32, self.activation)
-            check(lib.sfq_gemm_nvfp4(qb, sb, ptr(data), ptr(scale), C.byref(ep), yb, m, n, k, stream_ptr()))
+            check(lib.sfq_gemm_nvfp4(qb, sb, ptr(data), ptr(scale), C.byref(ep), yb, rows, n, k, stream_ptr()))
 
     def gather_only(self, group=None) -> None:
         """The collective of forward() alone, on whatever the buffers hold (for timing it)."""
         if self.world == 1:
             return
-        if self.pipeline == "blocking":
-            dist.all_gather_into_tensor(self.recv, self.send, group=group)
-        else:
-            gather_blocks_stepwise(self.blocks, self.rank, group)
+        for c in range(len(self.pieces)):
+            dist.all_gather_into_tensor(self.recv[c], self.send[c], group=group)
 
     def forward(self, x_local: torch.Tensor, group=None) -> torch.Tensor:
         """x_local bf16 [m, K] -> bf16 [world * m, n_local]: this rank's columns for all tokens."""
         from . import ptr
 
-        if self.world == 1 or self.pipeline == "blocking":
-            q_ptr = ptr(self.send)
-            self._quantize(x_local, q_ptr, q_ptr + self.q_bytes_padded)
-            if self.world > 1:
-                dist.all_gather_into_tensor(self.recv, self.send, group=group)  # the one collective
-                base = ptr(self.recv)
-            else:
-                base = ptr(self.send)
-            for r in range(self.world):
-                self._gemm_block(base, r)
+        pieces = range(len(self.pieces))
+        for c in pieces:
+            self._quantize(x_local, c)
+        if self.world == 1:
+            for c in pieces:
+                self._gemm(ptr(self.send[c]), c, 0)
             return self.y
-        # ---- overlap: own block first, peers' blocks as they land
+        if self.pipeline == "blocking":
+            for c in pieces:
+                dist.all_gather_into_tensor(self.recv[c], self.send[c], group=group)  # the one collective (one piece)
+            for src in range(self.world):
+                for c in pieces:
+                    self._gemm(ptr(self.recv[c]) + src * self.sub[c], c, src)
+            return self.y
+        # ---- overlap: own rows first, the peers' rows piece by piece as they land
         compute = torch.cuda.current_stream()
-        base = ptr(self.recv)
-        q_ptr = base + self.rank * self.block
-        self._quantize(x_local, q_ptr, q_ptr + self.q_bytes_padded)  # straight into this rank's slot of the gather
         self.ev_quantized.record(compute)  # also behind every GEMM of the previous call: their blocks may be overwritten
-        self._gemm_block(base, self.rank)
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(self.ev_quantized)
-            gather_blocks_stepwise(self.blocks, self.rank, group, on_block=lambda src: self.ev_block[src].record(self.comm_stream))
-        for _, src in exchange_steps(self.world, self.rank):
-            compute.wait_event(self.ev_block[src])
-            self._gemm_block(base, src)
-        # the last event also covers this rank's last send: the next call may rewrite its slot
+            for c in pieces:
+                dist.all_gather_into_tensor(self.recv[c], self.send[c], group=group)
+                self.ev_piece[c].record(self.comm_stream)
+        for c in pieces:
+            self._gemm(ptr(self.send[c]), c, self.rank)
+        for c in pieces:
+            compute.wait_event(self.ev_piece[c])  # the last one also says the send buffers may be rewritten
+            for src in range(self.world):
+                if src != self.rank:
+                    self._gemm(ptr(self.recv[c]) + src * self.sub[c], c, src)
         return self.y

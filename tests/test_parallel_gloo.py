@@ -9,8 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import oracle
-from slopfab_b200.parallel import (all_gather_rows, column_shard, column_split_int8_forward, exchange_steps,
-                                   gather_blocks_stepwise, token_shard)
+from slopfab_b200.parallel import all_gather_rows, column_shard, column_split_int8_forward, row_chunks, token_shard
 
 
 def test_shard_arithmetic():
@@ -25,54 +24,14 @@ def test_shard_arithmetic():
     assert sum(c for _, c in cols) == 13824 and all(s % 128 == 0 and c % 128 == 0 for s, c in cols)
 
 
-def test_exchange_steps_cover_every_source_once_and_pair_up():
-    for world in (1, 2, 3, 4, 8):
-        for rank in range(world):
-            steps = exchange_steps(world, rank)
-            assert sorted(src for _, src in steps) == [r for r in range(world) if r != rank]
-            for i, (dst, _) in enumerate(steps):
-                assert exchange_steps(world, dst)[i][1] == rank  # whoever I send to in step i receives from me in step i
-
-
-def _gather_worker(rank, world, port, out):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
-    try:
-        blocks = [torch.full((1000,), 255, dtype=torch.uint8) for _ in range(world)]
-        blocks[rank][:] = torch.arange(1000, dtype=torch.int64).remainder(200).to(torch.uint8) + rank
-        order = []
-        gather_blocks_stepwise(blocks, rank, on_block=order.append)
-        ok = order == [src for _, src in exchange_steps(world, rank)]
-        for r in range(world):
-            ok = ok and bool((blocks[r] == torch.arange(1000, dtype=torch.int64).remainder(200).to(torch.uint8) + r).all())
-        flag = torch.tensor([1 if ok else 0])
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if rank == 0:
-            out.put(bool(flag.item()))
-    finally:
-        dist.destroy_process_group()
-
-
-def test_stepwise_gather_world3():
-    ctx = mp.get_context("spawn")
-    out = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_gather_worker, args=(r, 3, port, out)) for r in range(3)]
-    for p in procs:
-        p.start()
-    try:
-        for p in procs:
-            p.join(timeout=120)
-    finally:
-        for p in procs:
-            if p.is_alive():
-                p.terminate()
-                p.join(timeout=10)
-            if p.is_alive():
-                p.kill()
-                p.join()
-    assert [p.exitcode for p in procs] == [0, 0, 0]
-    assert out.get(timeout=5) is True
+def test_row_chunks_are_aligned_and_cover_the_rows():
+    for rows in (1, 127, 128, 129, 1000, 13950, 55800):
+        for chunks in (1, 2, 3, 4):
+            pieces = row_chunks(rows, chunks)
+            assert pieces[0][0] == 0 and sum(c for _, c in pieces) == rows and len(pieces) <= chunks
+            assert all(pieces[i][0] + pieces[i][1] == pieces[i + 1][0] for i in range(len(pieces) - 1))
+            assert all(r0 % 128 == 0 for r0, _ in pieces)
+    assert row_chunks(13950, 2) == [(0, 7040), (7040, 6910)]
 
 
 def _free_port():
