@@ -4,16 +4,19 @@
 // (include/slopfab/cuda/attention.cuh:176-196): q, k, v are [seq, heads * 128] row-major bf16, exactly the thirds of the
 // fused QKV projection; queries may be a compact chunk of the sequence; no mask exists anywhere in the model.
 //
-// One CTA owns 128 queries of one head and walks the keys in tiles of 128 with an online softmax:
-//   warp 0      TMA producer: Q once, then a two-stage ring of K tiles [128 keys x 128 d] and V^T tiles
+// One CTA owns TWO tiles of 128 queries of one head and walks the keys in tiles of 128 with an online softmax, so that the
+// softmax of one query tile runs while the tensor pipe works on the other tile's products:
+//   warp 0      TMA producer: both Q tiles once, then a two-stage ring of K tiles [128 keys x 128 d] and V^T tiles
 //               [128 d x 128 keys]; V is transposed once per call by transpose_v_kernel so that both products are
 //               K-major x K-major, the operand form the GEMM kernels already use
-//   warp 1      issues S = Q K^T (8 MMAs 128x128x16 into one of two S buffers in TMEM) one tile AHEAD of
-//               O += P V^T (8 MMAs into the O accumulator in TMEM)
-//   warps 2-5   softmax, one query row per thread: S from TMEM, running maximum and sum, P = exp2(s - m) as bf16 into
-//               shared memory in the swizzled operand layout, and - only when a row's maximum has grown by more than
-//               2^8 since the accumulator was last scaled - a rescale of O in TMEM. A stale maximum changes nothing
-//               in exact arithmetic (numerator and denominator carry the same factor) and bounds every p by 2^8.
+//   warp 1      issues, per key tile j: O0 += P0(j) V(j), S0 = Q0 K(j+1)^T, O1 += P1(j) V(j), S1 = Q1 K(j+1)^T (8 MMAs
+//               128x128x16 each). S and O of both query tiles live in TMEM (4 x 128 columns); P is read by the second
+//               product straight from TMEM, where it overwrites the first 64 columns of the scores it was computed from
+//   warps 2-5   softmax of query tile 0, warps 6-9 of query tile 1, one query row per thread with all 128 keys of the
+//               tile: S from TMEM, running maximum and sum, P = exp2(s - m) as bf16 pairs back into TMEM, and - only
+//               when a row's maximum has grown by more than 2^8 since the accumulator was last scaled - a rescale of
+//               O in TMEM. A stale maximum changes nothing in exact arithmetic (numerator and denominator carry the
+//               same factor) and bounds every p by 2^8.
 // Every wait is bounded; a wait that runs out stores a code in the status word and the CTA leaves.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -34,20 +37,18 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kTile = 128;             // queries per CTA, keys per step, head_dim
+constexpr int kTile = 128;             // queries per query tile (two per CTA), keys per step, head_dim
 constexpr int kSlab = kTile * 128;     // 128 rows x 128 bytes: 64 bf16 columns of a tile
 constexpr int kTileBytes = 2 * kSlab;  // [128 x 128] bf16
 constexpr int kAttnThreads = 320;  // producer, MMA issuer, eight softmax warps
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnShared {
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done, pair[4];
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   volatile int abort;
-  float row_max[2][2][kTile];  // [tile parity][half][row]: what the two halves of a row exchange
-  float row_sum[2][kTile];
 };
-constexpr int kAttnSmem = 1024 /* alignment slack */ + 6 * kTileBytes /* Q, K x2, V^T x2, P */ + 4096;
+constexpr int kAttnSmem = 1024 /* alignment slack */ + 6 * kTileBytes /* Q x2, K x2, V^T x2 */ + 1024;
 
 struct AttnArgs {
   __nv_bfloat16* out;
@@ -84,14 +85,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                      const __grid_constant__ CUtensorMap map_vt, const AttnArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = smem;
-  uint8_t* k_s = smem + kTileBytes;       // two stages
-  uint8_t* v_s = smem + 3 * kTileBytes;   // two stages
-  uint8_t* p_s = smem + 5 * kTileBytes;
+  uint8_t* q_s = smem;                    // two query tiles
+  uint8_t* k_s = smem + 2 * kTileBytes;   // two stages
+  uint8_t* v_s = smem + 4 * kTileBytes;   // two stages
   AttnShared* sh = reinterpret_cast<AttnShared*>(smem + 6 * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * kTile;
+  const int q0 = blockIdx.x * (2 * kTile);
   const int head = blockIdx.y;
   const int kv_head = head / g.group;
   const int tiles = (g.seq_kv + kTile - 1) / kTile;
@@ -103,12 +103,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       mbar_init(smem_u32(&sh->k_empty[i]), 1);
       mbar_init(smem_u32(&sh->v_full[i]), 1);
       mbar_init(smem_u32(&sh->v_empty[i]), 1);
-      mbar_init(smem_u32(&sh->s_full[i]), 1);
-      mbar_init(smem_u32(&sh->s_empty[i]), 8);
+      mbar_init(smem_u32(&sh->s_full[i]), 1);   // per query tile: the scores of the current key tile are in TMEM
+      mbar_init(smem_u32(&sh->p_full[i]), 4);   // per query tile: its four softmax warps have written P (and rescaled O)
+      mbar_init(smem_u32(&sh->pv_done[i]), 1);  // per query tile: O += P V of the current key tile has completed
     }
-    mbar_init(smem_u32(&sh->p_full), 8);
-    mbar_init(smem_u32(&sh->pv_done), 1);
-    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sh->pair[i]), 64);
     sh->abort = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -122,15 +120,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem = sh->tmem_base;
-  const uint32_t tmem_o = tmem + 256;
+  const uint32_t tmem = sh->tmem_base;  // columns: S/P of tile 0 [0,128), of tile 1 [128,256), O of tile 0 [256,384), of tile 1 [384,512)
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(smem_u32(&sh->q_full), kTileBytes);
-      tma_load_2d(smem_u32(q_s), &map_q, head * 256, q0, smem_u32(&sh->q_full));
-      tma_load_2d(smem_u32(q_s + kSlab), &map_q, head * 256 + 128, q0, smem_u32(&sh->q_full));
+      mbar_arrive_expect_tx(smem_u32(&sh->q_full), 2 * kTileBytes);
+      for (int t = 0; t < 2; ++t) {
+        tma_load_2d(smem_u32(q_s + t * kTileBytes), &map_q, head * 256, q0 + t * kTile, smem_u32(&sh->q_full));
+        tma_load_2d(smem_u32(q_s + t * kTileBytes + kSlab), &map_q, head * 256 + 128, q0 + t * kTile, smem_u32(&sh->q_full));
+      }
       for (int j = 0; j < tiles; ++j) {
         const int st = j & 1;
         const uint32_t ph = ((j >> 1) & 1) ^ 1;
@@ -147,152 +146,141 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (converged warp, one elected lane issues)
+    // Issue order per key tile j: O0 += P0(j) V(j); S0 = Q0 K(j+1)^T; O1 += P1(j) V(j); S1 = Q1 K(j+1)^T. The tensor pipe
+    // executes what one thread issues in order, so S_t(j+1) overwrites the columns P_t(j) lived in only after the
+    // product that read them, and a completed S_t(j+1) also says that O_t holds the sum up to tile j.
     constexpr uint32_t idesc = idesc_bf16(kTile, kTile);
     const uint32_t full_mask = 0xffffffffu;
     bool ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->q_full), 0, sh, g.status, 13));
-    auto issue_s = [&](int j) {  // S[j & 1] = Q K_j^T
+    auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
       const int st = j & 1;
       if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14))) return false;
-      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->s_empty[st]), ((j >> 1) & 1) ^ 1, sh, g.status, 15))) return false;
       tc_fence_after_sync();
       if (elect_one()) {
 #pragma unroll
         for (int kb = 0; kb < 8; ++kb) {
           const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
-          mma_f16(tmem + st * kTile, smem_desc_sw128(smem_u32(q_s) + off), smem_desc_sw128(smem_u32(k_s + st * kTileBytes) + off), idesc,
-                  kb ? 1u : 0u);
+          mma_f16(tmem + t * kTile, smem_desc_sw128(smem_u32(q_s + t * kTileBytes) + off), smem_desc_sw128(smem_u32(k_s + st * kTileBytes) + off),
+                  idesc, kb ? 1u : 0u);
         }
-        tc_commit(smem_u32(&sh->k_empty[st]));
-        tc_commit(smem_u32(&sh->s_full[st]));
+        tc_commit(smem_u32(&sh->s_full[t]));
+        if (t == 1) tc_commit(smem_u32(&sh->k_empty[st]));  // both query tiles have read this K tile
       }
       __syncwarp();
       return true;
     };
-    if (ok) ok = issue_s(0);
-    for (int j = 0; j < tiles && ok; ++j) {
-      if (j + 1 < tiles && !(ok = issue_s(j + 1))) break;
+    auto issue_pv = [&](int t, int j) {  // O_t += P_t V_j: A = P_t in tensor memory [queries x keys], B = V^T [d x keys]
       const int st = j & 1;
-      if (!(ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16)))) break;
-      if (!(ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->p_full), j & 1, sh, g.status, 17)))) break;
+      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16))) return false;
+      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->p_full[t]), j & 1, sh, g.status, 17))) return false;
       tc_fence_after_sync();
       if (elect_one()) {
 #pragma unroll
-        for (int kb = 0; kb < 8; ++kb) {  // O += P V_j: A = P [queries x keys], B = V^T [d x keys]
+        for (int kb = 0; kb < 8; ++kb) {  // 16 keys per MMA: eight 32-bit columns of bf16 pairs
           const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
-          mma_f16(tmem_o, smem_desc_sw128(smem_u32(p_s) + off), smem_desc_sw128(smem_u32(v_s + st * kTileBytes) + off), idesc,
-                  (j | kb) ? 1u : 0u);
+          mma_f16_ts(tmem + 2 * kTile + t * kTile, tmem + t * kTile + kb * 8, smem_desc_sw128(smem_u32(v_s + st * kTileBytes) + off), idesc,
+                     (j | kb) ? 1u : 0u);
         }
-        tc_commit(smem_u32(&sh->v_empty[st]));
-        tc_commit(smem_u32(&sh->pv_done));
+        tc_commit(smem_u32(&sh->pv_done[t]));
+        if (t == 1) tc_commit(smem_u32(&sh->v_empty[st]));  // both query tiles have read this V tile
       }
       __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(0, 0) && issue_s(1, 0);
+    for (int j = 0; j < tiles && ok; ++j) {
+      const bool more = j + 1 < tiles;
+      ok = issue_pv(0, j) && (!more || issue_s(0, j + 1)) && issue_pv(1, j) && (!more || issue_s(1, j + 1));
     }
   } else {
     // ------------------------------------------------------------ softmax, rescale, output
-    // Two warps per 32-row quadrant of tensor memory (warps w and w + 4): each thread owns one query row and HALF of
-    // the tile's 128 keys (and half of the 128 output columns). Two warps per scheduler hide each other's latencies;
-    // the row maximum is the only thing the two halves exchange per tile (through shared memory and an mbarrier the
-    // 64 threads arrive on, waited for with the same bound as every other wait), the row sums are added once at the end.
+    // Warps 2-5 serve query tile 0, warps 6-9 query tile 1; within a tile a warp owns the 32 rows of the TMEM quadrant
+    // it may access (warp index % 4) and a thread one query row with all 128 keys of the tile, so nothing is exchanged
+    // between threads. While the softmax of one query tile runs, the tensor pipe works on the other tile's products.
+    const int t = (warp - 2) >> 2;
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 keys / 64 output columns
     const int row = quad * 32 + lane;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
-    const uint32_t pair_bar = smem_u32(&sh->pair[quad]);
+    const uint32_t tmem_s = tmem + lane_base + t * kTile;
+    const uint32_t tmem_o = tmem + lane_base + 2 * kTile + t * kTile;
     float m_used = -INFINITY;  // the maximum the accumulator and the running sum are expressed against (log2 units)
     float l = 0.0f;
     bool ok = true;
-    uint32_t r[2][32];
+    uint32_t r[4][32];
     for (int j = 0; j < tiles; ++j) {
-      const int b = j & 1;
-      if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->s_full[b]), (j >> 1) & 1, sh, g.status, 18)))) break;
+      if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->s_full[t]), j & 1, sh, g.status, 18)))) break;
       tc_fence_after_sync();
-      tmem_ld_32x32(tmem + lane_base + b * kTile + half * 64, r[0]);
-      tmem_ld_32x32(tmem + lane_base + b * kTile + half * 64 + 32, r[1]);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->s_empty[b]));
-      const int valid = g.seq_kv - j * kTile - half * 64;  // keys of this half that exist
-      if (valid < 64) {  // only ever in the last tile: keys past the end of the sequence never count
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, r[c]);
+      tmem_ld_wait();
+      const int valid = g.seq_kv - j * kTile;  // keys of this tile that exist
+      if (valid < kTile) {  // only ever in the last tile: keys past the end of the sequence never count
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
       }
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one of 32 steps
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one of 128 steps
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 8)
 #pragma unroll
           for (int k = 0; k < 4; ++k) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(r[c][i + 2 * k]), __uint_as_float(r[c][i + 2 * k + 1])));
-      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      sh->row_max[b][half][row] = mx;
-      mbar_arrive(pair_bar);  // 64 arrivals: both halves of these 32 rows have published their maxima
-      if (!(ok = __all_sync(0xffffffffu, attn_wait(pair_bar, j & 1, sh, g.status, 22)))) break;
-      const float m_tile = fmaxf(mx, sh->row_max[b][half ^ 1][row]) * g.scale_log2;  // scale > 0: the maximum commutes with it
+      const float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * g.scale_log2;  // scale > 0: the maximum commutes with it
       const bool grow = m_tile > m_used + kRescaleThreshold;  // also true at j == 0 (m_used = -inf)
       if (__any_sync(0xffffffffu, grow && j > 0)) {
-        // O belongs to the previous step's product until it has completed. The warp rescales its 32 rows x 64 columns
-        // together (the TMEM accesses are warp-wide); rows that did not grow use a factor of 1.
-        if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (j - 1) & 1, sh, g.status, 19)))) break;
+        // S_t(j) was issued behind O_t += P_t V(j-1), so its completion says that O_t is at rest. The warp rescales its
+        // 32 rows together (the TMEM accesses are warp-wide); rows that did not grow use a factor of 1.
         const float m_new = grow ? m_tile : m_used;
         const float f = grow ? fast_exp2(m_used - m_new) : 1.0f;
         l *= f;
         m_used = m_new;
-        tc_fence_after_sync();
         uint32_t o[32];
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld_32x32(tmem_o + lane_base + half * 64 + c * 32, o);
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_32x32(tmem_o + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st_32x32(tmem_o + lane_base + half * 64 + c * 32, o);
+          tmem_st_32x32(tmem_o + c * 32, o);
         }
-        tmem_st_wait();
-        tc_fence_before_sync();
       } else if (grow) {
         m_used = m_tile;  // first tile: nothing accumulated yet
       }
-      // p = 2^(s * scale - m_used) <= 2^8 as bf16 pairs, kept in registers until the P buffer is free
+      // p = 2^(s * scale - m_used) <= 2^8 as bf16 pairs, written over the first 64 columns of the scores they came from
       float sum0 = 0.0f, sum1 = 0.0f;
-      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), g.scale_log2, -m_used));
           const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), g.scale_log2, -m_used));
           sum0 += p0;
           sum1 += p1;
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&pb);
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);  // key 2i in the low half: the lower K index
+          pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
         }
+        tmem_st_32x16(tmem_s + c * 16, pk);
+      }
       l += sum0 + sum1;
-      // the P buffer belongs to the previous step's product until it has completed
-      if (j > 0 && !(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (j - 1) & 1, sh, g.status, 21)))) break;
-      uint8_t* prow = p_s + half * kSlab + row * 128;  // this half's 64 keys are one 128-byte row of slab `half`
-#pragma unroll
-      for (int u = 0; u < 8; ++u)  // 8 probabilities = 16 bytes = one swizzle unit
-        *reinterpret_cast<uint4*>(prow + ((u ^ (row & 7)) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-      fence_proxy_async();  // the tensor core reads P through the async proxy
+      tmem_st_wait();
+      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->p_full));
+      if (lane == 0) mbar_arrive(smem_u32(&sh->p_full[t]));
     }
-    if (ok && (ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done), (tiles - 1) & 1, sh, g.status, 20)))) {
+    if (ok && (ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->pv_done[t]), (tiles - 1) & 1, sh, g.status, 20)))) {
       tc_fence_after_sync();
-      sh->row_sum[half][row] = l;
-      mbar_arrive(pair_bar);
-      ok = __all_sync(0xffffffffu, attn_wait(pair_bar, tiles & 1, sh, g.status, 23));
-      const float inv = 1.0f / (l + sh->row_sum[half ^ 1][row]);
-      const bool row_ok = ok && q0 + row < g.seq_q;
-      __nv_bfloat16* dst = g.out + size_t(row_ok ? q0 + row : 0) * g.ld_out + head * kTile + half * 64;
+      const float inv = 1.0f / l;
+      const int qrow = q0 + t * kTile + row;
+      const bool row_ok = qrow < g.seq_q;
+      __nv_bfloat16* dst = g.out + size_t(row_ok ? qrow : 0) * g.ld_out + head * kTile;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_o + lane_base + half * 64 + c * 32, o);
+        tmem_ld_32x32(tmem_o + c * 32, o);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -394,7 +382,7 @@ void attention_forward(const __nv_bfloat16* q, int ld_q, const __nv_bfloat16* k,
   a.out = out, a.ld_out = ld_out, a.seq_q = seq_q, a.seq_kv = seq_kv, a.group = heads / kv_heads;
   a.scale_log2 = (scale > 0.0f ? scale : 1.0f / sqrtf(float(head_dim))) * 1.4426950408889634f;
   a.status = device_status_word();
-  attention_kernel<<<dim3((seq_q + kTile - 1) / kTile, heads), kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, a);
+  attention_kernel<<<dim3((seq_q + 2 * kTile - 1) / (2 * kTile), heads), kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("sfq attention: launch failed: ") + cudaGetErrorString(e));
 }

@@ -133,6 +133,15 @@ __device__ __forceinline__ void mma_f16(uint32_t d, uint64_t a, uint64_t b, uint
       "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand in tensor memory: lanes are the rows of A, every 32-bit column holds two consecutive
+// 16-bit elements of K (the lower index in the low half); `a_tmem` is a TMEM address (lane 0 of the tile).
+__device__ __forceinline__ void mma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Block-scaled e2m1 x e2m1, one ue4m3 scale per 16 elements (four per K=64 instruction).
 __device__ __forceinline__ void mma_nvfp4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate,
                                           uint32_t sfa, uint32_t sfb) {
@@ -301,6 +310,15 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
       "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
       "r"(r[31])
+      : "memory");
+}
+// Sixteen consecutive 32-bit columns per lane.
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {
