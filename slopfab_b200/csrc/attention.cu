@@ -12,7 +12,8 @@
 //   warp 1      issues, per key tile j: O0 += P0(j) V(j), S0 = Q0 K(j+1)^T, O1 += P1(j) V(j), S1 = Q1 K(j+1)^T (8 MMAs
 //               128x128x16 each). S and O of both query tiles live in TMEM (4 x 128 columns); P is read by the second
 //               product straight from TMEM, where it overwrites the first 64 columns of the scores it was computed from
-//   warps 2-5   softmax of query tile 0, warps 6-9 of query tile 1, one query row per thread with all 128 keys of the
+//   warps 4-7   softmax of query tile 0, warps 8-11 of query tile 1 (warps 2-3 only hand their registers over: the
+//               softmax warpgroups run with 216 registers, the first warpgroup with 56), one query row per thread with all 128 keys of the
 //               tile: S from TMEM, running maximum and sum, P = exp2(s - m) as bf16 pairs back into TMEM, and - only
 //               when a row's maximum has grown by more than 2^8 since the accumulator was last scaled - a rescale of
 //               O in TMEM. A stale maximum changes nothing in exact arithmetic (numerator and denominator carry the
@@ -40,7 +41,8 @@ using namespace ptx;
 constexpr int kTile = 128;             // queries per query tile (two per CTA), keys per step, head_dim
 constexpr int kSlab = kTile * 128;     // 128 rows x 128 bytes: 64 bf16 columns of a tile
 constexpr int kTileBytes = 2 * kSlab;  // [128 x 128] bf16
-constexpr int kAttnThreads = 320;  // producer, MMA issuer, eight softmax warps
+constexpr int kAttnThreads = 384;  // warpgroup 0: producer, MMA issuer, two idle warps; warpgroups 1 and 2: the softmax of query tiles 0 and 1
+constexpr int kAttnRegsLean = 56, kAttnRegsSoftmax = 216;  // after setmaxnreg: 128 x 56 + 256 x 216 <= 65536
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnShared {
@@ -59,12 +61,17 @@ struct AttnArgs {
   int* status;
 };
 
+// `nap` > 0: sleep that many nanoseconds between polls. The softmax warps and the producer wait for long stretches by
+// design; polling flat out they would take issue slots from the one warp that feeds the tensor pipe.
+template <int nap = 0>
 __device__ __forceinline__ bool attn_wait(uint32_t bar, uint32_t parity, AttnShared* sh, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock_now();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (nap > 0) __nanosleep(nap);
+    }
     if (sh->abort) return false;
     if (clock_now() - start > kWaitCycles) {
       atomicCAS(status, 0, code);
@@ -79,6 +86,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// 2^x for a pair of arguments on the FMA pipe instead of the special-function unit, which is what the softmax of two
+// query tiles saturates (32768 exponentials per key tile at 16 per clock = the 2048 cycles the tile's products take).
+// x = n + f with n = round(x), f in [-1/2, 1/2]: a cubic for 2^f (relative error 7.5e-5, a sixtieth of the bf16 rounding
+// the result goes through) and n added into the exponent field. Arguments are at most 2^8 by construction and are clamped
+// at -125 below, where the result (~2e-38) is as good as the zero the hardware instruction returns.
+__device__ __forceinline__ f32x2 exp2_pair_fma(f32x2 x) {
+  float x0, x1;
+  unpack2(x, x0, x1);
+  const f32x2 xc = pack2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+  const f32x2 magic = pack2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+  const f32x2 t = add2(xc, magic);
+  const f32x2 f = sub2(xc, sub2(t, magic));
+  f32x2 p = fma2(pack2(0.0551716648f, 0.0551716648f), f, pack2(0.2426111251f, 0.2426111251f));
+  p = fma2(p, f, pack2(0.6932609677f, 0.6932609677f));
+  p = fma2(p, f, pack2(0.9999280572f, 0.9999280572f));
+  float p0, p1, t0, t1;
+  unpack2(p, p0, p1);
+  unpack2(t, t0, t1);
+  return pack2(__int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23)), __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23)));
+}
+constexpr int kFmaPairsOfFour = 1;  // of every four pairs of probabilities, how many take the FMA-pipe exponential
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -122,6 +151,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem = sh->tmem_base;  // columns: S/P of tile 0 [0,128), of tile 1 [128,256), O of tile 0 [256,384), of tile 1 [384,512)
 
+  // Each role's code sits directly under its warpgroup's setmaxnreg, so the compiler budgets it accordingly.
+  if (warp < 4) {
+    reg_dec<kAttnRegsLean>();
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -133,11 +165,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       for (int j = 0; j < tiles; ++j) {
         const int st = j & 1;
         const uint32_t ph = ((j >> 1) & 1) ^ 1;
-        if (!attn_wait(smem_u32(&sh->k_empty[st]), ph, sh, g.status, 11)) break;
+        if (!attn_wait<200>(smem_u32(&sh->k_empty[st]), ph, sh, g.status, 11)) break;
         mbar_arrive_expect_tx(smem_u32(&sh->k_full[st]), kTileBytes);
         tma_load_2d(smem_u32(k_s + st * kTileBytes), &map_k, kv_head * 256, j * kTile, smem_u32(&sh->k_full[st]));
         tma_load_2d(smem_u32(k_s + st * kTileBytes + kSlab), &map_k, kv_head * 256 + 128, j * kTile, smem_u32(&sh->k_full[st]));
-        if (!attn_wait(smem_u32(&sh->v_empty[st]), ph, sh, g.status, 12)) break;
+        if (!attn_wait<200>(smem_u32(&sh->v_empty[st]), ph, sh, g.status, 12)) break;
         mbar_arrive_expect_tx(smem_u32(&sh->v_full[st]), kTileBytes);
         // V^T: rows are (kv_head, d), columns are keys; 64 keys = 128 bytes per slab
         tma_load_2d(smem_u32(v_s + st * kTileBytes), &map_vt, j * 256, kv_head * kTile, smem_u32(&sh->v_full[st]));
@@ -154,36 +186,23 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     bool ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->q_full), 0, sh, g.status, 13));
     auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
       const int st = j & 1;
-      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14))) return false;
+      // the second query tile reads the K tile the first one has just waited for
+      if (t == 0 && !__all_sync(full_mask, attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14))) return false;
       tc_fence_after_sync();
-      if (elect_one()) {
-#pragma unroll
-        for (int kb = 0; kb < 8; ++kb) {
-          const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
-          mma_f16(tmem + t * kTile, smem_desc_sw128(smem_u32(q_s + t * kTileBytes) + off), smem_desc_sw128(smem_u32(k_s + st * kTileBytes) + off),
-                  idesc, kb ? 1u : 0u);
-        }
-        tc_commit(smem_u32(&sh->s_full[t]));
-        if (t == 1) tc_commit(smem_u32(&sh->k_empty[st]));  // both query tiles have read this K tile
-      }
+      if (elect_one())  // eight MMAs, the commit for the softmax warps and, behind the second query tile, the one that frees K
+        mma_f16_x8_commit(tmem + t * kTile, smem_desc_sw128(smem_u32(q_s + t * kTileBytes)), smem_desc_sw128(smem_u32(k_s + st * kTileBytes)),
+                          idesc, 0u, kSlab >> 4, smem_u32(&sh->s_full[t]), smem_u32(&sh->k_empty[st]), t == 1 ? 1u : 0u);
       __syncwarp();
       return true;
     };
     auto issue_pv = [&](int t, int j) {  // O_t += P_t V_j: A = P_t in tensor memory [queries x keys], B = V^T [d x keys]
       const int st = j & 1;
-      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16))) return false;
+      if (t == 0 && !__all_sync(full_mask, attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16))) return false;
       if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->p_full[t]), j & 1, sh, g.status, 17))) return false;
       tc_fence_after_sync();
-      if (elect_one()) {
-#pragma unroll
-        for (int kb = 0; kb < 8; ++kb) {  // 16 keys per MMA: eight 32-bit columns of bf16 pairs
-          const uint32_t off = (kb >> 2) * kSlab + (kb & 3) * 32;
-          mma_f16_ts(tmem + 2 * kTile + t * kTile, tmem + t * kTile + kb * 8, smem_desc_sw128(smem_u32(v_s + st * kTileBytes) + off), idesc,
-                     (j | kb) ? 1u : 0u);
-        }
-        tc_commit(smem_u32(&sh->pv_done[t]));
-        if (t == 1) tc_commit(smem_u32(&sh->v_empty[st]));  // both query tiles have read this V tile
-      }
+      if (elect_one())  // 16 keys per MMA: eight 32-bit columns of bf16 pairs
+        mma_f16_ts_x8_commit(tmem + 2 * kTile + t * kTile, tmem + t * kTile, smem_desc_sw128(smem_u32(v_s + st * kTileBytes)), idesc,
+                             j ? 1u : 0u, kSlab >> 4, smem_u32(&sh->pv_done[t]), smem_u32(&sh->v_empty[st]), t == 1 ? 1u : 0u);
       __syncwarp();
       return true;
     };
@@ -192,12 +211,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const bool more = j + 1 < tiles;
       ok = issue_pv(0, j) && (!more || issue_s(0, j + 1)) && issue_pv(1, j) && (!more || issue_s(1, j + 1));
     }
+  }
   } else {
+    reg_inc<kAttnRegsSoftmax>();
     // ------------------------------------------------------------ softmax, rescale, output
-    // Warps 2-5 serve query tile 0, warps 6-9 query tile 1; within a tile a warp owns the 32 rows of the TMEM quadrant
+    // Warps 4-7 serve query tile 0, warps 8-11 query tile 1; within a tile a warp owns the 32 rows of the TMEM quadrant
     // it may access (warp index % 4) and a thread one query row with all 128 keys of the tile, so nothing is exchanged
     // between threads. While the softmax of one query tile runs, the tensor pipe works on the other tile's products.
-    const int t = (warp - 2) >> 2;
+    const int t = (warp - 4) >> 2;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
@@ -207,64 +228,90 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     float l = 0.0f;
     bool ok = true;
     uint32_t r[4][32];
-    for (int j = 0; j < tiles; ++j) {
-      if (!(ok = __all_sync(0xffffffffu, attn_wait(smem_u32(&sh->s_full[t]), j & 1, sh, g.status, 18)))) break;
-      tc_fence_after_sync();
+    const f32x2 scale2 = pack2(g.scale_log2, g.scale_log2);
+    // p = 2^(s * scale - m) <= 2^8 for the 32 keys of chunk c as bf16 pairs, written over columns [16 c, 16 c + 16) of the
+    // scores they came from (those columns belong to chunks 0 and 1, which are in registers by then); returns their sum.
+    auto emit_chunk = [&](int c, float m, f32x2 sum2) {
+      const f32x2 negm2 = pack2(-m, -m);
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, r[c]);
-      tmem_ld_wait();
-      const int valid = g.seq_kv - j * kTile;  // keys of this tile that exist
-      if (valid < kTile) {  // only ever in the last tile: keys past the end of the sequence never count
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
-      }
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one of 128 steps
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; i += 8)
-#pragma unroll
-          for (int k = 0; k < 4; ++k) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(r[c][i + 2 * k]), __uint_as_float(r[c][i + 2 * k + 1])));
-      const float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * g.scale_log2;  // scale > 0: the maximum commutes with it
-      const bool grow = m_tile > m_used + kRescaleThreshold;  // also true at j == 0 (m_used = -inf)
-      if (__any_sync(0xffffffffu, grow && j > 0)) {
-        // S_t(j) was issued behind O_t += P_t V(j-1), so its completion says that O_t is at rest. The warp rescales its
-        // 32 rows together (the TMEM accesses are warp-wide); rows that did not grow use a factor of 1.
-        const float m_new = grow ? m_tile : m_used;
-        const float f = grow ? fast_exp2(m_used - m_new) : 1.0f;
-        l *= f;
-        m_used = m_new;
-        uint32_t o[32];
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_32x32(tmem_o + c * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st_32x32(tmem_o + c * 32, o);
+      for (int i = 0; i < 32; i += 2) {
+        const f32x2 x = fma2(pack2(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])), scale2, negm2);
+        f32x2 p;
+        if (((i >> 1) & 3) < kFmaPairsOfFour) {
+          p = exp2_pair_fma(x);
+        } else {
+          float x0, x1;
+          unpack2(x, x0, x1);
+          p = pack2(fast_exp2(x0), fast_exp2(x1));
         }
-      } else if (grow) {
-        m_used = m_tile;  // first tile: nothing accumulated yet
+        sum2 = add2(sum2, p);
+        float p0, p1;
+        unpack2(p, p0, p1);
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);  // key 2i in the low half: the lower K index
+        pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
       }
-      // p = 2^(s * scale - m_used) <= 2^8 as bf16 pairs, written over the first 64 columns of the scores they came from
-      float sum0 = 0.0f, sum1 = 0.0f;
+      tmem_st_32x16(tmem_s + c * 16, pk);
+      return sum2;
+    };
+    auto chunk_max = [&](int c, int valid) {  // masks the keys past the end of the sequence (last tile only), then the maximum
+      if (valid < kTile) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
+      }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one of 32 steps
+#pragma unroll
+      for (int i = 0; i < 32; i += 8)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(r[c][i + 2 * k]), __uint_as_float(r[c][i + 2 * k + 1])));
+      return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+    };
+    for (int j = 0; j < tiles; ++j) {
+      if (!(ok = __all_sync(0xffffffffu, attn_wait<40>(smem_u32(&sh->s_full[t]), j & 1, sh, g.status, 18)))) break;
+      tc_fence_after_sync();
+      const int valid = g.seq_kv - j * kTile;  // keys of this tile that exist
+      // The probabilities are computed against the maximum the accumulator was last scaled to, which is known before the
+      // tile arrives: chunk c is exponentiated while chunk c + 1 is still on its way out of tensor memory, and the tile's
+      // own maximum is only gathered along the way to decide afterwards whether the reference has to move.
+      f32x2 sum2 = pack2(0.0f, 0.0f);
+      float mx = -INFINITY;
+      tmem_ld_32x32(tmem_s, r[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), g.scale_log2, -m_used));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), g.scale_log2, -m_used));
-          sum0 += p0;
-          sum1 += p1;
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);  // key 2i in the low half: the lower K index
-          pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
-        }
-        tmem_st_32x16(tmem_s + c * 16, pk);
+        tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld_32x32(tmem_s + (c + 1) * 32, r[c + 1]);
+        mx = fmaxf(mx, chunk_max(c, valid));
+        if (j > 0) sum2 = emit_chunk(c, m_used, sum2);
       }
+      const float m_tile = mx * g.scale_log2;  // scale > 0: the maximum commutes with it
+      const bool grow = m_tile > m_used + kRescaleThreshold;  // also true at j == 0 (m_used = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        // Rare after the first tiles: a row's maximum has grown by more than 2^8. S_t(j) was issued behind
+        // O_t += P_t V(j-1), so its completion says that O_t is at rest. The warp rescales its 32 rows together (the
+        // TMEM accesses are warp-wide; rows that did not grow use a factor of 1) and computes the tile's probabilities
+        // again against the new reference -- every score is still in registers -- over the ones just written.
+        const float m_new = grow ? m_tile : m_used;
+        if (j > 0) {
+          const float f = grow ? fast_exp2(m_used - m_new) : 1.0f;
+          l *= f;
+          uint32_t o[32];
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_32x32(tmem_o + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st_32x32(tmem_o + c * 32, o);
+          }
+        }
+        m_used = m_new;
+        sum2 = pack2(0.0f, 0.0f);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sum2 = emit_chunk(c, m_used, sum2);
+      }
+      float sum0, sum1;
+      unpack2(sum2, sum0, sum1);
       l += sum0 + sum1;
       tmem_st_wait();
       tc_fence_before_sync();

@@ -142,6 +142,56 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t
       "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Eight kind::f16 MMAs over one 128-byte-swizzled [rows x 128 columns of 16-bit] operand pair -- two 64-column slabs of
+// `slab16` 16-byte units each, four K = 16 steps of 32 bytes per slab -- and the commits that follow them, as ONE
+// instruction sequence from one thread: the descriptors advance by immediate adds inside the sequence, so the issuing
+// thread spends tens of cycles per MMA instead of rebuilding two 64-bit descriptors for each. `accumulate_first` == 0
+// makes the first MMA overwrite D. `bar2` gets a second commit when `commit2` != 0. The `_ts` form reads A from tensor
+// memory (eight 32-bit columns of 16-bit pairs per K step, 64 columns in all).
+__device__ __forceinline__ void mma_f16_x8_commit(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate_first,
+                                                  uint32_t slab16, uint32_t bar1, uint32_t bar2, uint32_t commit2) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt, pc;\n\t.reg .b64 s, a1, a2, a3, a4, a5, a6, a7, b1, b2, b3, b4, b5, b6, b7;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pc, %8, 0;\n\tcvt.u64.u32 s, %5;\n\t"
+      "add.s64 a1, %1, 2;\n\tadd.s64 a2, %1, 4;\n\tadd.s64 a3, %1, 6;\n\tadd.s64 a4, %1, s;\n\t"
+      "add.s64 a5, a4, 2;\n\tadd.s64 a6, a4, 4;\n\tadd.s64 a7, a4, 6;\n\t"
+      "add.s64 b1, %2, 2;\n\tadd.s64 b2, %2, 4;\n\tadd.s64 b3, %2, 6;\n\tadd.s64 b4, %2, s;\n\t"
+      "add.s64 b5, b4, 2;\n\tadd.s64 b6, b4, 4;\n\tadd.s64 b7, b4, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a4, b4, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a5, b5, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a6, b6, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a7, b7, %3, pt;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "@pc tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t}" ::"r"(d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate_first), "r"(slab16), "r"(bar1), "r"(bar2), "r"(commit2)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_x8_commit(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate_first,
+                                                     uint32_t slab16, uint32_t bar1, uint32_t bar2, uint32_t commit2) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt, pc;\n\t.reg .b64 s, b1, b2, b3, b4, b5, b6, b7;\n\t.reg .b32 a1, a2, a3, a4, a5, a6, a7;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tsetp.ne.b32 pc, %8, 0;\n\tcvt.u64.u32 s, %5;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\tadd.u32 a4, %1, 32;\n\t"
+      "add.u32 a5, %1, 40;\n\tadd.u32 a6, %1, 48;\n\tadd.u32 a7, %1, 56;\n\t"
+      "add.s64 b1, %2, 2;\n\tadd.s64 b2, %2, 4;\n\tadd.s64 b3, %2, 6;\n\tadd.s64 b4, %2, s;\n\t"
+      "add.s64 b5, b4, 2;\n\tadd.s64 b6, b4, 4;\n\tadd.s64 b7, b4, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a4], b4, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a5], b5, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a6], b6, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a7], b7, %3, pt;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "@pc tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t}" ::"r"(d),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate_first), "r"(slab16), "r"(bar1), "r"(bar2), "r"(commit2)
+      : "memory");
+}
 // Block-scaled e2m1 x e2m1, one ue4m3 scale per 16 elements (four per K=64 instruction).
 __device__ __forceinline__ void mma_nvfp4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate,
                                           uint32_t sfa, uint32_t sfb) {
@@ -323,6 +373,31 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- packed fp32 pairs
+// Two fp32 in one 64-bit register; add / sub / mul / fma on both halves in one instruction (round to nearest even).
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
 
 // ---------------------------------------------------------------- descriptors
