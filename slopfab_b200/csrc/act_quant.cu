@@ -29,6 +29,7 @@
 #include <string>
 
 #include "codec.cuh"
+#include "ptx.cuh"
 
 namespace sfq {
 namespace {
@@ -489,6 +490,102 @@ size_t nvfp4_act_scale_bytes(int rows, int dim) {
   return size_t((rows + 127) / 128) * 128 * size_t(dim / 16);
 }
 
+// ---- per-16-block fp4 quantizer without a norm in front (the Linear's own case) --------------------------------------
+// The same arithmetic as the fp4 branch of process_row (quantize_act_kernel, src/cuda/nvfp4_gemm.cu:107-158): per 16
+// elements s8 = e4m3_rn_sat(amax / 6), inv = 1 / decode(s8) (0 for an all-zero block), code = e2m1_rn_sat(x * inv). A
+// block's scale depends on that block alone, so there is nothing to exchange between threads: the activation is walked as
+// a flat array of 16-element blocks, two per thread in flight, with no barrier and no shared memory, the maximum on
+// bf16x2 words and the products on packed fp32 pairs. FEED: high nibble = even element, scales in the 128x4-tiled layout
+// with the rows padded to a multiple of 128 (the pad rows' scales are written as zero).
+namespace {
+__device__ __forceinline__ uint32_t habs2(uint32_t a) {
+  uint32_t d;
+  asm("abs.bf16x2 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ uint32_t hmax2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+template <bool FEED>
+__device__ __forceinline__ void quantize_block16(const uint4 r0, const uint4 r1, uint2& codes, uint8_t& s8) {
+  const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};  // element 2i in the low half of word i
+  uint32_t m = hmax2(hmax2(hmax2(habs2(w[0]), habs2(w[1])), hmax2(habs2(w[2]), habs2(w[3]))),
+                     hmax2(hmax2(habs2(w[4]), habs2(w[5])), hmax2(habs2(w[6]), habs2(w[7]))));
+  m = hmax2(m, m >> 16);
+  const float amax = __uint_as_float(m << 16);
+  s8 = uint8_t(__nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3));
+  const float decoded = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3)));
+  const float inv = decoded > 0.0f ? __frcp_rn(decoded) : 0.0f;  // the correctly rounded reciprocal, as 1.0f / decoded
+  const ptx::f32x2 inv2 = ptx::pack2(inv, inv);
+  uint32_t out[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float even, odd;
+    ptx::unpack2(ptx::mul2(ptx::pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u)), inv2), even, odd);
+    // The conversion puts its first component in the low nibble. The reference layout wants the even element there; the
+    // GEMM feed wants it in the high nibble, like the weight files.
+    const __nv_fp4x2_storage_t b = FEED ? __nv_cvt_float2_to_fp4x2(make_float2(odd, even), __NV_E2M1, cudaRoundNearest)
+                                        : __nv_cvt_float2_to_fp4x2(make_float2(even, odd), __NV_E2M1, cudaRoundNearest);
+    out[i >> 2] |= uint32_t(b) << (8 * (i & 3));
+  }
+  codes = make_uint2(out[0], out[1]);
+}
+
+template <bool FEED>
+__global__ void __launch_bounds__(256) quantize_nvfp4_flat_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ packed,
+                                                                  uint8_t* __restrict__ scales, int rows, int padded_rows, int chunks) {
+  // item g = (row, chunk): advance by the grid's stride without a division per item
+  const uint32_t stride = gridDim.x * blockDim.x;
+  const uint32_t first = blockIdx.x * blockDim.x + threadIdx.x;
+  int row = int(first / uint32_t(chunks)), c = int(first % uint32_t(chunks));
+  const int drow = int(stride / uint32_t(chunks)), dc = int(stride % uint32_t(chunks));
+  auto load = [&](int r, int cc, uint4& a, uint4& b) {
+    a = make_uint4(0, 0, 0, 0);
+    b = a;
+    if (r < rows) {
+      const uint4* src = reinterpret_cast<const uint4*>(x) + (size_t(r) * chunks + cc) * 2;
+      a = __ldg(src);
+      b = __ldg(src + 1);
+    }
+  };
+  auto emit = [&](int r, int cc, const uint4& a, const uint4& b) {
+    if (r >= padded_rows) return;
+    uint2 codes;
+    uint8_t s8 = 0;
+    if (r < rows) {
+      quantize_block16<FEED>(a, b, codes, s8);
+      reinterpret_cast<uint2*>(packed)[size_t(r) * chunks + cc] = codes;
+    }
+    scales[FEED ? nvfp4_scale_offset(r, cc, chunks) : size_t(r) * chunks + cc] = s8;
+  };
+  while (row < padded_rows) {
+    int row2 = row + drow, c2 = c + dc;
+    if (c2 >= chunks) c2 -= chunks, ++row2;
+    uint4 a0, b0, a1, b1;
+    load(row, c, a0, b0);
+    load(row2, c2, a1, b1);
+    emit(row, c, a0, b0);
+    emit(row2, c2, a1, b1);
+    row = row2 + drow, c = c2 + dc;
+    if (c >= chunks) c -= chunks, ++row;
+  }
+}
+
+template <bool FEED>
+void launch_nvfp4_flat(const __nv_bfloat16* x, uint8_t* packed, uint8_t* scales, int rows, int dim, cudaStream_t stream) {
+  const int chunks = dim / 16;
+  const int padded = FEED ? (rows + 127) / 128 * 128 : rows;
+  const size_t items = size_t(padded) * chunks;
+  if (items >= (size_t(1) << 31)) throw std::invalid_argument("quantize_nvfp4_block: too many 16-element blocks for one launch");
+  const int ctas = int(std::min<size_t>((items + 511) / 512, size_t(device_sm_count()) * 8));  // two items per thread and trip
+  quantize_nvfp4_flat_kernel<FEED><<<ctas, 256, 0, stream>>>(x, packed, scales, rows, padded, chunks);
+  check_launch("quantize_nvfp4_block");
+}
+}  // namespace
+
 void quantize_nvfp4_block(const __nv_bfloat16* x, const NormArgs& norm, uint8_t* packed, uint8_t* scales,
                           __nv_bfloat16* normed_out, int rows, int dim, int layout, cudaStream_t stream) {
   if (rows <= 0 || dim <= 0) return;
@@ -496,6 +593,16 @@ void quantize_nvfp4_block(const __nv_bfloat16* x, const NormArgs& norm, uint8_t*
   if (dim % 16 != 0)
     throw std::runtime_error("nvfp4: activation dim must be a multiple of 16, got " + std::to_string(dim));
   if (reinterpret_cast<uintptr_t>(packed) % 8 != 0) throw std::invalid_argument("quantize_nvfp4_block: output must be 8-byte aligned");
+  if (layout != SFQ_NVFP4_ACT_REFERENCE && layout != SFQ_NVFP4_ACT_GEMM_FEED) throw std::invalid_argument("quantize_nvfp4_block: unknown layout");
+  if (layout == SFQ_NVFP4_ACT_GEMM_FEED && dim % 64 != 0)
+    throw std::invalid_argument("quantize_nvfp4_block: the tiled scale layout needs dim % 64 == 0");
+  if (norm.weight == nullptr && reinterpret_cast<uintptr_t>(x) % 16 == 0) {  // no norm in front: the barrier-free kernel
+    if (layout == SFQ_NVFP4_ACT_REFERENCE)
+      launch_nvfp4_flat<false>(x, packed, scales, rows, dim, stream);
+    else
+      launch_nvfp4_flat<true>(x, packed, scales, rows, dim, stream);
+    return;
+  }
   FusedArgs a = base_args(x, norm, rows, dim);
   a.packed = packed;
   a.scales = scales;
