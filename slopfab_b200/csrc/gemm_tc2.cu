@@ -10,7 +10,8 @@
 //   both CTAs    warp 0 loads its own operand halves with TMA (no multicast); the bytes of BOTH CTAs are counted
 //                on the leader's `full` barrier. Warps 4-11 drain the CTA's own accumulator and store its rows.
 //   leader only  warp 1 issues the MMAs for the pair; its commits arrive on `empty` / `acc_full` in both CTAs.
-//                Warps 12-15 (nvfp4) copy block scales into TMEM in both CTAs (each from its own shared memory).
+//                For nvfp4 the same thread copies each k-block's scale atoms into TMEM of both CTAs (each from its own
+//                shared memory) right in front of the MMA that reads them.
 //   the peer's epilogue hands the accumulator back by arriving on the LEADER's acc_empty barrier.
 // Tail of the persistent schedule: when the last wave would leave more than half of the pairs idle, its tiles are
 // cut into two 256 x 128 halves (N = 128 MMAs, 64 weight rows per CTA), so that wave takes about two thirds of a
@@ -110,7 +111,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&sh->full[s]), 1);     // used in the leader: its producer's arrive + both CTAs' bytes
       mbar_init(smem_u32(&sh->empty[s]), 1);    // in each CTA: the pair's MMAs of that stage are done
-      mbar_init(smem_u32(&sh->sf_full[s]), 4);  // leader: the four scale-copy warps
     }
     for (int a = 0; a < ACC; ++a) {
       mbar_init(smem_u32(&sh->acc_full[a]), 1);    // in each CTA
@@ -197,10 +197,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
       int s = 0;
       uint32_t ph = 0, tile_it = 0;
-      // What the MMAs of stage s wait for: nvfp4 - the scale-copy warps arrive on sf_full[s] after they have seen
-      // full[s] themselves and their copies into TMEM slot s have landed, so that one barrier stands for operands and
-      // scales alike; the other kinds - the loads.
-      auto stage_bar = [&](int st) { return smem_u32(KIND == kNvfp4 ? &sh->sf_full[st] : &sh->full[st]); };
+      // nvfp4: this thread also copies the stage's scale atoms shared memory -> TMEM, each k-block's three copies right in
+      // front of the MMA that reads them (copy -> MMA from one thread execute in issue order). TMEM scale slot s belongs to
+      // stage s: full[s] of this round follows empty[s] of the previous one, i.e. the MMAs that read the slot are done.
+      auto stage_bar = [&](int st) { return smem_u32(&sh->full[st]); };
+      constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+      const uint32_t sfa0 = ((smem_u32(smem) & 0x3FFFFu) + C::kStageA + C::kStageB) >> 4;
       // The barrier of the NEXT stage is probed (without blocking) in the same breath as a stage's MMAs are issued, so
       // in steady state the blocking wait and its round trip never sit between two stages' MMAs.
       uint32_t ready = 0;
@@ -214,7 +216,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t sfb_step = narrow ? BN / 64 : BN / 32;  // TMEM columns of the weight scales per k-block
         for (int ks = 0; ks < k_stages; ++ks) {
           if (!__all_sync(0xffffffffu, ready != 0)) {
-            if (!(ok = wait_barrier_warp(stage_bar(s), ph, sh, g.status, KIND == kNvfp4 ? 5 : 3))) break;
+            if (!(ok = wait_barrier_warp(stage_bar(s), ph, sh, g.status, 3))) break;
           }
           tc_fence_after_sync();
           const int s_next = s + 1 == C::kStages ? 0 : s + 1;
@@ -225,8 +227,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t sf_cols = tmem + C::kAccCols + s * C::kSfSlotCols;
           ready = 1;  // the lanes that issue nothing do not vote against
           if (elect_one()) {
-            if (kb_valid == 4) {
-              // commit: frees the stage (and its scale slot) in both CTAs
+            if (KIND == kNvfp4 && kb_valid == 4 && !narrow) {
+              ready = stage4_pair_nvfp4_cp(d, da, db, idesc, ks ? 1u : 0u, sf_cols, kSfHi | uint64_t(sfa0 + s * kStageStep),
+                                           smem_u32(&sh->empty[s]), stage_bar(s_next), ph_next);
+            } else if (KIND != kNvfp4 && kb_valid == 4) {
+              // commit: frees the stage in both CTAs
               ready = stage4_pair<int(KIND)>(d, da, db, idesc, ks ? 1u : 0u, sf_cols, sf_cols + 16, sfb_step, smem_u32(&sh->empty[s]),
                                              stage_bar(s_next), ph_next);
             } else {
@@ -240,8 +245,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     mma_i8_pair(d, da + adv, db + adv, idesc, acc);
                   else if constexpr (KIND == kBf16)
                     mma_f16_pair(d, da + adv, db + adv, idesc, acc);
-                  else
+                  else {
+                    const uint32_t sfa = sfa0 + s * kStageStep, sfb = sfa + (C::kStageSfa >> 4);
+                    tc_copy_32x128b_x4_pair(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
+                    tc_copy_32x128b_x4_pair(sf_cols + 16 + kb * sfb_step, kSfHi | uint64_t(sfb + kb * 32));
+                    if (!narrow) tc_copy_32x128b_x4_pair(sf_cols + 16 + kb * sfb_step + 4, kSfHi | uint64_t(sfb + (4 + kb) * 32));
                     mma_nvfp4_pair(d, da + adv, db + adv, idesc, acc, sf_cols + kb * 4, sf_cols + 16 + kb * sfb_step);
+                  }
                 }
               }
               tc_commit_pair(smem_u32(&sh->empty[s]), 3);
@@ -256,44 +266,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp >= 12) {
     reg_dec<kRegsLean>();
-    // ------------------------------------------------------------ scale-factor copies (nvfp4, leader)
-    if constexpr (KIND == kNvfp4) {
-      if (rank == 0) {
-        const int kb = warp - 12;
-        constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
-        constexpr uint32_t kStageStep = C::kStageBytes >> 4;
-        const uint32_t sfa0 = ((smem_u32(smem) & 0x3FFFFu) + C::kStageA + C::kStageB) >> 4;
-        const int last_valid = min(4, (row_bytes - (k_stages - 1) * kSlabBytes + kMmaKBytes - 1) / kMmaKBytes);
-        int s = 0;
-        uint32_t ph = 0;
-        bool ok = true;
-        for (int t = pair; t < num_work && ok; t += num_pairs) {
-          const int row_tiles = (TAIL && t >= first_split) ? 1 : 2;  // 128-row weight scale tiles of this work item
-          for (int ks = 0; ks < k_stages; ++ks) {
-            // full[s] of this round completes only after the producer has seen empty[s] of the previous round, so the
-            // loads having landed also says that the MMAs which read this stage's scale slot are done: one wait, not two
-            if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 6))) break;
-            tc_fence_after_sync();
-            const int kb_valid = ks == k_stages - 1 ? last_valid : 4;
-            const uint32_t sf_cols = tmem + C::kAccCols + s * C::kSfSlotCols;
-            const uint32_t sfa = sfa0 + s * kStageStep;
-            const uint32_t sfb = sfa + (C::kStageSfa >> 4);
-            if (elect_one()) {
-              if (kb < kb_valid) {
-                tc_copy_32x128b_x4_pair(sf_cols + kb * 4, kSfHi | uint64_t(sfa + kb * 32));
-#pragma unroll
-                for (int rt = 0; rt < 2; ++rt)
-                  if (rt < row_tiles)
-                    tc_copy_32x128b_x4_pair(sf_cols + 16 + kb * (row_tiles * 4) + rt * 4, kSfHi | uint64_t(sfb + (rt * 4 + kb) * 32));
-              }
-              tc_commit_pair_local(smem_u32(&sh->sf_full[s]));
-            }
-            __syncwarp();
-            if (++s == C::kStages) s = 0, ph ^= 1;
-          }
-        }
-      }
-    }
+    // (no role in the pair kernel: the scale copies are issued by the MMA thread)
   } else {
     reg_inc<kRegsEpilogue>();
     // ------------------------------------------------------------ epilogue (8 warps, both CTAs)

@@ -279,6 +279,51 @@ __device__ __forceinline__ void mma_nvfp4_pair(uint32_t d, uint64_t a, uint64_t 
       : "memory");
 }
 
+// One whole nvfp4 stage of the pair kernel from a single thread, scale copies included: probe the NEXT stage's barrier,
+// then per 64-element k-block the three scale-atom copies shared memory -> TMEM (activation rows; weight rows 0-127 and
+// 128-255 of the tile) followed by the MMA that reads them, then the commit. tcgen05.cp followed by tcgen05.mma from one
+// thread execute in issue order, so no barrier stands between a copy and its MMA; and every tcgen05 instruction of an
+// SM goes through one issue path at about 28 cycles each, so 17 instructions per stage from this thread fit under the
+// 512 cycles the tensor pipe needs for the four MMAs, where copies from other warps with their own commits (21) do not.
+// `sf_desc` is the shared-memory descriptor of the stage's first activation scale atom; the weights' atoms follow 2 KB on.
+__device__ __forceinline__ uint32_t stage4_pair_nvfp4_cp(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate_first,
+                                                        uint32_t sf_cols, uint64_t sf_desc, uint32_t commit_bar, uint32_t next_bar,
+                                                        uint32_t next_parity) {
+  uint32_t ready;
+#define SFQ_CP "tcgen05.cp.cta_group::2.32x128b.warpx4 "
+#define SFQ_MMA "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X "
+  asm volatile(
+      "{\n\t.reg .pred p, pt, pn;\n\t.reg .b64 a1, a2, a3, b1, b2, b3, sa1, sa2, sa3, sb0, sb1, sb2, sb3, sc0, sc1, sc2, sc3;\n\t"
+      ".reg .b32 fa1, fa2, fa3, fb0, fb1, fb2, fb3, fc0, fc1, fc2, fc3;\n\t.reg .b16 m;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%8], %9;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tmov.b16 m, 3;\n\t"
+      "add.s64 a1, %2, 2;\n\tadd.s64 a2, %2, 4;\n\tadd.s64 a3, %2, 6;\n\t"
+      "add.s64 b1, %3, 2;\n\tadd.s64 b2, %3, 4;\n\tadd.s64 b3, %3, 6;\n\t"
+      "add.s64 sa1, %7, 32;\n\tadd.s64 sa2, %7, 64;\n\tadd.s64 sa3, %7, 96;\n\t"
+      "add.s64 sb0, %7, 128;\n\tadd.s64 sb1, %7, 160;\n\tadd.s64 sb2, %7, 192;\n\tadd.s64 sb3, %7, 224;\n\t"
+      "add.s64 sc0, %7, 256;\n\tadd.s64 sc1, %7, 288;\n\tadd.s64 sc2, %7, 320;\n\tadd.s64 sc3, %7, 352;\n\t"
+      "add.u32 fa1, %6, 4;\n\tadd.u32 fa2, %6, 8;\n\tadd.u32 fa3, %6, 12;\n\t"
+      "add.u32 fb0, %6, 16;\n\tadd.u32 fb1, %6, 24;\n\tadd.u32 fb2, %6, 32;\n\tadd.u32 fb3, %6, 40;\n\t"
+      "add.u32 fc0, %6, 20;\n\tadd.u32 fc1, %6, 28;\n\tadd.u32 fc2, %6, 36;\n\tadd.u32 fc3, %6, 44;\n\t"
+      SFQ_CP "[%6], %7;\n\t" SFQ_CP "[fb0], sb0;\n\t" SFQ_CP "[fc0], sc0;\n\t"
+      SFQ_MMA "[%1], %2, %3, %4, [%6], [fb0], p;\n\t"
+      SFQ_CP "[fa1], sa1;\n\t" SFQ_CP "[fb1], sb1;\n\t" SFQ_CP "[fc1], sc1;\n\t"
+      SFQ_MMA "[%1], a1, b1, %4, [fa1], [fb1], pt;\n\t"
+      SFQ_CP "[fa2], sa2;\n\t" SFQ_CP "[fb2], sb2;\n\t" SFQ_CP "[fc2], sc2;\n\t"
+      SFQ_MMA "[%1], a2, b2, %4, [fa2], [fb2], pt;\n\t"
+      SFQ_CP "[fa3], sa3;\n\t" SFQ_CP "[fb3], sb3;\n\t" SFQ_CP "[fc3], sc3;\n\t"
+      SFQ_MMA "[%1], a3, b3, %4, [fa3], [fb3], pt;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%10], m;\n\t"
+      "selp.u32 %0, 1, 0, pn;\n\t}"
+      : "=r"(ready)
+      : "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate_first), "r"(sf_cols), "l"(sf_desc), "r"(next_bar), "r"(next_parity),
+        "r"(commit_bar)
+      : "memory");
+#undef SFQ_CP
+#undef SFQ_MMA
+  return ready;
+}
+
 // One whole pipeline stage of the pair kernel from a single thread: probe the NEXT stage's barrier without blocking,
 // issue this stage's four MMAs (each advances the K offset of both descriptors by two 16-byte units; nvfp4 also
 // advances the scale columns: four per MMA for the activations, `sfb_step` for the weights), then commit to
