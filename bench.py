@@ -559,8 +559,10 @@ def run_case(name, band=0):
         raise SystemExit("unknown case " + name)
     fn(0)
     torch.cuda.synchronize()
-    ms = time_region(torch, fn, reps) / reps
-    print(json.dumps({"case": name, "band": band, "ms_per_launch": ms, "work_per_second": work / (ms * 1e-3),
+    reps = int(os.environ.get("SFQ_CASE_REPS", reps))
+    with ClockSampler(0) as clocks:
+        ms = time_region(torch, fn, reps) / reps
+    print(json.dumps({"case": name, "band": band, "ms_per_launch": ms, "work_per_second": work / (ms * 1e-3), "clocks": clocks.summary(),
                       "device_status": sfq.device_status()}))
 
 
