@@ -183,11 +183,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     // product that read them, and a completed S_t(j+1) also says that O_t holds the sum up to tile j.
     constexpr uint32_t idesc = idesc_bf16(kTile, kTile);
     const uint32_t full_mask = 0xffffffffu;
-    bool ok = __all_sync(full_mask, attn_wait(smem_u32(&sh->q_full), 0, sh, g.status, 13));
+    // A barrier that has already completed costs one non-suspending probe and a vote; only a real wait takes the polling loop.
+    auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (__all_sync(full_mask, mbar_test_wait(smem_u32(bar), parity))) return true;
+      return bool(__all_sync(full_mask, attn_wait(smem_u32(bar), parity, sh, g.status, code)));
+    };
+    bool ok = wait(&sh->q_full, 0, 13);
     auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
       const int st = j & 1;
       // the second query tile reads the K tile the first one has just waited for
-      if (t == 0 && !__all_sync(full_mask, attn_wait(smem_u32(&sh->k_full[st]), (j >> 1) & 1, sh, g.status, 14))) return false;
+      if (t == 0 && !wait(&sh->k_full[st], (j >> 1) & 1, 14)) return false;
       tc_fence_after_sync();
       if (elect_one())  // eight MMAs, the commit for the softmax warps and, behind the second query tile, the one that frees K
         mma_f16_x8_commit(tmem + t * kTile, smem_desc_sw128(smem_u32(q_s + t * kTileBytes)), smem_desc_sw128(smem_u32(k_s + st * kTileBytes)),
@@ -197,8 +202,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     };
     auto issue_pv = [&](int t, int j) {  // O_t += P_t V_j: A = P_t in tensor memory [queries x keys], B = V^T [d x keys]
       const int st = j & 1;
-      if (t == 0 && !__all_sync(full_mask, attn_wait(smem_u32(&sh->v_full[st]), (j >> 1) & 1, sh, g.status, 16))) return false;
-      if (!__all_sync(full_mask, attn_wait(smem_u32(&sh->p_full[t]), j & 1, sh, g.status, 17))) return false;
+      if (t == 0 && !wait(&sh->v_full[st], (j >> 1) & 1, 16)) return false;
+      if (!wait(&sh->p_full[t], j & 1, 17)) return false;
       tc_fence_after_sync();
       if (elect_one())  // 16 keys per MMA: eight 32-bit columns of bf16 pairs
         mma_f16_ts_x8_commit(tmem + 2 * kTile + t * kTile, tmem + t * kTile, smem_desc_sw128(smem_u32(v_s + st * kTileBytes)), idesc,
