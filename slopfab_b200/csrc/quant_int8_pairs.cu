@@ -6,7 +6,7 @@
 // wider rows with two to four). That kernel is bound by instruction
 // issue, not by HBM, so this one halves the instruction count per row:
 //   * a thread holds its 16 elements of TWO rows as 16 fp32x2 pairs (row r in the low half, row r+1 in the high
-//     half); every butterfly add, the 1/16 scale and the quotient refinement are one add/mul/fma.rn.f32x2 for both;
+//     half); every butterfly add, the 1/16 scale and the quotient are one add/mul.rn.f32x2 for both;
 //   * the in-group transposes move 64-bit pairs (half the shared-memory instructions);
 //   * the absolute maximum runs on bf16x2 words (both rows per max.bf16x2);
 //   * the rotated values are quantized in the transposed layout; the int8 bytes of both rows go to shared memory as
@@ -51,11 +51,6 @@ __device__ __forceinline__ f2 sub2(f2 a, f2 b) {
 __device__ __forceinline__ f2 mul2(f2 a, f2 b) {
   f2 d;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
-  f2 d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
 // bf16x2 word: low half = round(lo), high half = round(hi)
