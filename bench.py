@@ -477,6 +477,27 @@ def run_case(name, band=0):
         fn = lambda i: sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(a8), sfq.ptr(w8), C.byref(ep), sfq.ptr(y), m, n, k,  # noqa: E731
                                                        sfq.stream_ptr()))
         work = 2.0 * m * n * k
+    elif name in ("gemm_w4a8_fused", "gemm_w4a8_unpack_then_gemm"):
+        # W4A8 Linear at M rows (env SFQ_W4_ROWS, default 16384), weight in storage form: the int8 rows produced inside the GEMM,
+        # against the stand-alone expansion into a dense copy followed by the int8 GEMM (what `forward` does without `prepare`)
+        m = int(os.environ.get("SFQ_W4_ROWS", "16384"))
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        a8 = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
+        packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+        gs = torch.randint(0x28, 0x39, (n * k // 16,), dtype=torch.uint8, device="cuda")
+        book = (torch.arange(16, dtype=torch.float32, device="cuda") - 8.0)
+        w8 = torch.empty((n, k), dtype=torch.int8, device="cuda")
+        rs, cs = torch.rand(m, device="cuda") * 0.01, torch.rand(n, device="cuda") * 0.01
+        ep = sfq.Epilogue(sfq.ptr(rs), sfq.ptr(cs), 1.0, None, sfq.F32, sfq.ACT_NONE)
+        if name == "gemm_w4a8_fused":
+            fn = lambda i: sfq.check(sfq.lib.sfq_gemm_w4a8_fused(sfq.ptr(a8), sfq.ptr(packed), sfq.ptr(gs), sfq.ptr(book), C.byref(ep),  # noqa: E731
+                                                                 sfq.ptr(y), m, n, k, sfq.stream_ptr()))
+        else:
+            def fn(i):
+                sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(packed), sfq.ptr(gs), sfq.ptr(book), sfq.ptr(w8), n, k, 16, sfq.stream_ptr()))
+                sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(a8), sfq.ptr(w8), C.byref(ep), sfq.ptr(y), m, n, k, sfq.stream_ptr()))
+        work = 2.0 * m * n * k
+        reps = 10
     elif name == "gemm_int8_c2":
         # the benchmark's own GEMM (config 2) on four rotating operand sets, so that a captured launch reads cold data
         m, reps = 4096, 7

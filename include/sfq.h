@@ -253,6 +253,15 @@ SFQ_API int sfq_add_gated(void* d_x_bf16, const void* d_branch_bf16, const float
  * accumulators and therefore the bf16 output are bit-exact. K % 16 == 0. */
 SFQ_API int sfq_gemm_int8(const int8_t* d_q, const int8_t* d_w8, const sfq_epilogue* ep, void* d_y_bf16,
                           int M, int N, int K, void* stream);
+/* The same product with the weight still in its W4A8 storage form: nibbles [N, K/2] (element e of a group in nibble e),
+ * e4m3 group scales [N, K/16] and the 16-entry codebook. The int8 weight rows are produced in shared memory inside the
+ * GEMM, K-slab by K-slab (dequant_weight_kernel's arithmetic, src/cuda/w4a8.cu:44-68), instead of by sfq_unpack_w4a8_int8 into a
+ * dense [N, K] copy; accumulators and output bits are those of sfq_unpack_w4a8_int8 + sfq_gemm_int8. No counterpart in the
+ * reference, which always materialises the int8 weight. K % 128 == 0; bias and GELU allowed, no gate, no SwiGLU; nibbles and
+ * codebook 16-byte aligned, group scales 8-byte aligned. Returns an error (and launches nothing) where that does not hold. */
+SFQ_API int sfq_gemm_w4a8_fused(const int8_t* d_q, const uint8_t* d_w_packed, const uint8_t* d_group_scale,
+                                const float* d_codebook, const sfq_epilogue* ep, void* d_y_bf16, int M, int N, int K,
+                                void* stream);
 /* y = epilogue(global * sum(a_fp4 * w_fp4 * block scales)). Replaces nvfp4_gemm_forward_q
  * (include/slopfab/cuda/nvfp4_gemm.cuh:101-113). Activations in the GEMM_FEED layout. */
 SFQ_API int sfq_gemm_nvfp4(const uint8_t* d_a_packed, const uint8_t* d_a_scale_tiled, const uint8_t* d_w_packed,

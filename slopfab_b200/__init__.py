@@ -92,6 +92,7 @@ def _load() -> C.CDLL:
         "sfq_swiglu": (I, [V, V, I, I, V]),
         "sfq_add_gated": (I, [V, V, V, V, I, I, V]),
         "sfq_gemm_int8": (I, [V, V, P(Epilogue), V, I, I, I, V]),
+        "sfq_gemm_w4a8_fused": (I, [V, V, V, V, P(Epilogue), V, I, I, I, V]),
         "sfq_gemm_nvfp4": (I, [V, V, V, V, P(Epilogue), V, I, I, I, V]),
         "sfq_gemm_bf16": (I, [V, V, P(Epilogue), V, I, I, I, V]),
         "sfq_test_gemm_variant": (None, [I, I, I]),
@@ -144,7 +145,7 @@ lib = _load()
 EXPORTS = ("sfq_last_error sfq_version sfq_quant_weight_init sfq_device_status sfq_pack_nvfp4 sfq_pack_w4a8 "
            "sfq_pack_w6a8 sfq_pack_int8 sfq_unpack_nvfp4_bf16 sfq_unpack_w4a8_int8 sfq_unpack_w6a8_int8 "
            "sfq_unpack_int8_bf16 sfq_unpack_int8_f16 sfq_unpack_f8e4m3_bf16 sfq_unpack_nf4_bf16 sfq_pre_quant_scale sfq_rmsnorm sfq_convrot sfq_convrot_f32 sfq_int8_output_bf16 sfq_int8_output_f32 sfq_quantize_f8e4m3 sfq_unpack_nf4_f16 sfq_gemm_nvfp4_reference_layout sfq_quantize_int8_token "
-           "sfq_quantize_nvfp4_block sfq_nvfp4_act_scale_bytes sfq_gelu_tanh sfq_swiglu sfq_add_gated sfq_gemm_int8 "
+           "sfq_quantize_nvfp4_block sfq_nvfp4_act_scale_bytes sfq_gelu_tanh sfq_swiglu sfq_add_gated sfq_gemm_int8 sfq_gemm_w4a8_fused "
            "sfq_gemm_nvfp4 sfq_gemm_bf16 sfq_test_gemm_variant sfq_test_gemm_lost_load sfq_runner_create sfq_runner_destroy sfq_runner_set_native "
            "sfq_runner_native sfq_runner_set_activation sfq_linear_workspace_bytes sfq_linear_dense_weight_bytes "
            "sfq_linear_activation_workspace_bytes sfq_linear_forward sfq_linear_prepare "

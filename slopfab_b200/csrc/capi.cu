@@ -304,6 +304,17 @@ int sfq_gemm_int8(const int8_t* d_q, const int8_t* d_w8, const sfq_epilogue* ep,
                   void* stream) {
   return guarded([&] { sfq::gemm_int8(d_q, d_w8, to_gemm(ep, d_y_bf16, M, N, K), as_stream(stream)); });
 }
+int sfq_gemm_w4a8_fused(const int8_t* d_q, const uint8_t* d_w_packed, const uint8_t* d_group_scale, const float* d_codebook,
+                        const sfq_epilogue* ep, void* d_y_bf16, int M, int N, int K, void* stream) {
+  return guarded([&] {
+    if (!d_q || !d_w_packed || !d_group_scale || !d_codebook) throw std::invalid_argument("sfq_gemm_w4a8_fused: null operand");
+    sfq::GemmArgs g = to_gemm(ep, d_y_bf16, M, N, K);
+    g.w4_gscale = d_group_scale;
+    g.w4_codebook = d_codebook;
+    if (M <= 0 || N <= 0 || K <= 0 || !sfq::gemm_pair_w4a8(d_q, d_w_packed, g, as_stream(stream)))
+      throw std::invalid_argument("sfq_gemm_w4a8_fused: needs K % 128 == 0, the plain epilogue and a device that schedules CTA pairs");
+  });
+}
 int sfq_gemm_nvfp4(const uint8_t* d_a_packed, const uint8_t* d_a_scale_tiled, const uint8_t* d_w_packed,
                    const uint8_t* d_w_scale_tiled, const sfq_epilogue* ep, void* d_y_bf16, int M, int N, int K,
                    void* stream) {

@@ -33,7 +33,8 @@ struct Shared {  // lives after the stage ring
   uint64_t empty[8];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t sf_full[8];   // nvfp4: the scale factors of stage s are in TMEM slot s
+  uint64_t sf_full[8];   // one-CTA nvfp4: the scale factors of stage s are in TMEM slot s; pair kernel with W4 expansion: the int8 rows of stage s are written
+  uint64_t w4_full[8];   // pair kernel with W4 expansion: this CTA's nibbles of stage s have landed
   uint32_t tmem_base;
   volatile int abort;
   long long wait_cycles;  // limit of every bounded wait of this launch

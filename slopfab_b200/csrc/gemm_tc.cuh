@@ -29,6 +29,9 @@ struct GemmArgs {
   // nvfp4 block scales, both in the 128x4-tiled layout (512-byte tiles, row tile major)
   const uint8_t* a_scale_tiled = nullptr;
   const uint8_t* w_scale_tiled = nullptr;
+  // W4A8 weight expanded inside the CTA-pair int8 kernel (gemm_pair_w4a8): group scales [N, K/16] e4m3 and the codebook
+  const uint8_t* w4_gscale = nullptr;
+  const float* w4_codebook = nullptr;  // 16 floats, 16-byte aligned
   // bookkeeping
   int* status = nullptr;  // device word; a kernel that gives up waiting stores a non-zero code
   int band_m = 0;         // row tiles per raster band (0 = default)
@@ -50,5 +53,10 @@ void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g
 bool gemm_pair_int8(const int8_t* a, const int8_t* w, const GemmArgs& g, cudaStream_t stream);
 bool gemm_pair_nvfp4(const uint8_t* a_packed, const uint8_t* w_packed, const GemmArgs& g, cudaStream_t stream);
 bool gemm_pair_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream);
+// y = epilogue(int32(q * W^T)) with W given as W4A8 nibbles [N, K/2] + e4m3 group scales [N, K/16] (g.w4_gscale) + codebook
+// (g.w4_codebook): the int8 rows are produced in shared memory inside the kernel, stage by stage, instead of by
+// unpack_w4a8_int8 into a dense [N, K] copy. Same int32 accumulators, hence the same output bits. Needs K % 128 == 0 and the
+// plain epilogue (bias / GELU allowed, no gate, no SwiGLU); returns false without launching when that or the device does not fit.
+bool gemm_pair_w4a8(const int8_t* a, const uint8_t* w_packed, const GemmArgs& g, cudaStream_t stream);
 
 }  // namespace sfq

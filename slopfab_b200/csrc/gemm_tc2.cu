@@ -18,6 +18,7 @@
 // full one instead of a whole one (config 2: 320 tiles over 74 pairs = 4 waves + 24 tiles -> 48 half tiles).
 // Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before TMEM is freed, so
 // neither exits while its partner can still read its shared memory or signal its barriers.
+#include "codec.cuh"
 #include "gemm_common.cuh"
 
 namespace sfq {
@@ -26,12 +27,15 @@ namespace {
 constexpr int kPairBN = 256;
 constexpr int kPairBM = 256;  // rows of a pair's tile, 128 per CTA
 
-template <int KIND, int ACC> struct PairCfg {
+// W4 (int8 only): the weight arrives as W4A8 nibbles (64 bytes per row and K-slab) in a staging area of the stage and is
+// expanded to int8 in the stage's B area by warps 12-15 (see the kernel).
+template <int KIND, int ACC, bool W4 = false> struct PairCfg {
   static constexpr int kStageA = kBM * kSlabBytes;            // this CTA's 128 activation rows
   static constexpr int kStageB = (kPairBN / 2) * kSlabBytes;  // this CTA's 128 of the tile's 256 weight rows
   static constexpr int kStageSfa = KIND == kNvfp4 ? 4 * 512 : 0;      // scales of this CTA's rows, 4 k-blocks
   static constexpr int kStageSfb = KIND == kNvfp4 ? 2 * 4 * 512 : 0;  // scales of ALL 256 weight rows
-  static constexpr int kStageBytes = kStageA + kStageB + kStageSfa + kStageSfb;
+  static constexpr int kStageW4 = W4 ? (kPairBN / 2) * (kSlabBytes / 2) : 0;  // this CTA's 128 weight rows as nibbles
+  static constexpr int kStageBytes = kStageA + kStageB + kStageSfa + kStageSfb + kStageW4;
   static constexpr int kBarrierBytes = 5120;
   static constexpr int kStagingBytes = 8 * 2048;
   static constexpr int kRingBudget = 227 * 1024 - 1024 - kBarrierBytes - kStagingBytes;
@@ -40,7 +44,9 @@ template <int KIND, int ACC> struct PairCfg {
   static constexpr int kSfSlotCols = KIND == kNvfp4 ? 4 * 4 + 4 * (kPairBN / 32) : 0;
   static constexpr int kTmemCols = 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;
-  static constexpr uint32_t kTxBytes = 2u * kStageBytes;  // what both CTAs land per stage (TMA counts whole boxes)
+  // what both CTAs land per stage on the leader's barrier (TMA counts whole boxes); W4: the activations only, the
+  // nibbles are counted on each CTA's own w4_full barrier
+  static constexpr uint32_t kTxBytes = W4 ? 2u * kStageA : 2u * kStageBytes;
   static constexpr uint32_t kTxBytesNarrow = 2u * (kStageA + kStageB / 2 + kStageSfa + kStageSfb / 2);  // 256 x 128 tile
   static_assert(kAccCols + kStages * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kStageBytes % 1024 == 0, "stage bases must keep the 1024-byte swizzle alignment");
@@ -53,13 +59,14 @@ enum { kEpiPlain = 0, kEpiGated = 1, kEpiSwiglu = 2 };
 
 // TAIL: the schedule ends with tiles cut into 128-column halves (see above); without it every tile is 256 wide at
 // compile time.
-template <int KIND, int ACC, int EPI, bool TAIL>
+template <int KIND, int ACC, int EPI, bool TAIL, bool W4 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                  const __grid_constant__ CUtensorMap map_b_narrow, const __grid_constant__ CUtensorMap map_sfb_narrow,
                  GemmArgs g) {
-  using C = PairCfg<KIND, ACC>;
+  static_assert(!W4 || (KIND == kI8 && !TAIL && EPI == kEpiPlain), "the in-kernel W4 expansion is built for the plain int8 kernel");
+  using C = PairCfg<KIND, ACC, W4>;
   constexpr int BN = kPairBN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -111,6 +118,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&sh->full[s]), 1);     // used in the leader: its producer's arrive + both CTAs' bytes
       mbar_init(smem_u32(&sh->empty[s]), 1);    // in each CTA: the pair's MMAs of that stage are done
+      if constexpr (W4) {
+        mbar_init(smem_u32(&sh->w4_full[s]), 1);  // in each CTA: its own nibbles of the stage have landed
+        mbar_init(smem_u32(&sh->sf_full[s]), 8);  // leader: the four expanding warps of each CTA have written their int8 rows
+      }
     }
     for (int a = 0; a < ACC; ++a) {
       mbar_init(smem_u32(&sh->acc_full[a]), 1);    // in each CTA
@@ -149,7 +160,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint8_t* stage = smem + s * C::kStageBytes;
             const uint32_t bar = smem_u32(&sh->full[s]);  // the loads redirect it to the leader's copy
             if (rank == 0) mbar_arrive_expect_tx(bar, narrow ? C::kTxBytesNarrow : C::kTxBytes);
-            if (int(it) != g.test_drop_iteration) {  // test hook: that iteration announces its bytes and leaves the loads out
+            if constexpr (W4) {  // this CTA's 128 weight rows of the slab as nibbles (the map is passed in map_b's place)
+              mbar_arrive_expect_tx(smem_u32(&sh->w4_full[s]), C::kStageW4);
+              tma_load_2d(smem_u32(stage + C::kStageA + C::kStageB), &map_b, ks * (kSlabBytes / 2), tn * BN + int(rank) * (BN / 2),
+                          smem_u32(&sh->w4_full[s]));
+              tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
+            } else if (int(it) != g.test_drop_iteration) {  // test hook: that iteration announces its bytes and leaves the loads out
               tma_load_2d_pair(smem_u32(stage), &map_a, ks * kSlabBytes, tm * kPairBM + int(rank) * kBM, bar);
               if (swiglu)
                 tma_load_2d_pair(smem_u32(stage + C::kStageA), &map_b, ks * kSlabBytes, tn * (BN / 2) + int(rank) * inner, bar);
@@ -200,7 +216,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // nvfp4: this thread also copies the stage's scale atoms shared memory -> TMEM, each k-block's three copies right in
       // front of the MMA that reads them (copy -> MMA from one thread execute in issue order). TMEM scale slot s belongs to
       // stage s: full[s] of this round follows empty[s] of the previous one, i.e. the MMAs that read the slot are done.
-      auto stage_bar = [&](int st) { return smem_u32(&sh->full[st]); };
+      // W4: the expanding warps of both CTAs arrive on sf_full[st] when the stage's int8 weight rows are in place; the
+      // activations' full[st] has normally completed long before and is checked behind it.
+      auto stage_bar = [&](int st) { return smem_u32(W4 ? &sh->sf_full[st] : &sh->full[st]); };
       constexpr uint64_t kSfHi = (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
       const uint32_t sfa0 = ((smem_u32(smem) & 0x3FFFFu) + C::kStageA + C::kStageB) >> 4;
       // The barrier of the NEXT stage is probed (without blocking) in the same breath as a stage's MMAs are issued, so
@@ -217,6 +235,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int ks = 0; ks < k_stages; ++ks) {
           if (!__all_sync(0xffffffffu, ready != 0)) {
             if (!(ok = wait_barrier_warp(stage_bar(s), ph, sh, g.status, 3))) break;
+          }
+          if constexpr (W4) {
+            if (!(ok = wait_barrier_warp(smem_u32(&sh->full[s]), ph, sh, g.status, 7))) break;
           }
           tc_fence_after_sync();
           const int s_next = s + 1 == C::kStages ? 0 : s + 1;
@@ -266,7 +287,79 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp >= 12) {
     reg_dec<kRegsLean>();
-    // (no role in the pair kernel: the scale copies are issued by the MMA thread)
+    // ------------------------------------------------------------ W4A8 nibbles -> int8 rows of the B tile (both CTAs)
+    if constexpr (W4) {
+      // q = clamp(rint(codebook[code] * e4m3(scale)), -127, 127) (dequant_weight_kernel, src/cuda/w4a8.cu:44-68) through a
+      // table q[scale byte][code] built once per CTA, as in the stand-alone unpacker: a group of 16 weights is one 16-byte
+      // table row and four byte-permute lookups. Thread r owns weight row r of the CTA's 128: 64 bytes of nibbles and 8
+      // scale bytes per stage in, 128 bytes out, written where the 128-byte swizzle puts the row's eight 16-byte units.
+      __shared__ __align__(16) uint8_t table[256 * 16];
+      const int et = threadIdx.x - 384;  // 0..127
+      for (int e = et; e < 256; e += 128) {
+        const float sc = e4m3_decode(uint8_t(e));
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 c = __ldg(reinterpret_cast<const float4*>(g.w4_codebook) + j);
+          const float cc[4] = {c.x, c.y, c.z, c.w};
+          uint32_t acc = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc |= uint32_t(uint8_t(max(-127, min(127, __float2int_rn(cc[i] * sc))))) << (8 * i);
+          w[j] = acc;
+        }
+        reinterpret_cast<uint4*>(table)[e] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      const uint4* trow = reinterpret_cast<const uint4*>(table);
+      const uint32_t b_full_leader = map_to_rank(smem_u32(&sh->sf_full[0]), 0);
+      const int groups_per_row = g.K / 16;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_work && ok; t += num_pairs) {
+        int tm, tn, n_off, n_cols;
+        work_item(t, tm, tn, n_off, n_cols);
+        const int wrow = tn * BN + int(rank) * (BN / 2) + et;  // this thread's weight row (output channel)
+        const uint8_t* srow = g.w4_gscale + size_t(min(wrow, g.N - 1)) * groups_per_row;
+        uint2 sc_next = __ldg(reinterpret_cast<const uint2*>(srow));  // 8 scale bytes of the first slab
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          const uint2 sc = sc_next;
+          if (ks + 1 < k_stages) sc_next = __ldg(reinterpret_cast<const uint2*>(srow + (ks + 1) * 8));
+          // the nibbles have landed; the producer issued them only after empty[s], so the B area is free as well
+          if (!(ok = wait_barrier_warp(smem_u32(&sh->w4_full[s]), ph, sh, g.status, 6))) break;
+          uint8_t* stage = smem + s * C::kStageBytes;
+          const uint4* src = reinterpret_cast<const uint4*>(stage + C::kStageA + C::kStageB) + et * 4;  // 64 bytes per row
+          uint8_t* dst = stage + C::kStageA + et * kSlabBytes;
+          const uint32_t swz = uint32_t(et & 7);
+          const uint32_t scw[2] = {sc.x, sc.y};
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {  // 16 bytes of nibbles = two groups of 16 weights
+            const uint4 raw = src[q4];
+            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int grp = q4 * 2 + h;
+              const uint4 row = trow[(scw[grp >> 2] >> (8 * (grp & 3))) & 0xFFu];
+              uint32_t o[4];
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const uint32_t codes = (words[h * 2 + (w >> 1)] >> (16 * (w & 1))) & 0xFFFFu;  // four nibbles = elements 4w .. 4w+3
+                const uint32_t sel = codes & 0x7777u;                                          // index inside an 8-entry half
+                const uint32_t lo = __byte_perm(row.x, row.y, sel), hi = __byte_perm(row.z, row.w, sel);
+                const uint32_t b3 = ((codes >> 3) & 1u) | ((codes >> 7) & 1u) << 8 | ((codes >> 11) & 1u) << 16 | ((codes >> 15) & 1u) << 24;
+                const uint32_t mask = b3 * 0xFFu;
+                o[w] = (lo & ~mask) | (hi & mask);
+              }
+              *reinterpret_cast<uint4*>(dst + ((uint32_t(grp) ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+          fence_proxy_async();  // the rows are read by the tensor core's proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(b_full_leader + uint32_t(s) * 8u);
+        }
+      }
+    }
   } else {
     reg_inc<kRegsEpilogue>();
     // ------------------------------------------------------------ epilogue (8 warps, both CTAs)
@@ -515,6 +608,66 @@ bool gemm_pair_nvfp4(const uint8_t* a, const uint8_t* w, const GemmArgs& g, cuda
 }
 bool gemm_pair_bf16(const __nv_bfloat16* a, const __nv_bfloat16* w, const GemmArgs& g, cudaStream_t stream) {
   return launch_pair<kBf16, 2>(a, w, size_t(g.K) * 2, g, stream);
+}
+
+bool gemm_pair_w4a8(const int8_t* a, const uint8_t* w_packed, const GemmArgs& g, cudaStream_t stream) {
+  using C = PairCfg<kI8, 2, true>;
+  if (g.K % kSlabBytes != 0 || g.act == SFQ_ACT_SWIGLU || g.gate != nullptr || !g.w4_gscale || !g.w4_codebook) return false;
+  if (reinterpret_cast<uintptr_t>(g.w4_codebook) % 16 != 0 || reinterpret_cast<uintptr_t>(g.w4_gscale) % 8 != 0 ||
+      reinterpret_cast<uintptr_t>(w_packed) % 16 != 0)
+    throw std::invalid_argument("sfq gemm: W4A8 nibbles and codebook must be 16-byte aligned, the group scales 8-byte aligned");
+  auto kernel = gemm_pair_kernel<kI8, 2, kEpiPlain, false, true>;
+  reserve_dynamic_smem(reinterpret_cast<const void*>(kernel), C::kSmemBytes, "sfq gemm");
+  static PerDevice<int> cache;
+  const int pairs_fit = cache.get([&] {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      return 0;
+    }
+    return clusters;
+  });
+  if (pairs_fit <= 0) return false;
+  const CUtensorMap ma = make_map(a, size_t(g.M), size_t(g.K), kBM);
+  // nibbles [N, K/2]: boxes of 64 bytes x 128 rows, unswizzled, zero beyond the array
+  CUtensorMap mw;
+  {
+    const cuuint64_t dims[2] = {cuuint64_t(g.K) / 2, cuuint64_t(g.N)};
+    const cuuint64_t strides[1] = {cuuint64_t(g.K) / 2};
+    const cuuint32_t box[2] = {kSlabBytes / 2, kPairBN / 2};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode_fn()(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w_packed), dims, strides, box, elem,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("sfq gemm: cuTensorMapEncodeTiled failed for the W4A8 nibbles (" + std::to_string(int(r)) + ")");
+  }
+  const int tiles = ((g.M + kPairBM - 1) / kPairBM) * ((g.N + kPairBN - 1) / kPairBN);
+  int pairs_cap = pairs_fit;
+  if (g.max_ctas > 0) pairs_cap = std::max(1, std::min(pairs_cap, g.max_ctas / 2));
+  GemmArgs ga = g;
+  ga.tail_split = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * std::min(tiles, pairs_cap));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, ma, ma, ma, ma, ga);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("sfq gemm: pair launch failed: ") + cudaGetErrorString(e));
+  return true;
 }
 
 }  // namespace sfq

@@ -59,6 +59,50 @@ def test_gemm_int8_bit_exact(M, N, K, tile_n):
         sfq.lib.sfq_test_gemm_variant(0, 0, 0)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 512, 1024), (257, 384, 2048), (1000, 5120, 5120), (4096, 1280, 13824)])
+def test_w4a8_expanded_inside_the_gemm_equals_unpack_then_gemm(M, N, K):
+    """The int8 weight rows produced in shared memory inside the GEMM are those of the stand-alone unpacker, so the int32
+    accumulators and every output bit agree with unpack + GEMM (which the tests above pin to the oracle); the oracle's own
+    decode is checked directly on a sample of rows."""
+    packed, s_rel, s_ch, book = synthetic_packed_int8(4, 16, N, K, seed=M + N + K)
+    rng = np.random.default_rng(M * 3 + K)
+    a = rng.integers(-128, 128, size=(M, K), dtype=np.int8)
+    rs = (rng.random(M, dtype=np.float32) * 0.05 + 1e-3).astype(np.float32)
+    bias = (0.01 * rng.standard_normal(N)).astype(np.float32)
+    da, dp, dg, dbk, drs, dcs, db = dev(a), dev(packed), dev(s_rel), dev(book), dev(rs), dev(s_ch), dev(bias)
+    w8 = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    sfq.check(sfq.lib.sfq_unpack_w4a8_int8(sfq.ptr(dp), sfq.ptr(dg), sfq.ptr(dbk), sfq.ptr(w8), N, K, 16, S))
+    for use_bias, act in ((False, sfq.ACT_NONE), (True, sfq.ACT_GELU_TANH)):
+        ep = sfq.Epilogue(sfq.ptr(drs), sfq.ptr(dcs), 1.0, sfq.ptr(db) if use_bias else None, sfq.F32, act)
+        want = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        sfq.check(sfq.lib.sfq_gemm_int8(sfq.ptr(da), sfq.ptr(w8), C.byref(ep), sfq.ptr(want), M, N, K, S))
+        for rep in range(2):  # twice: the second launch starts from warm barriers' other phase
+            got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            sfq.check(sfq.lib.sfq_gemm_w4a8_fused(sfq.ptr(da), sfq.ptr(dp), sfq.ptr(dg), sfq.ptr(dbk), C.byref(ep), sfq.ptr(got), M, N, K, S))
+            _status_clean()
+            bad = int((got.view(torch.int16) != want.view(torch.int16)).sum())
+            assert bad == 0, f"{bad} of {M * N} outputs differ (bias={use_bias}, launch {rep})"
+    # against the oracle's decode and integer product on a few rows of the activation
+    rows = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, size=6)]))
+    w_ref = w8.cpu().numpy()
+    acc = oracle.int8_gemm(np.ascontiguousarray(a[rows]), w_ref)
+    out = np.empty((len(rows), N), np.uint16)
+    oracle.lib.orc_w4a8_output_bf16(P(acc), P(np.ascontiguousarray(rs[rows])), P(s_ch), len(rows), N, P(out))
+    ep = sfq.Epilogue(sfq.ptr(drs), sfq.ptr(dcs), 1.0, None, sfq.F32, sfq.ACT_NONE)
+    got = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sfq.check(sfq.lib.sfq_gemm_w4a8_fused(sfq.ptr(da), sfq.ptr(dp), sfq.ptr(dg), sfq.ptr(dbk), C.byref(ep), sfq.ptr(got), M, N, K, S))
+    assert np.array_equal(bits(got)[rows], out)
+
+
+def test_w4a8_fused_refuses_what_it_does_not_cover():
+    M, N, K = 128, 256, 192  # K is not a multiple of 128
+    z = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    ep = sfq.Epilogue(sfq.ptr(z), sfq.ptr(z), 1.0, None, sfq.F32, sfq.ACT_NONE)
+    assert sfq.lib.sfq_gemm_w4a8_fused(sfq.ptr(z), sfq.ptr(z), sfq.ptr(z), sfq.ptr(z), C.byref(ep), sfq.ptr(y), M, N, K, S) != 0
+    assert sfq.lib.sfq_gemm_w4a8_fused(None, sfq.ptr(z), sfq.ptr(z), sfq.ptr(z), C.byref(ep), sfq.ptr(y), M, N, 256, S) != 0
+
+
 def test_gemm_int8_multi_tile_persistence():
     # more tiles than SMs, ragged M, several raster bands: every CTA walks several tiles through both accumulators
     M, N, K = 128 * 37 - 8, 1536, 512
