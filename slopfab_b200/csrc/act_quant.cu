@@ -596,7 +596,8 @@ void quantize_nvfp4_block(const __nv_bfloat16* x, const NormArgs& norm, uint8_t*
   if (layout != SFQ_NVFP4_ACT_REFERENCE && layout != SFQ_NVFP4_ACT_GEMM_FEED) throw std::invalid_argument("quantize_nvfp4_block: unknown layout");
   if (layout == SFQ_NVFP4_ACT_GEMM_FEED && dim % 64 != 0)
     throw std::invalid_argument("quantize_nvfp4_block: the tiled scale layout needs dim % 64 == 0");
-  if (norm.weight == nullptr && reinterpret_cast<uintptr_t>(x) % 16 == 0) {  // no norm in front: the barrier-free kernel
+  if (norm.weight == nullptr) {  // no norm in front: the barrier-free kernel
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0) throw std::invalid_argument("quantize_nvfp4_block: activation pointer must be 16-byte aligned");
     if (layout == SFQ_NVFP4_ACT_REFERENCE)
       launch_nvfp4_flat<false>(x, packed, scales, rows, dim, stream);
     else

@@ -242,6 +242,42 @@ def test_nvfp4_activation_quantizer_reference_layout(golden):
                                             sfq.NVFP4_ACT_REFERENCE, S) == sfq.ERR_RUNTIME
 
 
+@pytest.mark.parametrize("rows,dim,offset", [(257, 13824, 0), (1, 64, 0), (129, 5120, 4), (64, 256, 4)])
+def test_nvfp4_activation_quantizer_both_kernels_agree_with_the_oracle(rows, dim, offset):
+    """The barrier-free walk writes the oracle's bytes, outliers included, in both layouts (an odd number of blocks exercises
+    its tail); an input that starts 8 bytes off a 16-byte boundary is refused, as by the row kernel before it."""
+    x = gaussian_bf16((rows, dim), seed=rows + dim, outliers=True)
+    flat = torch.empty(rows * dim + 8, dtype=torch.bfloat16, device="cuda")
+    dx = flat[offset:offset + rows * dim].view(rows, dim)
+    dx.copy_(bf16_tensor(x))
+    assert dx.data_ptr() % 16 == (8 if offset else 0)
+    wp, ws, _ = oracle.nvfp4_quantize_act(x)
+    packed = torch.empty((rows, dim // 2), dtype=torch.uint8, device="cuda")
+    scales = torch.empty((rows, dim // 16), dtype=torch.uint8, device="cuda")
+    if offset:
+        assert sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(packed), sfq.ptr(scales), None, rows, dim,
+                                                sfq.NVFP4_ACT_REFERENCE, S) != 0
+        return
+    sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(packed), sfq.ptr(scales), None, rows, dim,
+                                               sfq.NVFP4_ACT_REFERENCE, S))
+    assert np.array_equal(_u8(packed), wp) and np.array_equal(_u8(scales), ws)
+    if dim % 64 == 0:
+        nb = sfq.lib.sfq_nvfp4_act_scale_bytes(rows, dim)
+        fp = torch.empty_like(packed)
+        fs = torch.full((nb,), 0x55, dtype=torch.uint8, device="cuda")
+        sfq.check(sfq.lib.sfq_quantize_nvfp4_block(sfq.ptr(dx), None, sfq.ptr(fp), sfq.ptr(fs), None, rows, dim,
+                                                   sfq.NVFP4_ACT_GEMM_FEED, S))
+        assert np.array_equal(_u8(fp), ((wp << 4) | (wp >> 4)).astype(np.uint8))
+        blocks = dim // 16
+        slots = np.array([[oracle.lib.orc_nvfp4_scale_slot(r, b, blocks) for b in range(blocks)] for r in range(min(rows, 130))])
+        got = _u8(fs)
+        assert np.array_equal(got[slots], ws[:slots.shape[0]])
+        used = np.zeros(nb, bool)
+        used[slots.ravel()] = True
+        if rows <= 130:
+            assert not got[~used].any()  # the padding rows of the last 128-row tile
+
+
 def test_pointwise_kernels_match_reference():
     rng = np.random.default_rng(1)
     rows, inner = 6, 512
