@@ -120,7 +120,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       mbar_init(smem_u32(&sh->empty[s]), 1);    // in each CTA: the pair's MMAs of that stage are done
       if constexpr (W4) {
         mbar_init(smem_u32(&sh->w4_full[s]), 1);  // in each CTA: its own nibbles of the stage have landed
-        mbar_init(smem_u32(&sh->sf_full[s]), 8);  // leader: the four expanding warps of each CTA have written their int8 rows
+        mbar_init(smem_u32(&sh->sf_full[s]), 2);  // leader: the expanding warp of each CTA has written the stage's int8 rows
       }
     }
     for (int a = 0; a < ACC; ++a) {
@@ -291,8 +291,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if constexpr (W4) {
       // q = clamp(rint(codebook[code] * e4m3(scale)), -127, 127) (dequant_weight_kernel, src/cuda/w4a8.cu:44-68) through a
       // table q[scale byte][code] built once per CTA, as in the stand-alone unpacker: a group of 16 weights is one 16-byte
-      // table row and four byte-permute lookups. Thread r owns weight row r of the CTA's 128: 64 bytes of nibbles and 8
-      // scale bytes per stage in, 128 bytes out, written where the 128-byte swizzle puts the row's eight 16-byte units.
+      // table row and byte-permute lookups. Per weight row of the CTA's 128 and stage: 64 bytes of nibbles and 8 scale
+      // bytes in, 128 bytes out, written where the 128-byte swizzle puts the row's eight 16-byte units.
       __shared__ __align__(16) uint8_t table[256 * 16];
       const int et = threadIdx.x - 384;  // 0..127
       for (int e = et; e < 256; e += 128) {
@@ -313,26 +313,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint4* trow = reinterpret_cast<const uint4*>(table);
       const uint32_t b_full_leader = map_to_rank(smem_u32(&sh->sf_full[0]), 0);
       const int groups_per_row = g.K / 16;
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = pair; t < num_work && ok; t += num_pairs) {
+      // Warp e of the four takes every fourth stage whole (its lanes walk the 128 rows in four passes of 32), so that four
+      // stages are being expanded at a time: a stage's chain -- wait, loads, lookups, stores, the fence for the tensor
+      // core's proxy, the arrival -- is several times longer than the 512 cycles the stage's MMAs take, and with one row per
+      // thread and all four warps on the same stage the chains ran one after the other.
+      const int ew = warp - 12;
+      const int my_tiles = pair < num_work ? (num_work - pair + num_pairs - 1) / num_pairs : 0;
+      const uint32_t total_iters = uint32_t(my_tiles) * uint32_t(k_stages);
+      auto scale_rows = [&](uint32_t it, uint2 (&sc)[4]) {  // the 8 scale bytes of this lane's four rows for pipeline iteration `it`
+        const int seq = int(it / uint32_t(k_stages)), ks = int(it - uint32_t(seq) * uint32_t(k_stages));
         int tm, tn, n_off, n_cols;
-        work_item(t, tm, tn, n_off, n_cols);
-        const int wrow = tn * BN + int(rank) * (BN / 2) + et;  // this thread's weight row (output channel)
-        const uint8_t* srow = g.w4_gscale + size_t(min(wrow, g.N - 1)) * groups_per_row;
-        uint2 sc_next = __ldg(reinterpret_cast<const uint2*>(srow));  // 8 scale bytes of the first slab
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
-          const int s = it % C::kStages;
-          const uint32_t ph = (it / C::kStages) & 1;
-          const uint2 sc = sc_next;
-          if (ks + 1 < k_stages) sc_next = __ldg(reinterpret_cast<const uint2*>(srow + (ks + 1) * 8));
-          // the nibbles have landed; the producer issued them only after empty[s], so the B area is free as well
-          if (!(ok = wait_barrier_warp(smem_u32(&sh->w4_full[s]), ph, sh, g.status, 6))) break;
-          uint8_t* stage = smem + s * C::kStageBytes;
-          const uint4* src = reinterpret_cast<const uint4*>(stage + C::kStageA + C::kStageB) + et * 4;  // 64 bytes per row
-          uint8_t* dst = stage + C::kStageA + et * kSlabBytes;
-          const uint32_t swz = uint32_t(et & 7);
-          const uint32_t scw[2] = {sc.x, sc.y};
+        work_item(pair + seq * num_pairs, tm, tn, n_off, n_cols);
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) {
+          const int wrow = min(tn * BN + int(rank) * (BN / 2) + p4 * 32 + lane, g.N - 1);
+          sc[p4] = __ldg(reinterpret_cast<const uint2*>(g.w4_gscale + size_t(wrow) * groups_per_row + ks * 8));
+        }
+      };
+      uint2 sc_next[4];
+      if (uint32_t(ew) < total_iters) scale_rows(uint32_t(ew), sc_next);
+      bool ok = true;
+      for (uint32_t it = uint32_t(ew); it < total_iters && ok; it += 4) {
+        const int s = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1;
+        uint2 sc[4];
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) sc[p4] = sc_next[p4];
+        if (it + 4 < total_iters) scale_rows(it + 4, sc_next);
+        // the nibbles have landed; the producer issued them only after empty[s], so the B area is free as well
+        if (!(ok = wait_barrier_warp(smem_u32(&sh->w4_full[s]), ph, sh, g.status, 6))) break;
+        uint8_t* stage = smem + s * C::kStageBytes;
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) {
+          const int r = p4 * 32 + lane;
+          const uint4* src = reinterpret_cast<const uint4*>(stage + C::kStageA + C::kStageB) + r * 4;  // 64 bytes per row
+          uint8_t* dst = stage + C::kStageA + r * kSlabBytes;
+          const uint32_t swz = uint32_t(r & 7);
+          const uint32_t scw[2] = {sc[p4].x, sc[p4].y};
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {  // 16 bytes of nibbles = two groups of 16 weights
             const uint4 raw = src[q4];
@@ -347,17 +364,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t codes = (words[h * 2 + (w >> 1)] >> (16 * (w & 1))) & 0xFFFFu;  // four nibbles = elements 4w .. 4w+3
                 const uint32_t sel = codes & 0x7777u;                                          // index inside an 8-entry half
                 const uint32_t lo = __byte_perm(row.x, row.y, sel), hi = __byte_perm(row.z, row.w, sel);
-                const uint32_t b3 = ((codes >> 3) & 1u) | ((codes >> 7) & 1u) << 8 | ((codes >> 11) & 1u) << 16 | ((codes >> 15) & 1u) << 24;
-                const uint32_t mask = b3 * 0xFFu;
-                o[w] = (lo & ~mask) | (hi & mask);
+                o[w] = __byte_perm(lo, hi, 0x3210u | ((codes & 0x8888u) >> 1));  // byte i from `hi` when bit 3 of code i is set
               }
               *reinterpret_cast<uint4*>(dst + ((uint32_t(grp) ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
-          fence_proxy_async();  // the rows are read by the tensor core's proxy
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(b_full_leader + uint32_t(s) * 8u);
         }
+        fence_proxy_async();  // the rows are read by the tensor core's proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(b_full_leader + uint32_t(s) * 8u);
       }
     }
   } else {

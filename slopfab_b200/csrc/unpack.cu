@@ -54,8 +54,8 @@ unpack_nvfp4_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict_
 // A group's 16 outputs depend only on its scale byte and its codes, and there are 256 scale bytes: every CTA first
 // builds the table q[scale byte][code] (4 KB of shared memory, the reference's expression evaluated once per
 // entry), then walks groups. For a group, one 16-byte shared load fetches the table row of its scale; four codes
-// at a time are looked up with byte permutes (two 8-entry halves of the row, selected by bit 3 of each code), so a
-// group costs ~30 instructions instead of ~170 and the kernel runs at memory speed.
+// at a time are looked up with three byte permutes (the two 8-entry halves of the row, then a per-byte choice between them
+// by bit 3 of each code), so a group costs ~20 instructions instead of ~170 and the kernel runs at memory speed.
 __global__ void __launch_bounds__(kThreads)
 unpack_w4a8_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ gscale,
                    const float* __restrict__ codebook, int8_t* __restrict__ out, size_t groups) {
@@ -89,10 +89,8 @@ unpack_w4a8_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict
       const uint32_t codes = (words[w >> 1] >> (16 * (w & 1))) & 0xFFFFu;      // four nibbles = elements 4w .. 4w+3
       const uint32_t sel = codes & 0x7777u;                                   // index inside an 8-entry half
       const uint32_t lo = __byte_perm(row.x, row.y, sel), hi = __byte_perm(row.z, row.w, sel);
-      // bit 3 of each code, spread to a full-byte mask in that element's output byte
-      const uint32_t b3 = ((codes >> 3) & 1u) | ((codes >> 7) & 1u) << 8 | ((codes >> 11) & 1u) << 16 | ((codes >> 15) & 1u) << 24;
-      const uint32_t mask = b3 * 0xFFu;
-      o[w] = (lo & ~mask) | (hi & mask);
+      // output byte i comes from `hi` when bit 3 of code i is set: a third permute whose selector is i + 4 * bit3(i)
+      o[w] = __byte_perm(lo, hi, 0x3210u | ((codes & 0x8888u) >> 1));
     }
     reinterpret_cast<uint4*>(out)[g] = make_uint4(o[0], o[1], o[2], o[3]);
   };
