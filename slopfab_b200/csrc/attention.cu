@@ -81,6 +81,11 @@ __device__ __forceinline__ bool attn_wait(uint32_t bar, uint32_t parity, AttnSha
   }
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {  // one instruction on sm_100
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -269,7 +274,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #pragma unroll
       for (int i = 0; i < 32; i += 8)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) m4[k] = fmaxf(m4[k], fmaxf(__uint_as_float(r[c][i + 2 * k]), __uint_as_float(r[c][i + 2 * k + 1])));
+        for (int k = 0; k < 4; ++k) m4[k] = max3(m4[k], __uint_as_float(r[c][i + 2 * k]), __uint_as_float(r[c][i + 2 * k + 1]));
       return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
     };
     for (int j = 0; j < tiles; ++j) {
