@@ -14,10 +14,12 @@
 //               product straight from TMEM, where it overwrites the first 64 columns of the scores it was computed from
 //   warps 4-7   softmax of query tile 0, warps 8-11 of query tile 1 (warps 2-3 only hand their registers over: the
 //               softmax warpgroups run with 216 registers, the first warpgroup with 56), one query row per thread with all 128 keys of the
-//               tile: S from TMEM, running maximum and sum, P = exp2(s - m) as bf16 pairs back into TMEM, and - only
-//               when a row's maximum has grown by more than 2^8 since the accumulator was last scaled - a rescale of
-//               O in TMEM. A stale maximum changes nothing in exact arithmetic (numerator and denominator carry the
-//               same factor) and bounds every p by 2^8.
+//               tile: S from TMEM, P = exp2(s - m) as bf16 pairs back into TMEM, the running sum, and - only when the
+//               tile's probabilities sum to more than 2^15, i.e. the row has outgrown the reference maximum m the
+//               accumulator was last scaled to - the true running maximum, a rescale of O in TMEM and the tile's
+//               probabilities again. A stale reference changes nothing in exact arithmetic (numerator and denominator
+//               carry the same factor); the limit keeps every p far inside the range of bf16 and fp32, and no maximum over
+//               the scores is computed on the common path.
 // Every wait is bounded; a wait that runs out stores a code in the status word and the CTA leaves.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -43,7 +45,7 @@ constexpr int kSlab = kTile * 128;     // 128 rows x 128 bytes: 64 bf16 columns 
 constexpr int kTileBytes = 2 * kSlab;  // [128 x 128] bf16
 constexpr int kAttnThreads = 384;  // warpgroup 0: producer, MMA issuer, two idle warps; warpgroups 1 and 2: the softmax of query tiles 0 and 1
 constexpr int kAttnRegsLean = 56, kAttnRegsSoftmax = 216;  // after setmaxnreg: 128 x 56 + 256 x 216 <= 65536
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr float kTileSumLimit = 32768.0f;  // a key tile's 128 probabilities may sum to this before the reference maximum moves
 
 struct AttnShared {
   uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
@@ -95,12 +97,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // 2^x for a pair of arguments on the FMA pipe instead of the special-function unit, which is what the softmax of two
 // query tiles saturates (32768 exponentials per key tile at 16 per clock = the 2048 cycles the tile's products take).
 // x = n + f with n = round(x), f in [-1/2, 1/2]: a cubic for 2^f (relative error 7.5e-5, a sixtieth of the bf16 rounding
-// the result goes through) and n added into the exponent field. Arguments are at most 2^8 by construction and are clamped
-// at -125 below, where the result (~2e-38) is as good as the zero the hardware instruction returns.
+// the result goes through) and n added into the exponent field. Arguments are clamped at -125 below, where the result
+// (~2e-38) is as good as the zero the hardware instruction returns, and at 126 above: a row that has outgrown its
+// reference by that much must still produce a huge value, which the caller's sum test then catches.
 __device__ __forceinline__ f32x2 exp2_pair_fma(f32x2 x) {
   float x0, x1;
   unpack2(x, x0, x1);
-  const f32x2 xc = pack2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+  const f32x2 xc = pack2(fminf(fmaxf(x0, -125.0f), 126.0f), fminf(fmaxf(x1, -125.0f), 126.0f));
   const f32x2 magic = pack2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
   const f32x2 t = add2(xc, magic);
   const f32x2 f = sub2(xc, sub2(t, magic));
@@ -239,7 +242,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     bool ok = true;
     uint32_t r[4][32];
     const f32x2 scale2 = pack2(g.scale_log2, g.scale_log2);
-    // p = 2^(s * scale - m) <= 2^8 for the 32 keys of chunk c as bf16 pairs, written over columns [16 c, 16 c + 16) of the
+    // p = 2^(s * scale - m) for the 32 keys of chunk c as bf16 pairs, written over columns [16 c, 16 c + 16) of the
     // scores they came from (those columns belong to chunks 0 and 1, which are in registers by then); returns their sum.
     auto emit_chunk = [&](int c, float m, f32x2 sum2) {
       const f32x2 negm2 = pack2(-m, -m);
@@ -264,12 +267,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       tmem_st_32x16(tmem_s + c * 16, pk);
       return sum2;
     };
-    auto chunk_max = [&](int c, int valid) {  // masks the keys past the end of the sequence (last tile only), then the maximum
-      if (valid < kTile) {
+    auto mask_chunk = [&](int c, int valid) {  // the keys past the end of the sequence (last tile only)
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
-      }
+      for (int i = 0; i < 32; ++i)
+        if (c * 32 + i >= valid) r[c][i] = __float_as_uint(-INFINITY);
+    };
+    auto chunk_max = [&](int c) {
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one of 32 steps
 #pragma unroll
       for (int i = 0; i < 32; i += 8)
@@ -281,29 +284,33 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       if (!(ok = __all_sync(0xffffffffu, attn_wait<40>(smem_u32(&sh->s_full[t]), j & 1, sh, g.status, 18)))) break;
       tc_fence_after_sync();
       const int valid = g.seq_kv - j * kTile;  // keys of this tile that exist
-      // The probabilities are computed against the maximum the accumulator was last scaled to, which is known before the
-      // tile arrives: chunk c is exponentiated while chunk c + 1 is still on its way out of tensor memory, and the tile's
-      // own maximum is only gathered along the way to decide afterwards whether the reference has to move.
+      // The probabilities are computed against the reference maximum the accumulator was last scaled to, which is known
+      // before the tile arrives: chunk c is exponentiated while chunk c + 1 is still on its way out of tensor memory. No
+      // maximum is taken on this path: that the reference is still good enough is read off the tile's sum of probabilities.
       f32x2 sum2 = pack2(0.0f, 0.0f);
-      float mx = -INFINITY;
       tmem_ld_32x32(tmem_s, r[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         tmem_ld_wait();
         if (c + 1 < 4) tmem_ld_32x32(tmem_s + (c + 1) * 32, r[c + 1]);
-        mx = fmaxf(mx, chunk_max(c, valid));
+        if (valid < kTile) mask_chunk(c, valid);
         if (j > 0) sum2 = emit_chunk(c, m_used, sum2);
       }
-      const float m_tile = mx * g.scale_log2;  // scale > 0: the maximum commutes with it
-      const bool grow = m_tile > m_used + kRescaleThreshold;  // also true at j == 0 (m_used = -inf)
-      if (__any_sync(0xffffffffu, grow)) {
-        // Rare after the first tiles: a row's maximum has grown by more than 2^8. S_t(j) was issued behind
-        // O_t += P_t V(j-1), so its completion says that O_t is at rest. The warp rescales its 32 rows together (the
-        // TMEM accesses are warp-wide; rows that did not grow use a factor of 1) and computes the tile's probabilities
-        // again against the new reference -- every score is still in registers -- over the ones just written.
-        const float m_new = grow ? m_tile : m_used;
+      float sum0, sum1;
+      unpack2(sum2, sum0, sum1);
+      float tile_sum = sum0 + sum1;
+      const bool over = j == 0 || !(tile_sum <= kTileSumLimit);  // the first tile; a row that outgrew its reference; inf or NaN
+      if (__any_sync(0xffffffffu, over)) {
+        // Rare after the first tiles. The reference becomes the running maximum. S_t(j) was issued behind O_t += P_t V(j-1),
+        // so its completion says that O_t is at rest. The warp rescales its 32 rows together (the TMEM accesses are
+        // warp-wide; rows within their limit use a factor of 1) and computes the tile's probabilities again against the new
+        // reference -- every score is still in registers -- over the ones just written.
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mx = fmaxf(mx, chunk_max(c));
+        const float m_new = over ? fmaxf(m_used, mx * g.scale_log2) : m_used;  // scale > 0: the maximum commutes with it
         if (j > 0) {
-          const float f = grow ? fast_exp2(m_used - m_new) : 1.0f;
+          const float f = over ? fast_exp2(m_used - m_new) : 1.0f;
           l *= f;
           uint32_t o[32];
 #pragma unroll 1
@@ -319,10 +326,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         sum2 = pack2(0.0f, 0.0f);
 #pragma unroll
         for (int c = 0; c < 4; ++c) sum2 = emit_chunk(c, m_used, sum2);
+        unpack2(sum2, sum0, sum1);
+        tile_sum = sum0 + sum1;
       }
-      float sum0, sum1;
-      unpack2(sum2, sum0, sum1);
-      l += sum0 + sum1;
+      l += tile_sum;
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
